@@ -1,0 +1,72 @@
+"""ctypes binding of libarcq.so (the C ABI declared in include/arcq.h).
+
+There is no fallback: if the shared library has not been built, importing this
+module raises, and so does every operator of the package.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libarcq.so")
+
+OK = 0
+ERR_BAD_SHAPE = 1
+ERR_UNSUPPORTED_K = 2
+ERR_NULL_POINTER = 3
+ERR_CUDA = 4
+ERR_ALIGNMENT = 5
+ERR_TIMEOUT = 6
+
+MODE_16 = 16
+MODE_32 = 32
+
+# name -> (restype, argtypes); mirrors include/arcq.h one to one
+_vp, _i64, _i32, _f32 = C.c_void_p, C.c_int64, C.c_int, C.c_float
+SIGNATURES = {
+    "arcq_status_string": (C.c_char_p, [_i32]),
+    "arcq_last_cuda_error": (_i32, []),
+    "arcq_version": (_i32, []),
+    "arcq_sf_bytes": (C.c_size_t, [_i64, _i64]),
+    "arcq_reference_mode": (_i32, [_i32]),
+    "arcq_reorder_quantize_x": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "arcq_rmsnorm_quantize_x": (_i32, [_vp, _vp, _f32, _vp, _i64, _i32, _i32, _vp, _vp, _vp]),
+    "arcq_reorder_quantize_w": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "arcq_matmul_nvfp4": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp]),
+    "arcq_matmul_nvfp4_dev_alpha": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "arcq_gemm_poll_error": (_i32, []),
+    "arcq_absmax_bf16": (_i32, [_vp, _i64, _vp, _i32, _vp]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m arcquant_b200.build` "
+                "(nvcc, sm_100a). There is no CPU or PyTorch fallback.")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+class ArcqError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        lib = load()
+        text = lib.arcq_status_string(status).decode()
+        extra = f" (cudaError {lib.arcq_last_cuda_error()})" if status == ERR_CUDA else ""
+        super().__init__(f"{where}: {text}{extra}")
+        self.status = status
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        raise ArcqError(status, where)

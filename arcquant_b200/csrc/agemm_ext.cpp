@@ -1,0 +1,131 @@
+// Python extension module `agemm`: the operator surface of ARCQuant's torch extension
+// (kernels/src/bindings.cpp:551-582) on top of libarcq.so's C ABI.  Same function names, argument
+// order and return types for the four quantized-linear operators; outputs are allocated here with
+// torch::empty, inputs are borrowed, kernels run on torch's current CUDA stream.  The reference's
+// KV-cache operators (batch_decode_*, init_kv_*, append_kv_*) are not part of this library.
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include <sstream>
+#include <stdexcept>
+#include <tuple>
+
+#include "arcq.h"
+
+namespace {
+
+void check_status(int status, const char* where) {
+  if (status == ARCQ_OK) return;
+  std::ostringstream os;
+  os << "Value error in " << where << ": " << arcq_status_string(status);
+  if (status == ARCQ_ERR_CUDA) os << " (cudaError " << arcq_last_cuda_error() << ")";
+  throw std::runtime_error(os.str());
+}
+
+void* current_stream(const torch::Tensor& t) {
+  return static_cast<void*>(c10::cuda::getCurrentCUDAStream(t.device().index()).stream());
+}
+
+void require_cuda(const torch::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor (this library has no CPU path)");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+std::tuple<torch::Tensor, torch::Tensor> quantize_common(const torch::Tensor& X, const torch::Tensor* gamma,
+                                                         float eps, const torch::Tensor& reorder_index, int KE,
+                                                         bool is_weight, const char* where) {
+  require_cuda(X, "input");
+  require_cuda(reorder_index, "reorder_index");
+  TORCH_CHECK(X.dim() == 2, "input must be 2-D");
+  const int64_t rows = X.size(0);
+  const int KQ = static_cast<int>(X.size(1));
+  const int K = KQ + KE;
+  TORCH_CHECK(reorder_index.numel() == KQ, "reorder_index must have KQ entries");
+  c10::cuda::CUDAGuard guard(X.device());
+  auto options = torch::dtype(torch::kUInt8).device(X.device());
+  auto Q = torch::empty({rows, K / 2}, options);
+  auto SF = torch::empty({static_cast<int64_t>(arcq_sf_bytes(rows, K))}, options);
+  const void* px = X.data_ptr<at::BFloat16>();                 // throws on a wrong dtype, as the reference does
+  const int16_t* pidx = reorder_index.data_ptr<int16_t>();
+  int status;
+  if (gamma) {
+    require_cuda(*gamma, "weight");
+    status = arcq_rmsnorm_quantize_x(px, gamma->data_ptr<at::BFloat16>(), eps, pidx, rows, KQ, KE,
+                                     Q.data_ptr<uint8_t>(), SF.data_ptr<uint8_t>(), current_stream(X));
+  } else if (is_weight) {
+    status = arcq_reorder_quantize_w(px, pidx, rows, KQ, KE, arcq_reference_mode(KQ), Q.data_ptr<uint8_t>(),
+                                     SF.data_ptr<uint8_t>(), current_stream(X));
+  } else {
+    status = arcq_reorder_quantize_x(px, pidx, rows, KQ, KE, arcq_reference_mode(KQ), Q.data_ptr<uint8_t>(),
+                                     SF.data_ptr<uint8_t>(), current_stream(X));
+  }
+  check_status(status, where);
+  return std::make_tuple(Q, SF);
+}
+
+torch::Tensor matmul(const torch::Tensor& A, const torch::Tensor& B, const torch::Tensor& SFA,
+                     const torch::Tensor& SFB, const float scale) {
+  require_cuda(A, "A");
+  require_cuda(B, "B");
+  require_cuda(SFA, "SFA");
+  require_cuda(SFB, "SFB");
+  const int64_t M = A.size(0), N = B.size(0), K = A.size(1) * 2;
+  c10::cuda::CUDAGuard guard(A.device());
+  auto C = torch::empty({M, N}, torch::dtype(torch::kBFloat16).device(A.device()));
+  int status = arcq_matmul_nvfp4(A.data_ptr<uint8_t>(), B.data_ptr<uint8_t>(), SFA.data_ptr<uint8_t>(),
+                                 SFB.data_ptr<uint8_t>(), M, N, K, scale, C.data_ptr<at::BFloat16>(),
+                                 current_stream(A));
+  check_status(status, "matmul_host_nvfp4_bf16");
+  return C;
+}
+
+// Extra: alpha = alpha_a * alpha_b read on the device (0-dim fp32 CUDA tensors), no host sync.
+torch::Tensor matmul_dev_alpha(const torch::Tensor& A, const torch::Tensor& B, const torch::Tensor& SFA,
+                               const torch::Tensor& SFB, const torch::Tensor& alpha_a,
+                               const c10::optional<torch::Tensor>& alpha_b) {
+  require_cuda(A, "A");
+  require_cuda(B, "B");
+  const int64_t M = A.size(0), N = B.size(0), K = A.size(1) * 2;
+  c10::cuda::CUDAGuard guard(A.device());
+  auto C = torch::empty({M, N}, torch::dtype(torch::kBFloat16).device(A.device()));
+  int status = arcq_matmul_nvfp4_dev_alpha(
+      A.data_ptr<uint8_t>(), B.data_ptr<uint8_t>(), SFA.data_ptr<uint8_t>(), SFB.data_ptr<uint8_t>(), M, N, K,
+      alpha_a.data_ptr<float>(), alpha_b.has_value() ? alpha_b->data_ptr<float>() : nullptr,
+      C.data_ptr<at::BFloat16>(), current_stream(A));
+  check_status(status, "matmul_host_nvfp4_bf16");
+  return C;
+}
+
+std::tuple<torch::Tensor, torch::Tensor> reorder_quantize_x(const torch::Tensor& X,
+                                                            const torch::Tensor& reorder_index, const int KE) {
+  return quantize_common(X, nullptr, 0.f, reorder_index, KE, false, "run_reorder_x_bf16_nvfp4");
+}
+
+std::tuple<torch::Tensor, torch::Tensor> reorder_quantize_w(const torch::Tensor& W,
+                                                            const torch::Tensor& reorder_index, const int KE) {
+  return quantize_common(W, nullptr, 0.f, reorder_index, KE, true, "run_reorder_w_bf16_nvfp4");
+}
+
+std::tuple<torch::Tensor, torch::Tensor> rmsnorm_quantize_x(const torch::Tensor& X, const torch::Tensor& W,
+                                                            const float eps, const torch::Tensor& reorder_index,
+                                                            const int KE) {
+  return quantize_common(X, &W, eps, reorder_index, KE, false, "run_rmsnorm_x_bf16_nvfp4");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("matmul", &matmul, "our ARC gemm (sm_100a)", py::arg("A"), py::arg("B"), py::arg("SFA"), py::arg("SFB"),
+        py::arg("scale"));
+  m.def("reorder_quantize_x", &reorder_quantize_x, "Reorder and quantize activation.", py::arg("X"),
+        py::arg("reorder_index"), py::arg("KE"));
+  m.def("reorder_quantize_w", &reorder_quantize_w, "Reorder and quantize weight.", py::arg("W"),
+        py::arg("reorder_index"), py::arg("KE"));
+  m.def("rmsnorm_quantize_x", &rmsnorm_quantize_x, "RMSNorm, reorder and quantize activation.", py::arg("X"),
+        py::arg("W"), py::arg("eps"), py::arg("reorder_index"), py::arg("KE"));
+  m.def("matmul_dev_alpha", &matmul_dev_alpha, "gemm with device-resident global scales", py::arg("A"),
+        py::arg("B"), py::arg("SFA"), py::arg("SFB"), py::arg("alpha_a"), py::arg("alpha_b") = py::none());
+  m.def("sf_bytes", [](int64_t rows, int64_t k_eff) { return static_cast<int64_t>(arcq_sf_bytes(rows, k_eff)); },
+        "bytes of a scale-factor buffer");
+}

@@ -1,0 +1,155 @@
+// C-ABI entry points of libarcq.so: argument validation, then the kernel launchers.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+
+#include "arcq_internal.h"
+
+namespace arcq {
+
+static thread_local int g_last_cuda_error = 0;
+
+int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  (void)cudaGetLastError();  // clear the sticky "last error" of non-fatal failures
+  return ARCQ_ERR_CUDA;
+}
+
+int get_device_info(DeviceInfo* out) {
+  static std::mutex mu;
+  static DeviceInfo cache[64];
+  static bool have[64] = {};
+  int dev = 0;
+  ARCQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return ARCQ_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!have[dev]) {
+    DeviceInfo d;
+    d.device = dev;
+    ARCQ_CUDA_TRY(cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev));
+    ARCQ_CUDA_TRY(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    cache[dev] = d;
+    have[dev] = true;
+  }
+  *out = cache[dev];
+  return ARCQ_OK;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int check_quant_shape(int64_t rows, int KQ, int KE, int mode) {
+  if (rows < 0 || KQ <= 0 || KE < 0 || KE > KQ) return ARCQ_ERR_BAD_SHAPE;
+  if (mode != ARCQ_MODE_16 && mode != ARCQ_MODE_32) return ARCQ_ERR_BAD_SHAPE;
+  if (KQ % 16 || KE % 16) return ARCQ_ERR_BAD_SHAPE;
+  if (mode == ARCQ_MODE_32 && (KQ % 32 || KE % 32)) return ARCQ_ERR_BAD_SHAPE;
+  if (KQ > 32752) return ARCQ_ERR_UNSUPPORTED_K;  // int16 channel numbers
+  return ARCQ_OK;
+}
+
+}  // namespace arcq
+
+using namespace arcq;
+
+extern "C" {
+
+const char* arcq_status_string(int status) {
+  switch (status) {
+    case ARCQ_OK: return "ok";
+    case ARCQ_ERR_BAD_SHAPE: return "bad shape";
+    case ARCQ_ERR_UNSUPPORTED_K: return "unsupported K";
+    case ARCQ_ERR_NULL_POINTER: return "null pointer";
+    case ARCQ_ERR_CUDA: return "CUDA error";
+    case ARCQ_ERR_ALIGNMENT: return "pointer not 16-byte aligned";
+    case ARCQ_ERR_TIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+  }
+}
+
+int arcq_last_cuda_error(void) { return g_last_cuda_error; }
+
+int arcq_version(void) { return 100; }
+
+size_t arcq_sf_bytes(int64_t rows, int64_t k_eff) {
+  if (rows < 0 || k_eff < 0) return 0;
+  int64_t ncols = k_eff / 16;
+  int64_t ref = (rows / 128 + 1) * 128 * k_eff / 16;
+  int64_t span = ((rows + 127) / 128) * ((ncols + 3) / 4) * 512;
+  return (size_t)(ref > span ? ref : span);
+}
+
+int arcq_reference_mode(int kq) {
+  return (kq == 3584 || kq == 18944 || kq == 27648 || kq == 28672) ? ARCQ_MODE_32 : ARCQ_MODE_16;
+}
+
+int arcq_reorder_quantize_x(const void* x, const int16_t* reorder_index, int64_t M, int KQ, int KE, int mode,
+                            uint8_t* qx, uint8_t* sfx, void* stream) {
+  int rc = check_quant_shape(M, KQ, KE, mode);
+  if (rc != ARCQ_OK) return rc;
+  if (M == 0) return ARCQ_OK;
+  if (!x || !qx || !sfx) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(qx)) return ARCQ_ERR_ALIGNMENT;
+  return launch_quantize(x, nullptr, 0.f, reorder_index, M, KQ, KE, mode, 0, qx, sfx, (cudaStream_t)stream);
+}
+
+int arcq_rmsnorm_quantize_x(const void* x, const void* gamma, float eps, const int16_t* reorder_index,
+                            int64_t M, int KQ, int KE, uint8_t* qx, uint8_t* sfx, void* stream) {
+  int rc = check_quant_shape(M, KQ, KE, ARCQ_MODE_16);
+  if (rc != ARCQ_OK) return rc;
+  int g = KQ / 16;
+  if (g % 32 || g > 512) return ARCQ_ERR_UNSUPPORTED_K;
+  if (M == 0) return ARCQ_OK;
+  if (!x || !gamma || !qx || !sfx) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(qx)) return ARCQ_ERR_ALIGNMENT;
+  return launch_quantize(x, gamma, eps, reorder_index, M, KQ, KE, ARCQ_MODE_16, 0, qx, sfx,
+                         (cudaStream_t)stream);
+}
+
+int arcq_reorder_quantize_w(const void* w, const int16_t* reorder_index, int64_t N, int KQ, int KE, int mode,
+                            uint8_t* qw, uint8_t* sfw, void* stream) {
+  int rc = check_quant_shape(N, KQ, KE, mode);
+  if (rc != ARCQ_OK) return rc;
+  if (N == 0) return ARCQ_OK;
+  if (!w || !qw || !sfw) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(w) || !aligned16(qw)) return ARCQ_ERR_ALIGNMENT;
+  return launch_quantize(w, nullptr, 0.f, reorder_index, N, KQ, KE, mode, 1, qw, sfw, (cudaStream_t)stream);
+}
+
+static int check_gemm(const void* A, const void* B, const void* SFA, const void* SFB, int64_t M, int64_t N,
+                      int64_t K, const void* C) {
+  if (M < 0 || N <= 0 || K <= 0) return ARCQ_ERR_BAD_SHAPE;
+  if (K % 64 || N % 8) return ARCQ_ERR_BAD_SHAPE;
+  if (M > (int64_t)1 << 30 || N > (int64_t)1 << 30 || K > (int64_t)1 << 20) return ARCQ_ERR_BAD_SHAPE;
+  if (M == 0) return ARCQ_OK;
+  if (!A || !B || !SFA || !SFB || !C) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(SFA) || !aligned16(SFB) || !aligned16(C))
+    return ARCQ_ERR_ALIGNMENT;
+  return ARCQ_OK;
+}
+
+int arcq_matmul_nvfp4(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                      int64_t N, int64_t K_eff, float alpha, void* C, void* stream) {
+  int rc = check_gemm(A, B, SFA, SFB, M, N, K_eff, C);
+  if (rc != ARCQ_OK || M == 0) return rc;
+  return launch_gemm(A, B, SFA, SFB, M, N, K_eff, alpha, nullptr, nullptr, C, (cudaStream_t)stream);
+}
+
+int arcq_matmul_nvfp4_dev_alpha(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                                int64_t M, int64_t N, int64_t K_eff, const float* alpha_a,
+                                const float* alpha_b, void* C, void* stream) {
+  int rc = check_gemm(A, B, SFA, SFB, M, N, K_eff, C);
+  if (rc != ARCQ_OK || M == 0) return rc;
+  if (!alpha_a) return ARCQ_ERR_NULL_POINTER;
+  return launch_gemm(A, B, SFA, SFB, M, N, K_eff, 1.0f, alpha_a, alpha_b, C, (cudaStream_t)stream);
+}
+
+int arcq_gemm_poll_error(void) { return gemm_poll_error(); }
+
+int arcq_absmax_bf16(const void* x, int64_t n, float* out, int accumulate, void* stream) {
+  if (n < 0) return ARCQ_ERR_BAD_SHAPE;
+  if (!out || (n > 0 && !x)) return ARCQ_ERR_NULL_POINTER;
+  if (n > 0 && !aligned16(x)) return ARCQ_ERR_ALIGNMENT;
+  return launch_absmax(x, n, out, accumulate, (cudaStream_t)stream);
+}
+
+}  // extern "C"

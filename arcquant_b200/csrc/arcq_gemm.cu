@@ -1,0 +1,447 @@
+// Block-scaled NVFP4 GEMM for sm_100a:  C[M,N] = bf16(alpha * (A.SFA)(B.SFB)^T), fp32 accumulation
+// in tensor memory.  A [M,K/2] and B [N,K/2] hold packed e2m1 codes (K-major, two per byte), SFA/SFB
+// hold one ue4m3 scale per 16 elements in 512-byte atoms of 128 rows x 4 scale columns - exactly
+// what one 128-row, K=64 tcgen05 block-scaled MMA consumes, so an atom travels
+// global -> shared (bulk copy) -> tensor memory (tcgen05.cp) without being touched by a thread.
+//
+// Organisation (one CTA per SM, persistent over output tiles of 128 x BN):
+//   warp 0    producer: per K stage (256 elements = one 128-byte swizzled row) two tiled TMA loads
+//             (A box 128 rows, B box BN rows, 128B swizzle) and the bulk copies of the scale atoms,
+//             all completing on the stage's "full" mbarrier
+//   warp 1    tensor-core issuer: one thread copies the stage's scale atoms into TMEM and issues
+//             four tcgen05.mma.kind::mxf4nvf4.block_scale (M128 x BN x K64) per stage;
+//             tcgen05.commit releases the stage ("empty") and finally publishes the accumulator
+//   warps 2-5 epilogue: tcgen05.ld 32 lanes x 32 columns, scale by alpha, convert to bf16, 64-byte
+//             contiguous global stores per thread; then hand the accumulator back
+// Replaces the CUTLASS sm_120 instantiation of kernels/src/nvfp4.cu in ARCQuant.
+//
+// Every wait on an mbarrier is bounded: after ~2 s without progress the waiting thread raises a
+// CTA-wide abort flag, records ARCQ_ERR_TIMEOUT in a device word the host can poll, and all roles
+// fall through to the common exit, where tensor memory is released.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+
+#include "arcq_internal.h"
+
+namespace arcq {
+namespace {
+
+constexpr int BM = 128;            // rows of A per tile (MMA M)
+constexpr int BK_BYTES = 128;      // bytes of packed codes per row per stage (256 elements)
+constexpr int KSTEPS = 4;          // MMAs (K=64 each) per stage
+constexpr int ATOM = 512;          // bytes of one scale atom
+constexpr int NUM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ int g_gemm_error = 0;   // sticky until polled
+
+template <int BN>
+struct Cfg {
+  static constexpr int NB = BN > 128 ? BN / 128 : 1;           // scale atoms of B per K step
+  static constexpr int A_BYTES = BM * BK_BYTES;                // 16 KB
+  static constexpr int B_BYTES = BN * BK_BYTES;
+  static constexpr int SFA_BYTES = KSTEPS * ATOM;              // 2 KB
+  static constexpr int SFB_BYTES = NB * KSTEPS * ATOM;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 7);
+  static constexpr int SF_COLS = KSTEPS * 4 + KSTEPS * 4 * NB;  // TMEM columns of one stage's scales
+  static constexpr int TMEM_NEED = BN + 2 * SF_COLS;
+  static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
+  // 1 KB alignment slack + stages + barriers; at least ~120 KB so that two CTAs never share an SM
+  static constexpr int SMEM_RAW = 1024 + STAGES * STAGE_BYTES + 256;
+  static constexpr int SMEM_BYTES = SMEM_RAW < 124 * 1024 ? 124 * 1024 : SMEM_RAW;
+};
+
+struct GemmParams {
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  __nv_bfloat16* c;
+  const float* alpha_a;
+  const float* alpha_b;
+  float alpha;
+  int M, N;
+  int ksteps_total;   // K_eff / 64
+  int natoms;         // ceil((K_eff/16)/4): scale atoms per 128-row tile
+  int tiles_m, tiles_n;
+};
+
+// ----------------------------------------------------------------------------- PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false if the CTA is aborting (this wait or another one timed out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        atomicExch(&g_gemm_error, ARCQ_ERR_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t tsfa, uint32_t tsfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%4], [%5], p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tsfa), "r"(tsfb), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading/stride byte offsets
+// (16-byte units), descriptor version 1, swizzle mode.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t sbo_bytes, uint32_t layout_type) {
+  uint32_t lo = (saddr >> 4) & 0x3fffu;                      // LBO = 0: one core matrix along K
+  uint32_t hi = ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (layout_type << 29);
+  return ((uint64_t)hi << 32) | lo;
+}
+constexpr uint32_t LAYOUT_SW128 = 2, LAYOUT_NONE = 0;
+
+// Instruction descriptor of kind::mxf4nvf4 block-scaled MMA: e2m1 x e2m1 (format id 1), ue4m3
+// scales (bit 23 = 0), both operands K-major, N>>3 at bit 17, M>>4 at bit 24, K=64 (bit 31 = 0).
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t instr_desc() {
+  return (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ----------------------------------------------------------------------------- kernel
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // 128B swizzle needs 1 KB alignment
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar_base = base + C::STAGES * C::STAGE_BYTES;
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(base_ptr + C::STAGES * C::STAGE_BYTES + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 1);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+  const uint32_t tmem_full_bar = bar_base + 8u * (2 * C::STAGES);
+  const uint32_t tmem_empty_bar = tmem_full_bar + 8u;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(tmem_full_bar, 1);
+    mbar_init(tmem_empty_bar, 4);
+    misc[1] = 0;  // abort flag
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)misc)),
+                 "r"((uint32_t)C::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = misc[0];
+  const uint32_t tmem_sf = tmem_base + BN;   // two stage-parity buffers of SF_COLS columns each
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int kstages = (p.ksteps_total + KSTEPS - 1) / KSTEPS;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        const int rtb = (tn * BN) / 128;   // first 128-row scale tile of B this output tile touches
+        for (int ks = 0; ks < kstages; ++ks, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+          const int nk = min(KSTEPS, p.ksteps_total - ks * KSTEPS);
+          const uint32_t sf_bytes = (uint32_t)nk * ATOM;
+          const uint32_t st = base + s * C::STAGE_BYTES;
+          mbar_expect_tx(full_bar(s), C::A_BYTES + C::B_BYTES + sf_bytes * (1 + C::NB));
+          tma_load_2d(st, &map_a, full_bar(s), ks * BK_BYTES, tm * BM);
+          tma_load_2d(st + C::A_BYTES, &map_b, full_bar(s), ks * BK_BYTES, tn * BN);
+          const uint8_t* sa = p.sfa + ((size_t)tm * p.natoms + (size_t)ks * KSTEPS) * ATOM;
+          bulk_load(st + C::A_BYTES + C::B_BYTES, sa, sf_bytes, full_bar(s));
+#pragma unroll
+          for (int a = 0; a < C::NB; ++a) {
+            const uint8_t* sb = p.sfb + ((size_t)(rtb + a) * p.natoms + (size_t)ks * KSTEPS) * ATOM;
+            bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + a * (KSTEPS * ATOM), sb, sf_bytes, full_bar(s));
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc<BN>();
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+        const int tn = tile / p.tiles_m;
+        // sub-atom column offset when BN < 128: rows 32j..32j+31 of an atom live in TMEM column j
+        const uint32_t sfb_sub = (BN < 128) ? (uint32_t)(((tn * BN) % 128) / 32) : 0u;
+        if (!mbar_wait(tmem_empty_bar, (tile_it & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        for (int ks = 0; ks < kstages; ++ks, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1u;
+          if (!mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const int nk = min(KSTEPS, p.ksteps_total - ks * KSTEPS);
+          const uint32_t st = base + s * C::STAGE_BYTES;
+          const uint32_t a_s = st, b_s = st + C::A_BYTES;
+          const uint32_t sfa_s = b_s + C::B_BYTES, sfb_s = sfa_s + C::SFA_BYTES;
+          const uint32_t t_sfa = tmem_sf + (it & 1u) * C::SF_COLS;
+          const uint32_t t_sfb = t_sfa + KSTEPS * 4;
+          for (int k = 0; k < nk; ++k) {
+            tc_cp_sf(t_sfa + k * 4, smem_desc(sfa_s + k * ATOM, 128, LAYOUT_NONE));
+#pragma unroll
+            for (int a = 0; a < C::NB; ++a)
+              tc_cp_sf(t_sfb + k * 4 * C::NB + a * 4,
+                       smem_desc(sfb_s + a * (KSTEPS * ATOM) + k * ATOM, 128, LAYOUT_NONE));
+          }
+          for (int k = 0; k < nk; ++k) {
+            const uint64_t adesc = smem_desc(a_s + k * 32, 1024, LAYOUT_SW128);
+            const uint64_t bdesc = smem_desc(b_s + k * 32, 1024, LAYOUT_SW128);
+            tc_mma_nvf4(tmem_base, adesc, bdesc, idesc, t_sfa + k * 4, t_sfb + k * 4 * C::NB + sfb_sub,
+                        (ks | k) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(s));   // stage reusable once these MMAs have read it
+        }
+        if (ok) tc_commit(tmem_full_bar);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;       // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+    float alpha = p.alpha;
+    if (p.alpha_a) alpha *= __ldg(p.alpha_a);
+    if (p.alpha_b) alpha *= __ldg(p.alpha_b);
+    uint32_t tile_it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      ok = mbar_wait(tmem_full_bar, tile_it & 1u, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);   // keep the warp converged for the .sync.aligned loads
+      if (!ok) break;
+      tc_fence_after();
+      const int row = tm * BM + quad * 32 + lane;
+      __nv_bfloat16* crow = p.c + (size_t)row * p.N;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
+        tc_wait_ld();
+        const int col = tn * BN + c0;
+        if (row < p.M && col < p.N) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col + v * 8 < p.N) {   // N is a multiple of 8: whole 16-byte pieces are in or out
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * alpha, __uint_as_float(r[v * 8 + 1]) * alpha);
+              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * alpha, __uint_as_float(r[v * 8 + 3]) * alpha);
+              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * alpha, __uint_as_float(r[v * 8 + 5]) * alpha);
+              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * alpha, __uint_as_float(r[v * 8 + 7]) * alpha);
+              *reinterpret_cast<uint4*>(crow + col + v * 8) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ----------------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encode_fn(EncodeTiledFn* out) {
+  static std::mutex mu;
+  static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    ARCQ_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || !sym) return cuda_fail(cudaErrorNotSupported);
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  *out = fn;
+  return ARCQ_OK;
+}
+
+// Packed-code operand [rows, kbytes] (uint8, row-major) with a box of 128 bytes x box_rows rows.
+int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t kbytes, int box_rows) {
+  EncodeTiledFn fn;
+  int rc = get_encode_fn(&fn);
+  if (rc != ARCQ_OK) return rc;
+  cuuint64_t dims[2] = {(cuuint64_t)kbytes, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)kbytes};
+  cuuint32_t box[2] = {(cuuint32_t)BK_BYTES, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  return ARCQ_OK;
+}
+
+template <int BN>
+int launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int num_sms, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  auto kern = arcq_gemm_kernel<BN>;
+  ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  p.tiles_n = (p.N + BN - 1) / BN;
+  long long tiles = (long long)p.tiles_m * p.tiles_n;
+  int grid = (int)(tiles < num_sms ? tiles : num_sms);
+  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, p);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
+
+}  // namespace
+
+int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M, int64_t N,
+                int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* Cout,
+                cudaStream_t stream) {
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+
+  GemmParams p;
+  p.sfa = SFA;
+  p.sfb = SFB;
+  p.c = static_cast<__nv_bfloat16*>(Cout);
+  p.alpha_a = alpha_a;
+  p.alpha_b = alpha_b;
+  p.alpha = alpha;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.ksteps_total = (int)(K_eff / 64);
+  p.natoms = (int)((K_eff / 16 + 3) / 4);
+  p.tiles_m = (int)((M + BM - 1) / BM);
+  p.tiles_n = 0;
+
+  // Widest tile that still gives every SM work; narrow tiles for skinny problems.
+  int bn = 256;
+  while (bn > 32 && (long long)p.tiles_m * ((N + bn - 1) / bn) < di.num_sms) bn >>= 1;
+  if (N % 32 && bn > 8) { /* partial tiles are clipped by the TMA box and the store guards */ }
+
+  CUtensorMap ma, mb;
+  rc = make_operand_map(&ma, A, M, K_eff / 2, BM);
+  if (rc != ARCQ_OK) return rc;
+  rc = make_operand_map(&mb, B, N, K_eff / 2, bn);
+  if (rc != ARCQ_OK) return rc;
+
+  switch (bn) {
+    case 256: return launch_bn<256>(ma, mb, p, di.num_sms, stream);
+    case 128: return launch_bn<128>(ma, mb, p, di.num_sms, stream);
+    case 64: return launch_bn<64>(ma, mb, p, di.num_sms, stream);
+    default: return launch_bn<32>(ma, mb, p, di.num_sms, stream);
+  }
+}
+
+int gemm_poll_error() {
+  ARCQ_CUDA_TRY(cudaDeviceSynchronize());
+  int v = 0;
+  ARCQ_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)));
+  if (v != 0) {
+    int zero = 0;
+    ARCQ_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int)));
+  }
+  return v;
+}
+
+}  // namespace arcq

@@ -1,0 +1,37 @@
+// Internal declarations shared by the translation units of libarcq.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "arcq.h"
+
+namespace arcq {
+
+// Records a failing CUDA call for arcq_last_cuda_error() and returns ARCQ_ERR_CUDA.
+int cuda_fail(cudaError_t e);
+
+#define ARCQ_CUDA_TRY(expr)                                  \
+  do {                                                       \
+    cudaError_t _e = (expr);                                 \
+    if (_e != cudaSuccess) return ::arcq::cuda_fail(_e);     \
+  } while (0)
+
+struct DeviceInfo {
+  int device;
+  int num_sms;
+  int max_smem_optin;
+};
+// Cached properties of the current device (queried once per device).
+int get_device_info(DeviceInfo* out);
+
+// Launchers (defined in arcq_quant.cu / arcq_gemm.cu); arguments are validated by the callers
+// in arcq_api.cu.
+int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* idx, int64_t rows, int KQ,
+                    int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream);
+int launch_absmax(const void* x, int64_t n, float* out, int accumulate, cudaStream_t stream);
+int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                int64_t N, int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* C,
+                cudaStream_t stream);
+int gemm_poll_error();
+
+}  // namespace arcq

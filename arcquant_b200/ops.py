@@ -1,0 +1,131 @@
+"""Torch-facing operators over the C ABI, with the reference extension's
+signatures (kernels/src/bindings.cpp:99-254 of ARCQuant): they allocate their
+outputs, borrow their inputs and run on torch's current CUDA stream.
+
+These are thin: shape bookkeeping in Python, every byte of work in libarcq.so.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require(t: torch.Tensor, dtype, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name}: expected {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def sf_bytes(rows: int, k_eff: int) -> int:
+    return int(_lib.load().arcq_sf_bytes(rows, k_eff))
+
+
+def reference_mode(kq: int) -> int:
+    return int(_lib.load().arcq_reference_mode(kq))
+
+
+def _quantize(kind: str, x, gamma, eps, reorder_index, ke: int, mode):
+    lib = _lib.load()
+    _require(x, torch.bfloat16, "input")
+    if x.dim() != 2:
+        raise RuntimeError("input must be 2-D [rows, KQ]")
+    rows, kq = x.shape
+    if mode is None:
+        mode = reference_mode(kq)
+    idx_ptr = None
+    if reorder_index is not None:
+        _require(reorder_index, torch.int16, "reorder_index")
+        if reorder_index.numel() != kq:
+            raise RuntimeError("reorder_index must have KQ entries")
+        idx_ptr = reorder_index.data_ptr()
+    k_eff = kq + ke
+    q = torch.empty((rows, k_eff // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((sf_bytes(rows, k_eff),), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        if kind == "x":
+            rc = lib.arcq_reorder_quantize_x(x.data_ptr(), idx_ptr, rows, kq, ke, mode, q.data_ptr(),
+                                             sf.data_ptr(), _stream())
+        elif kind == "w":
+            rc = lib.arcq_reorder_quantize_w(x.data_ptr(), idx_ptr, rows, kq, ke, mode, q.data_ptr(),
+                                             sf.data_ptr(), _stream())
+        else:
+            _require(gamma, torch.bfloat16, "weight")
+            rc = lib.arcq_rmsnorm_quantize_x(x.data_ptr(), gamma.data_ptr(), float(eps), idx_ptr, rows, kq, ke,
+                                             q.data_ptr(), sf.data_ptr(), _stream())
+    _lib.check(rc, f"{kind}-quantize KQ={kq} KE={ke}")
+    return q, sf
+
+
+def reorder_quantize_x(x, reorder_index, ke: int, mode=None):
+    """(QX u8 [M,(KQ+KE)/2], SFX u8 [sf_bytes]) = ARC-NVFP4 of bf16 x [M,KQ]."""
+    return _quantize("x", x, None, 0.0, reorder_index, ke, mode)
+
+
+def reorder_quantize_w(w, reorder_index, ke: int, mode=None):
+    """Offline weight packer: residual slots duplicate the critical columns."""
+    return _quantize("w", w, None, 0.0, reorder_index, ke, mode)
+
+
+def rmsnorm_quantize_x(x, weight, eps: float, reorder_index, ke: int):
+    """RMSNorm(x)*weight fused in front of reorder_quantize_x."""
+    return _quantize("rms", x, weight, eps, reorder_index, ke, _lib.MODE_16)
+
+
+def matmul(a, b, sfa, sfb, scale) -> torch.Tensor:
+    """bf16 [M,N] = scale * (A.SFA)(B.SFB)^T.  ``scale`` may be a Python float or
+    a 0-dim tensor; a CUDA 0-dim fp32 tensor is consumed on the device (no
+    host synchronisation)."""
+    lib = _lib.load()
+    for t, n in ((a, "A"), (b, "B"), (sfa, "SFA"), (sfb, "SFB")):
+        _require(t, torch.uint8, n)
+    m, kb = a.shape
+    n = b.shape[0]
+    if b.shape[1] != kb:
+        raise RuntimeError("A and B disagree on K")
+    c = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    with torch.cuda.device(a.device):
+        if isinstance(scale, torch.Tensor) and scale.is_cuda and scale.dtype == torch.float32:
+            rc = lib.arcq_matmul_nvfp4_dev_alpha(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n,
+                                                 kb * 2, scale.data_ptr(), None, c.data_ptr(), _stream())
+        else:
+            rc = lib.arcq_matmul_nvfp4(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, kb * 2,
+                                       float(scale), c.data_ptr(), _stream())
+    _lib.check(rc, f"matmul M={m} N={n} K={kb * 2}")
+    return c
+
+
+def matmul_dev_alpha(a, b, sfa, sfb, alpha_a: torch.Tensor, alpha_b: torch.Tensor | None = None) -> torch.Tensor:
+    """matmul with alpha = alpha_a * alpha_b, both fp32 scalars in device memory."""
+    lib = _lib.load()
+    m, kb = a.shape
+    n = b.shape[0]
+    c = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    with torch.cuda.device(a.device):
+        rc = lib.arcq_matmul_nvfp4_dev_alpha(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, kb * 2,
+                                             alpha_a.data_ptr(), None if alpha_b is None else alpha_b.data_ptr(),
+                                             c.data_ptr(), _stream())
+    _lib.check(rc, f"matmul M={m} N={n} K={kb * 2}")
+    return c
+
+
+def absmax(x: torch.Tensor) -> torch.Tensor:
+    """0-dim fp32 CUDA tensor max|x| of a bf16 tensor, one pass."""
+    lib = _lib.load()
+    _require(x, torch.bfloat16, "input")
+    out = torch.empty((), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.arcq_absmax_bf16(x.data_ptr(), x.numel(), out.data_ptr(), 0, _stream())
+    _lib.check(rc, "absmax")
+    return out
+
+
+def gemm_poll_error() -> int:
+    return int(_lib.load().arcq_gemm_poll_error())

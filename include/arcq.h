@@ -1,0 +1,129 @@
+/*
+ * arcq.h - C ABI of libarcq.so, the sm_100a (B200) implementation of the
+ * ARC-NVFP4 quantized-linear hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * handle (a cudaStream_t passed as void*; NULL = legacy default stream) and
+ * returns an int status (ARCQ_OK = 0).  Nothing here allocates device memory
+ * unless its comment says so; outputs are caller-allocated.  The library has
+ * no CPU fallback: without a CUDA device every compute call returns
+ * ARCQ_ERR_CUDA.
+ *
+ * Each function names the reference interface it replaces (paths relative to
+ * the ARCQuant source tree).
+ *
+ * Data formats (identical to the reference's):
+ *   - activations / weights in: bf16, row-major [rows, KQ]
+ *   - reorder_index: int16 [KQ], ascending-by-importance channel order; the
+ *     LAST KE entries are the critical channels whose quantization residual is
+ *     appended (ARC)
+ *   - packed codes out: uint8 [rows, (KQ+KE)/2]; element 2i in the low nibble;
+ *     bytes [0, 8*G0) hold the G0=(KQ-KE)/16 plain groups, then per critical
+ *     group 16 bytes [8 B main codes][8 B residual codes]
+ *   - scale factors out: one ue4m3 byte per 16 elements in the 512-byte
+ *     128-row x 4-column atom layout of block-scaled tensor-core GEMMs:
+ *       offset(r,c) = ((r/128)*ceil(C/4) + c/4)*512 + (r%32)*16 + ((r/32)%4)*4 + c%4,
+ *     C = (KQ+KE)/16.  Padding bytes are left unwritten.
+ */
+#ifndef ARCQ_H_
+#define ARCQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ARCQ_OK 0
+#define ARCQ_ERR_BAD_SHAPE 1      /* sizes that the data layout cannot express */
+#define ARCQ_ERR_UNSUPPORTED_K 2  /* KQ outside what the kernels cover */
+#define ARCQ_ERR_NULL_POINTER 3
+#define ARCQ_ERR_CUDA 4           /* a CUDA runtime/driver call failed; see arcq_last_cuda_error() */
+#define ARCQ_ERR_ALIGNMENT 5      /* a pointer is not 16-byte aligned */
+#define ARCQ_ERR_TIMEOUT 6        /* a bounded device-side wait expired (reported by arcq_gemm_poll_error) */
+
+/* Channel-layout family of the critical groups.
+ * 16: one group per slot  - [main][residual] per critical group
+ *     (kernels/src/reorder.cu:68-203).
+ * 32: groups in pairs     - [main1][main2][res1][res2], residual taken against
+ *     the un-rounded fp32 block scale (kernels/src/reorder.cu:381-555,
+ *     kernels/src/down.cu:71-236). */
+#define ARCQ_MODE_16 16
+#define ARCQ_MODE_32 32
+
+/* Human-readable text for a status code. */
+const char* arcq_status_string(int status);
+
+/* cudaError_t value of the last failing CUDA call made by this library on the
+ * calling thread (0 if none). */
+int arcq_last_cuda_error(void);
+
+/* Library version: major*10000 + minor*100 + patch. */
+int arcq_version(void);
+
+/* Bytes to allocate for the scale-factor buffer of `rows` rows and K_eff =
+ * KQ+KE columns.  Never smaller than the reference's own size
+ * (rows/128+1)*128*K_eff/16 (kernels/src/bindings.cpp:83-95) and never smaller
+ * than what the atom layout spans. */
+size_t arcq_sf_bytes(int64_t rows, int64_t k_eff);
+
+/* Which family the reference dispatches a given KQ to
+ * (kernels/src/bindings.cpp:141-160): ARCQ_MODE_32 for 3584, 18944, 27648,
+ * 28672, else ARCQ_MODE_16. */
+int arcq_reference_mode(int kq);
+
+/* Replaces agemm.reorder_quantize_x (kernels/src/bindings.cpp:122-163 ->
+ * run_reorder_x_bf16_nvfp4 kernels/src/reorder.cu:332-351, and the 32-wide /
+ * pre-gathered variants reorder.cu:698-717, down.cu:363-381).
+ * x: bf16 [M,KQ]; reorder_index: int16 [KQ] on the device, or NULL for the
+ * identity order (an input gathered beforehand).  KQ % 16 == 0, KE % 16 == 0
+ * (mode 32: % 32), 0 <= KE <= KQ, KQ <= 32752. */
+int arcq_reorder_quantize_x(const void* x, const int16_t* reorder_index, int64_t M, int KQ, int KE,
+                            int mode, uint8_t* qx, uint8_t* sfx, void* stream);
+
+/* Replaces agemm.rmsnorm_quantize_x (kernels/src/bindings.cpp:216-254 ->
+ * kernels/src/rmsnorm.cu:68-281): RMSNorm with gain `gamma` (bf16 [KQ]) fused
+ * in front of the mode-16 quantizer.  The sum of squares is accumulated in the
+ * reference's order; the reciprocal root is the correctly rounded fp32
+ * 1/sqrt(ss/KQ + eps).  KQ/16 must be a multiple of 32 and at most 512. */
+int arcq_rmsnorm_quantize_x(const void* x, const void* gamma, float eps, const int16_t* reorder_index,
+                            int64_t M, int KQ, int KE, uint8_t* qx, uint8_t* sfx, void* stream);
+
+/* Replaces agemm.reorder_quantize_w (kernels/src/bindings.cpp:170-210 ->
+ * kernels/src/reorder.cu:353-372, 719-738, down.cu:383-401): the offline
+ * weight packer.  The residual slot of each critical group is a copy of its
+ * main codes and scale, so the GEMM needs no knowledge of ARC. */
+int arcq_reorder_quantize_w(const void* w, const int16_t* reorder_index, int64_t N, int KQ, int KE,
+                            int mode, uint8_t* qw, uint8_t* sfw, void* stream);
+
+/* Replaces agemm.matmul (kernels/src/bindings.cpp:99-120 ->
+ * matmul_host_nvfp4_bf16 kernels/src/nvfp4.cu:35-132):
+ *   C[m,n] = bf16( alpha * sum_k val(A[m,k])*SFA[m,k/16] * val(B[n,k])*SFB[n,k/16] ),
+ * fp32 accumulation.  A: [M,K_eff/2], B: [N,K_eff/2] packed e2m1; C: bf16 [M,N]
+ * row-major.  K_eff % 64 == 0, N % 8 == 0, all pointers 16-byte aligned. */
+int arcq_matmul_nvfp4(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                      int64_t M, int64_t N, int64_t K_eff, float alpha, void* C, void* stream);
+
+/* Same as arcq_matmul_nvfp4 with alpha = (*alpha_a) * (*alpha_b) read on the
+ * device (fp32 scalars in device memory; alpha_b may be NULL = 1), so the
+ * per-tensor global scales never travel to the host.  Replaces the
+ * `scale * self.scale` host round trip of model/qLinearLayer.py:69. */
+int arcq_matmul_nvfp4_dev_alpha(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                                int64_t M, int64_t N, int64_t K_eff, const float* alpha_a,
+                                const float* alpha_b, void* C, void* stream);
+
+/* The GEMM kernel bounds every wait on a barrier; if one ever expires the
+ * kernel records it and returns.  This reads (and clears) that record for the
+ * current device: ARCQ_OK or ARCQ_ERR_TIMEOUT.  Synchronises the device. */
+int arcq_gemm_poll_error(void);
+
+/* One pass max|x| over n bf16 elements into *out (fp32, device memory; the
+ * caller zero-fills it first or passes accumulate=0 to have it cleared by the
+ * call).  Replaces the torch.max(x.abs()) pass of model/qLlamaLayer.py:74. */
+int arcq_absmax_bf16(const void* x, int64_t n, float* out, int accumulate, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ARCQ_H_ */

@@ -1,0 +1,78 @@
+"""The drop-in boundary without a GPU: the C ABI exports what include/arcq.h declares, refuses to
+compute without a CUDA device, and the `agemm` module offers the reference's operator names."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "arcq.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(arcq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from arcquant_b200 import _lib
+
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    names = _declared()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), n
+    assert sorted(_lib.SIGNATURES) == names          # the ctypes table mirrors the header
+
+
+def test_host_side_helpers():
+    from arcquant_b200 import _lib
+
+    L = _lib.load()
+    assert L.arcq_sf_bytes(512, 4224) == 168960
+    assert L.arcq_sf_bytes(128, 4224) == 2 * 128 * 264
+    assert L.arcq_sf_bytes(1, 4160) >= 65 * 512
+    assert [L.arcq_reference_mode(k) for k in (4096, 3584, 14336, 28672, 18944, 27648)] == [16, 32, 16, 32, 32, 32]
+    assert L.arcq_status_string(0) == b"ok"
+
+
+def test_argument_validation_precedes_any_cuda_call():
+    from arcquant_b200 import _lib
+
+    L = _lib.load()
+    p = 1 << 12
+    assert L.arcq_reorder_quantize_x(p, None, 4, 40, 0, 16, p, p, None) == _lib.ERR_BAD_SHAPE
+    assert L.arcq_reorder_quantize_x(p, None, 4, 64, 8, 16, p, p, None) == _lib.ERR_BAD_SHAPE
+    assert L.arcq_reorder_quantize_x(p, None, 4, 64, 16, 32, p, p, None) == _lib.ERR_BAD_SHAPE
+    assert L.arcq_reorder_quantize_x(None, None, 4, 64, 0, 16, p, p, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_reorder_quantize_x(p + 2, None, 4, 64, 0, 16, p, p, None) == _lib.ERR_ALIGNMENT
+    assert L.arcq_rmsnorm_quantize_x(p, p, 1e-5, None, 4, 14336, 0, p, p, None) == _lib.ERR_UNSUPPORTED_K
+    assert L.arcq_matmul_nvfp4(p, p, p, p, 4, 64, 96, 1.0, p, None) == _lib.ERR_BAD_SHAPE      # K % 64
+    assert L.arcq_matmul_nvfp4(p, p, p, p, 4, 60, 128, 1.0, p, None) == _lib.ERR_BAD_SHAPE     # N % 8
+    assert L.arcq_matmul_nvfp4(p, p, p, p, 0, 64, 128, 1.0, p, None) == _lib.OK                # empty M
+    assert L.arcq_reorder_quantize_x(p, None, 0, 64, 0, 16, p, p, None) == _lib.OK             # empty input
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-device behaviour")
+def test_no_cpu_fallback():
+    from arcquant_b200 import _lib, ops
+
+    L = _lib.load()
+    p = 1 << 12
+    assert L.arcq_reorder_quantize_x(p, None, 4, 64, 0, 16, p, p, None) == _lib.ERR_CUDA
+    with pytest.raises(RuntimeError):
+        ops.reorder_quantize_x(torch.zeros(4, 64, dtype=torch.bfloat16), None, 0)
+
+
+def test_agemm_module_surface():
+    import importlib
+    import sys
+
+    sys.path.insert(0, os.path.join(ROOT, "arcquant_b200"))
+    agemm = importlib.import_module("agemm")
+    for name in ("matmul", "reorder_quantize_x", "reorder_quantize_w", "rmsnorm_quantize_x"):
+        assert callable(getattr(agemm, name))
+    with pytest.raises(RuntimeError):
+        agemm.reorder_quantize_x(torch.zeros(4, 64, dtype=torch.bfloat16), torch.arange(64, dtype=torch.int16), 0)
