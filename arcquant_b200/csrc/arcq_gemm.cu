@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "arcq_internal.h"
@@ -67,6 +68,7 @@ struct GemmParams {
   int ksteps_total;   // K_eff / 64
   int natoms;         // ceil((K_eff/16)/4): scale atoms per 128-row tile
   int tiles_m, tiles_n;
+  int sfb_tiles;      // ceil(N/128): 128-row scale tiles of B that exist
 };
 
 // ----------------------------------------------------------------------------- PTX wrappers
@@ -236,15 +238,21 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const int nk = min(KSTEPS, p.ksteps_total - ks * KSTEPS);
           const uint32_t sf_bytes = (uint32_t)nk * ATOM;
           const uint32_t st = base + s * C::STAGE_BYTES;
-          mbar_expect_tx(full_bar(s), C::A_BYTES + C::B_BYTES + sf_bytes * (1 + C::NB));
+          // scale tiles of B that exist (a 256-wide tile may hang over the last 128-row scale tile)
+          int nb_valid = 0;
+#pragma unroll
+          for (int a = 0; a < C::NB; ++a) nb_valid += (rtb + a) < p.sfb_tiles ? 1 : 0;
+          mbar_expect_tx(full_bar(s), C::A_BYTES + C::B_BYTES + sf_bytes * (1 + nb_valid));
           tma_load_2d(st, &map_a, full_bar(s), ks * BK_BYTES, tm * BM);
           tma_load_2d(st + C::A_BYTES, &map_b, full_bar(s), ks * BK_BYTES, tn * BN);
           const uint8_t* sa = p.sfa + ((size_t)tm * p.natoms + (size_t)ks * KSTEPS) * ATOM;
           bulk_load(st + C::A_BYTES + C::B_BYTES, sa, sf_bytes, full_bar(s));
 #pragma unroll
           for (int a = 0; a < C::NB; ++a) {
-            const uint8_t* sb = p.sfb + ((size_t)(rtb + a) * p.natoms + (size_t)ks * KSTEPS) * ATOM;
-            bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + a * (KSTEPS * ATOM), sb, sf_bytes, full_bar(s));
+            if ((rtb + a) < p.sfb_tiles) {
+              const uint8_t* sb = p.sfb + ((size_t)(rtb + a) * p.natoms + (size_t)ks * KSTEPS) * ATOM;
+              bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + a * (KSTEPS * ATOM), sb, sf_bytes, full_bar(s));
+            }
           }
         }
       }
@@ -335,6 +343,7 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
+    __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS)
                  : "memory");
@@ -413,11 +422,17 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   p.natoms = (int)((K_eff / 16 + 3) / 4);
   p.tiles_m = (int)((M + BM - 1) / BM);
   p.tiles_n = 0;
+  p.sfb_tiles = (int)((N + 127) / 128);
 
-  // Widest tile that still gives every SM work; narrow tiles for skinny problems.
+  // Widest tile that still gives every SM work; narrow tiles for skinny problems.  Partial tiles
+  // are clipped by the TMA box (zero fill) and by the store guards.  ARCQ_GEMM_BN=32|64|128|256
+  // overrides the choice (tuning / testing knob).
   int bn = 256;
   while (bn > 32 && (long long)p.tiles_m * ((N + bn - 1) / bn) < di.num_sms) bn >>= 1;
-  if (N % 32 && bn > 8) { /* partial tiles are clipped by the TMA box and the store guards */ }
+  if (const char* e = getenv("ARCQ_GEMM_BN")) {
+    int v = atoi(e);
+    if (v == 32 || v == 64 || v == 128 || v == 256) bn = v;
+  }
 
   CUtensorMap ma, mb;
   rc = make_operand_map(&ma, A, M, K_eff / 2, BM);

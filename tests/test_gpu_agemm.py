@@ -1,0 +1,87 @@
+"""The reference's call pattern through the `agemm` module (model/qLinearLayer.py:25-28,64-81 and
+model/qLlamaLayer.py:73-77 of ARCQuant): config 1 of the benchmark contract, end to end."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from arcquant_b200 import synth
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _agemm():
+    sys.path.insert(0, os.path.join(ROOT, "arcquant_b200"))
+    import agemm
+    return agemm
+
+
+def test_config1_single_linear_matches_oracle_and_fp32():
+    from oracle import oracle as O
+
+    agemm = _agemm()
+    x, w, idx, ke = synth.config1()
+    dev = "cuda:0"
+    xd, wd, idxd = x.to(dev), w.to(dev), idx.to(dev)
+    # the callers' pre-scaling (bf16 tensor / 0-dim fp32 CUDA tensor)
+    sx = torch.max(xd.abs()).float() / (448.0 * 6.0)
+    sw = torch.max(wd.abs()).float() / (448.0 * 6.0)
+    xs, ws = xd / sx, wd / sw
+    assert xs.dtype == torch.bfloat16
+    A, SFA = agemm.reorder_quantize_x(xs, idxd, ke)
+    B, SFB = agemm.reorder_quantize_w(ws, idxd, ke)
+    Y = agemm.matmul(A, B, SFA, SFB, float(sx * sw))
+    torch.cuda.synchronize()
+    assert Y.shape == (512, 4096) and Y.dtype == torch.bfloat16
+    assert A.shape == (512, 2112) and SFA.numel() == 168960 and SFA.dtype == torch.uint8
+    # bit-exact codes/scales against the oracle fed the very same pre-scaled bf16 inputs
+    qa, sfa = O.quantize_x(xs.cpu(), idx.numpy(), ke)
+    qb, sfb = O.quantize_w(ws.cpu(), idx.numpy(), ke)
+    assert np.array_equal(A.cpu().numpy(), qa) and np.array_equal(B.cpu().numpy(), qb)
+    va, vb = O.sf_valid_offsets(512, 4224), O.sf_valid_offsets(4096, 4224)
+    assert np.array_equal(SFA.cpu().numpy()[va], sfa[va]) and np.array_equal(SFB.cpu().numpy()[vb], sfb[vb])
+    ref = O.gemm_fast(qa, sfa, qb, sfb, float(sx * sw))
+    y = Y.float().cpu().numpy()
+    assert np.linalg.norm(y - ref) / np.linalg.norm(ref) <= 1e-3
+    # and the quantization error itself is where ARC puts it (about 0.1 on this input)
+    full = (x.float() @ w.float().T).numpy()
+    err = np.linalg.norm(y - full) / np.linalg.norm(full)
+    assert 0.02 < err < 0.13
+
+
+def test_fused_rmsnorm_operator():
+    from oracle import oracle as O
+
+    agemm = _agemm()
+    kq = 4096
+    out = synth.outlier_channels(kq, 41, 1)
+    x = synth.activations(48, kq, 2, out)
+    gamma = synth.rms_gain(kq, 3)
+    idx = synth.reorder_index_from_stats(x.abs().amax(0))
+    A, SFA = agemm.rmsnorm_quantize_x(x.cuda(), gamma.cuda(), 1e-5, idx.cuda(), 128)
+    qa, sfa = O.quantize_x(x, idx.numpy(), 128, gamma=gamma, eps=1e-5)
+    assert np.array_equal(A.cpu().numpy(), qa)
+    v = O.sf_valid_offsets(48, kq + 128)
+    assert np.array_equal(SFA.cpu().numpy()[v], sfa[v])
+
+
+def test_error_behaviour_mirrors_the_reference():
+    agemm = _agemm()
+    idx = torch.arange(4096, dtype=torch.int16, device="cuda")
+    with pytest.raises(RuntimeError):          # wrong dtype: data_ptr<BFloat16>() throws
+        agemm.reorder_quantize_x(torch.zeros(4, 4096, dtype=torch.float16, device="cuda"), idx, 128)
+    with pytest.raises(RuntimeError):          # a width the kernels do not serve
+        agemm.reorder_quantize_x(torch.zeros(4, 40, dtype=torch.bfloat16, device="cuda"),
+                                 torch.arange(40, dtype=torch.int16, device="cuda"), 0)
+    with pytest.raises(RuntimeError):
+        agemm.rmsnorm_quantize_x(torch.zeros(4, 14336, dtype=torch.bfloat16, device="cuda"),
+                                 torch.ones(14336, dtype=torch.bfloat16, device="cuda"), 1e-5,
+                                 torch.arange(14336, dtype=torch.int16, device="cuda"), 128)
+    # inputs are borrowed, never mutated
+    x = torch.randn(8, 4096, device="cuda").to(torch.bfloat16)
+    keep = x.clone()
+    agemm.reorder_quantize_x(x, idx, 128)
+    assert torch.equal(x, keep)

@@ -1,0 +1,159 @@
+"""Parity of the tcgen05 block-scaled NVFP4 GEMM with the oracle's dequantised fp32 matmul:
+relative Frobenius error <= 1e-3 (bf16 output rounding alone is ~2^-9 per element)."""
+import numpy as np
+import pytest
+import torch
+
+from arcquant_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3
+
+
+def _ops():
+    from arcquant_b200 import ops
+    return ops
+
+
+def _oracle():
+    from oracle import oracle as O
+    return O
+
+
+def _operands(m, n, kq, ke, seed):
+    """Packed operands made by the ORACLE from seeded N(0,1) activations / N(0,0.02) weights."""
+    O = _oracle()
+    out = synth.outlier_channels(kq, max(1, kq // 100), seed)
+    x = synth.activations(m, kq, seed + 1, out)
+    w = synth.weights(n, kq, seed + 2)
+    sx, sw = synth.global_scale(x), synth.global_scale(w)
+    idx = synth.reorder_index_from_stats(synth.activations(128, kq, seed + 3, out).abs().amax(0)).numpy()
+    a, sfa = O.quantize_x((x / sx).contiguous(), idx, ke)
+    b, sfb = O.quantize_w((w / sw).contiguous(), idx, ke)
+    return a, sfa, b, sfb, float(sx * sw)
+
+
+def _run(a, sfa, b, sfb, alpha):
+    ops = _ops()
+    dev = "cuda:0"
+    t = [torch.from_numpy(v).to(dev) for v in (a, b, sfa, sfb)]
+    c = ops.matmul(t[0], t[1], t[2], t[3], alpha)
+    torch.cuda.synchronize()
+    assert ops.gemm_poll_error() == 0
+    return c.float().cpu().numpy()
+
+
+def _relerr(c, ref):
+    return float(np.linalg.norm(c - ref) / max(np.linalg.norm(ref), 1e-30))
+
+
+def test_one_hot_operands_land_where_they_should():
+    """A single non-zero code in A and in B with unit scales: exactly one output element is set.
+    Catches nibble order, swizzle, K-step and scale-atom placement errors by position."""
+    O = _oracle()
+    m, n, k = 128, 256, 512
+    ncols = k // 16
+    for (am, ak, bn, bk) in [(0, 0, 0, 0), (5, 1, 9, 1), (127, 511, 255, 511), (64, 70, 130, 70), (33, 200, 7, 200),
+                             (99, 321, 200, 321)]:
+        a = np.zeros((m, k // 2), np.uint8); b = np.zeros((n, k // 2), np.uint8)
+        sfa = np.zeros(O.sf_alloc_bytes(m, k), np.uint8); sfb = np.zeros(O.sf_alloc_bytes(n, k), np.uint8)
+        a[am, ak // 2] = 0x2 << (4 * (ak & 1))          # +1.0
+        b[bn, bk // 2] = 0x4 << (4 * (bk & 1))          # +2.0
+        sfa[O.sf_offset(am, ak // 16, ncols)] = 0x38    # 1.0
+        sfb[O.sf_offset(bn, bk // 16, ncols)] = 0x40    # 2.0
+        c = _run(a, sfa, b, sfb, 1.0)
+        want = np.zeros((m, n), np.float32); want[am, bn] = 4.0
+        assert np.array_equal(c, want), (am, ak, bn, bk, np.argwhere(c != 0)[:4].tolist())
+
+
+def test_exact_small_integers():
+    """Codes in {0, +-1, +-2} with scales in {1, 2} and K=64: every partial sum is a small integer,
+    so the bf16 result is exact."""
+    O = _oracle()
+    rng = np.random.default_rng(0)
+    m, n, k = 128, 128, 64
+    lut = np.array([0x0, 0x2, 0xA, 0x4, 0xC], np.uint8)
+    ca = lut[rng.integers(0, 5, (m, k))]; cb = lut[rng.integers(0, 5, (n, k))]
+    a = (ca[:, 0::2] | (ca[:, 1::2] << 4)).astype(np.uint8); b = (cb[:, 0::2] | (cb[:, 1::2] << 4)).astype(np.uint8)
+    sfa = np.zeros(O.sf_alloc_bytes(m, k), np.uint8); sfb = np.zeros(O.sf_alloc_bytes(n, k), np.uint8)
+    for r in range(128):
+        for c in range(4):
+            sfa[O.sf_offset(r, c, 4)] = 0x38 if (r + c) % 2 else 0x40
+            sfb[O.sf_offset(r, c, 4)] = 0x40 if (r * c) % 3 else 0x38
+    ref = O.gemm(a, sfa, b, sfb, 1.0)
+    c = _run(a, sfa, b, sfb, 1.0)
+    assert np.array_equal(c, ref)
+
+
+@pytest.mark.parametrize("m,n,kq,ke", [
+    (1, 128, 64, 0), (16, 256, 256, 64), (128, 256, 1024, 0), (130, 264, 448, 64), (257, 512, 4096, 128),
+    (128, 6144, 4096, 128), (64, 4096, 14336, 128), (300, 1000, 1984, 64), (16, 28672, 4096, 128)])
+def test_matches_dequantised_fp32_matmul(m, n, kq, ke):
+    O = _oracle()
+    a, sfa, b, sfb, alpha = _operands(m, n, kq, ke, seed=m + n)
+    ref = O.gemm_fast(a, sfa, b, sfb, alpha)
+    c = _run(a, sfa, b, sfb, alpha)
+    assert _relerr(c, ref) <= TOL
+
+
+def test_tail_k_stage_and_garbage_in_scale_padding():
+    """K_eff = 4224 is 16.5 stages of 256: the last stage is half.  Scale bytes outside the valid
+    region are poisoned with NaN codes and must never reach an output."""
+    O = _oracle()
+    m, n, kq, ke = 100, 136, 4096, 128
+    a, sfa, b, sfb, alpha = _operands(m, n, kq, ke, seed=5)
+    ref = O.gemm_fast(a, sfa, b, sfb, alpha)
+    for arr, rows in ((sfa, m), (sfb, n)):
+        keep = np.zeros(arr.size, bool); keep[O.sf_valid_offsets(rows, kq + ke)] = True
+        arr[~keep] = 0x7F
+    c = _run(a, sfa, b, sfb, alpha)
+    assert np.isfinite(c).all()
+    assert _relerr(c, ref) <= TOL
+
+
+def test_device_resident_alpha():
+    ops, O = _ops(), _oracle()
+    a, sfa, b, sfb, alpha = _operands(64, 256, 512, 64, seed=11)
+    t = [torch.from_numpy(v).cuda() for v in (a, b, sfa, sfb)]
+    sa = torch.tensor(alpha ** 0.5, dtype=torch.float32, device="cuda")
+    c1 = ops.matmul_dev_alpha(t[0], t[1], t[2], t[3], sa, sa).float().cpu().numpy()
+    ref = O.gemm_fast(a, sfa, b, sfb, float(np.float32(alpha ** 0.5)) ** 2)
+    assert _relerr(c1, ref) <= TOL
+
+
+@pytest.mark.parametrize("m,n,kq", [(4096, 4096, 4096), (16384, 6144, 4096), (4096, 4096, 14336)])
+def test_large_shapes_by_row_independence_and_samples(m, n, kq):
+    """Full BASELINE shapes: the scalar oracle checks a sample of output rows; the rest is covered
+    by row independence (the GEMM of a row subset equals the subset of the GEMM)."""
+    ops, O = _ops(), _oracle()
+    ke = 128
+    dev = "cuda:0"
+    out = synth.outlier_channels(kq, kq // 100, 1)
+    x = synth.activations(m, kq, 2, out, device=dev)
+    w = synth.weights(n, kq, 3, device=dev)
+    idx = synth.reorder_index_from_stats(x[:2048].abs().amax(0)).to(dev)
+    sx, sw = ops.absmax(x) / 2688.0, ops.absmax(w) / 2688.0
+    a, sfa = ops.reorder_quantize_x((x / sx).to(torch.bfloat16), idx, ke)
+    b, sfb = ops.reorder_quantize_w((w / sw).to(torch.bfloat16), idx, ke)
+    alpha = float(sx * sw)
+    c = ops.matmul(a, b, sfa, sfb, alpha)
+    assert ops.gemm_poll_error() == 0
+    rows = torch.cat([torch.arange(0, 4), torch.arange(m - 4, m), torch.randint(0, m, (24,), generator=torch.Generator().manual_seed(1))])
+    asub = a[rows.to(dev)].contiguous()
+    # scales of the sampled rows, re-laid out for a 32-row operand
+    ncols = (kq + ke) // 16
+    sfh = sfa.cpu().numpy()
+    sfsub = np.zeros(O.sf_alloc_bytes(len(rows), kq + ke), np.uint8)
+    cols = np.arange(ncols)
+    for j, r in enumerate(rows.tolist()):
+        src = ((r // 128) * ((ncols + 3) // 4) + cols // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + cols % 4
+        dst = (cols // 4) * 512 + (j % 32) * 16 + ((j // 32) % 4) * 4 + cols % 4
+        sfsub[dst] = sfh[src]
+    csub = ops.matmul(asub, b, torch.from_numpy(sfsub).to(dev), sfb, alpha)
+    assert torch.equal(csub, c[rows.to(dev)])
+    ref = O.gemm_fast(asub.cpu().numpy(), sfsub, b.cpu().numpy(), sfb.cpu().numpy(), alpha)
+    assert _relerr(csub.float().cpu().numpy(), ref) <= TOL
+    # and against the unquantised product the ARC error stays in the expected band
+    y = (x[rows.to(dev)].float() @ w.float().T).cpu().numpy()
+    assert _relerr(csub.float().cpu().numpy(), y) < 0.2

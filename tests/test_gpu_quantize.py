@@ -1,0 +1,158 @@
+"""Parity of the CUDA quantizer with the CPU oracle, through the C ABI (ctypes): packed e2m1 codes
+and ue4m3 scale bytes must be bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from arcquant_b200 import synth
+from tests.helpers import adversarial_rows, scaled_activations, valid_sf
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from arcquant_b200 import ops
+    return ops
+
+
+def _oracle():
+    from oracle import oracle as O
+    return O
+
+
+def _check(kind, x, idx, ke, mode, gamma=None, eps=0.0):
+    ops, O = _ops(), _oracle()
+    dev = torch.device("cuda:0")
+    xd = x.to(dev)
+    idxd = None if idx is None else idx.to(dev)
+    if kind == "x":
+        q, sf = ops.reorder_quantize_x(xd, idxd, ke, mode=mode)
+        qo, sfo = O.quantize_x(x, None if idx is None else idx.numpy(), ke, mode=mode)
+    elif kind == "w":
+        q, sf = ops.reorder_quantize_w(xd, idxd, ke, mode=mode)
+        qo, sfo = O.quantize_w(x, None if idx is None else idx.numpy(), ke, mode=mode)
+    else:
+        q, sf = ops.rmsnorm_quantize_x(xd, gamma.to(dev), eps, idxd, ke)
+        qo, sfo = O.quantize_x(x, None if idx is None else idx.numpy(), ke, mode=16, gamma=gamma, eps=eps)
+    torch.cuda.synchronize()
+    rows, kq = x.shape
+    qg = q.cpu().numpy()
+    assert qg.shape == qo.shape
+    bad = np.argwhere(qg != qo)
+    assert bad.size == 0, f"{len(bad)} code bytes differ, first at {bad[:5].tolist()}: gpu {qg[tuple(bad[0])]:#x} oracle {qo[tuple(bad[0])]:#x}"
+    sg, so = valid_sf(sf, rows, kq + ke), valid_sf(sfo, rows, kq + ke)
+    bad = np.argwhere(sg != so)
+    assert bad.size == 0, f"{len(bad)} scale bytes differ, first {bad[:5].tolist()}"
+    assert sf.numel() >= O.sf_bytes_reference(rows, kq + ke)
+
+
+@pytest.mark.parametrize("tokens", [1, 16, 128, 1024])
+@pytest.mark.parametrize("ke", [0, 64, 128, 256])
+def test_reorder_quantize_x_hidden4096(tokens, ke):
+    xs, idx = scaled_activations(tokens, 4096, seed=100 + tokens + ke)
+    _check("x", xs, idx, ke, 16)
+
+
+@pytest.mark.parametrize("kq,ke,mode,tokens", [
+    (2048, 128, 16, 33), (3072, 64, 16, 7), (5120, 128, 16, 5), (8192, 256, 16, 9), (11008, 128, 16, 4),
+    (13824, 64, 16, 3), (14336, 128, 16, 130), (3584, 64, 32, 19), (18944, 128, 32, 5), (512, 512, 16, 6),
+    (1792, 16, 16, 11), (64, 0, 16, 257)])
+def test_reorder_quantize_x_other_widths(kq, ke, mode, tokens):
+    xs, idx = scaled_activations(tokens, kq, seed=kq + ke)
+    _check("x", xs, idx, ke, mode)
+
+
+@pytest.mark.parametrize("kq", [27648, 28672])
+def test_pre_gathered_wide_rows_mode32(kq):
+    xs, _ = scaled_activations(3, kq, seed=kq)
+    _check("x", xs, None, 128, 32)          # identity order: the caller gathered beforehand
+    w = synth.weights(4, kq, seed=1)
+    _check("w", (w / synth.global_scale(w)).contiguous(), None, 128, 32)
+
+
+def test_rounding_boundaries_and_signed_zeros():
+    x = adversarial_rows(4096)
+    idx = torch.randperm(4096, generator=torch.Generator().manual_seed(3)).to(torch.int16)
+    _check("x", x, idx, 128, 16)
+    _check("x", x, None, 0, 16)
+    _check("x", adversarial_rows(3584), None, 64, 32)
+
+
+@pytest.mark.parametrize("kq", [2048, 3072, 3584, 4096, 5120, 8192])
+@pytest.mark.parametrize("tokens", [1, 130])
+def test_rmsnorm_quantize_x(kq, tokens):
+    out = synth.outlier_channels(kq, kq // 100, 5)
+    x = synth.activations(tokens, kq, 17 + kq, out)
+    gamma = synth.rms_gain(kq, 3)
+    idx = synth.reorder_index_from_stats(synth.activations(256, kq, 9, out).abs().amax(0))
+    _check("rms", x, idx, 128, 16, gamma=gamma, eps=1e-5)
+    if kq == 4096:
+        for ke in (0, 64, 256):
+            _check("rms", x, idx, ke, 16, gamma=gamma, eps=1e-5)
+
+
+def test_rmsnorm_rows_with_extreme_norms():
+    kq = 4096
+    x = adversarial_rows(kq)
+    gamma = synth.rms_gain(kq, 4)
+    _check("rms", x, None, 128, 16, gamma=gamma, eps=1e-6)
+
+
+@pytest.mark.parametrize("kq,ke,mode,n", [(4096, 128, 16, 300), (14336, 128, 16, 40), (3584, 64, 32, 64), (4096, 0, 16, 17)])
+def test_reorder_quantize_w(kq, ke, mode, n):
+    w = synth.weights(n, kq, seed=kq + n)
+    ws = (w / synth.global_scale(w)).contiguous()
+    idx = torch.randperm(kq, generator=torch.Generator().manual_seed(kq)).to(torch.int16)
+    _check("w", ws, idx, ke, mode)
+
+
+def test_full_size_is_row_independent_and_matches_oracle_on_samples():
+    """32768 tokens x 4096: too large for the scalar oracle as a whole, so (a) quantizing the halves
+    separately must give the same bytes as quantizing everything (rows are independent), (b) a
+    spread of rows is checked against the oracle, (c) a checksum over everything is stable across
+    two runs."""
+    ops, O = _ops(), _oracle()
+    tokens, kq, ke = 32768, 4096, 128
+    dev = torch.device("cuda:0")
+    out = synth.outlier_channels(kq, 41, 1)
+    x = synth.activations(tokens, kq, 2, out, device=dev)
+    idx = synth.reorder_index_from_stats(x[:4096].abs().amax(0)).to(dev)
+    q, sf = ops.reorder_quantize_x(x, idx, ke)
+    q2, sf2 = ops.reorder_quantize_x(x, idx, ke)
+    assert torch.equal(q, q2)
+    qa, sfa = ops.reorder_quantize_x(x[:16384].contiguous(), idx, ke)
+    qb, sfb = ops.reorder_quantize_x(x[16384:].contiguous(), idx, ke)
+    assert torch.equal(q[:16384], qa) and torch.equal(q[16384:], qb)
+    span = O.sf_bytes_span(16384, kq + ke)
+    assert torch.equal(sf[:span], sfa[:span]) and torch.equal(sf[span:2 * span], sfb[:span])
+    rows = torch.cat([torch.arange(0, 8), torch.arange(16380, 16388), torch.arange(tokens - 8, tokens),
+                      torch.randint(0, tokens, (40,), generator=torch.Generator().manual_seed(0))])
+    xs = x[rows.to(dev)].cpu()
+    qo, sfo = O.quantize_x(xs, idx.cpu().numpy(), ke)
+    assert np.array_equal(q[rows.to(dev)].cpu().numpy(), qo)
+    ncols = (kq + ke) // 16
+    sfh = sf.cpu().numpy()
+    for j, r in enumerate(rows.tolist()):
+        for c in (0, 1, 131, 247, 248, 249, 263):
+            assert sfh[O.sf_offset(r, c, ncols)] == sfo[O.sf_offset(j, c, ncols)]
+
+
+def test_absmax():
+    ops = _ops()
+    g = torch.Generator().manual_seed(0)
+    for n in (1, 7, 8, 4096, 1 << 20, (1 << 20) + 5):
+        x = (torch.randn(n, generator=g) * 3).to(torch.bfloat16).cuda()
+        assert float(ops.absmax(x)) == float(x.abs().max().float())
+
+
+def test_runs_on_the_current_stream_and_device_memory_only():
+    ops = _ops()
+    xs, idx = scaled_activations(64, 4096, seed=1)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        xd, idxd = xs.cuda(non_blocking=True), idx.cuda(non_blocking=True)
+        q, sf = ops.reorder_quantize_x(xd, idxd, 128)
+    s.synchronize()
+    O = _oracle()
+    qo, _ = O.quantize_x(xs, idx.numpy(), 128)
+    assert np.array_equal(q.cpu().numpy(), qo)
