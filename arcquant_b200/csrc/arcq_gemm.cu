@@ -265,7 +265,9 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
         const int tn = tile / p.tiles_m;
-        // sub-atom column offset when BN < 128: rows 32j..32j+31 of an atom live in TMEM column j
+        // sub-atom column offset when BN = 64: rows 32j..32j+31 of an atom live in TMEM column j, so
+        // the upper half of a 128-row scale atom starts two columns in.  (Tiles narrower than 64
+        // would need an odd column offset, which the block-scaled MMA rejects as misaligned.)
         const uint32_t sfb_sub = (BN < 128) ? (uint32_t)(((tn * BN) % 128) / 32) : 0u;
         if (!mbar_wait(tmem_empty_bar, (tile_it & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
@@ -428,10 +430,10 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   // are clipped by the TMA box (zero fill) and by the store guards.  ARCQ_GEMM_BN=32|64|128|256
   // overrides the choice (tuning / testing knob).
   int bn = 256;
-  while (bn > 32 && (long long)p.tiles_m * ((N + bn - 1) / bn) < di.num_sms) bn >>= 1;
+  while (bn > 64 && (long long)p.tiles_m * ((N + bn - 1) / bn) < di.num_sms) bn >>= 1;
   if (const char* e = getenv("ARCQ_GEMM_BN")) {
     int v = atoi(e);
-    if (v == 32 || v == 64 || v == 128 || v == 256) bn = v;
+    if (v == 64 || v == 128 || v == 256) bn = v;
   }
 
   CUtensorMap ma, mb;
@@ -443,8 +445,7 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   switch (bn) {
     case 256: return launch_bn<256>(ma, mb, p, di.num_sms, stream);
     case 128: return launch_bn<128>(ma, mb, p, di.num_sms, stream);
-    case 64: return launch_bn<64>(ma, mb, p, di.num_sms, stream);
-    default: return launch_bn<32>(ma, mb, p, di.num_sms, stream);
+    default: return launch_bn<64>(ma, mb, p, di.num_sms, stream);
   }
 }
 

@@ -45,7 +45,10 @@ def test_config1_single_linear_matches_oracle_and_fp32():
     assert np.array_equal(SFA.cpu().numpy()[va], sfa[va]) and np.array_equal(SFB.cpu().numpy()[vb], sfb[vb])
     ref = O.gemm_fast(qa, sfa, qb, sfb, float(sx * sw))
     y = Y.float().cpu().numpy()
-    assert np.linalg.norm(y - ref) / np.linalg.norm(ref) <= 1e-3
+    # output type is bf16: compare with the oracle rounded to bf16 (see tests/test_gpu_gemm.py)
+    refb = torch.from_numpy(ref).to(torch.bfloat16).float().numpy()
+    assert np.linalg.norm(y - refb) / np.linalg.norm(refb) <= 1e-3
+    assert np.linalg.norm(y - ref) / np.linalg.norm(ref) <= 2.2e-3
     # and the quantization error itself is where ARC puts it (about 0.1 on this input)
     full = (x.float() @ w.float().T).numpy()
     err = np.linalg.norm(y - full) / np.linalg.norm(full)

@@ -1,5 +1,11 @@
-"""Parity of the tcgen05 block-scaled NVFP4 GEMM with the oracle's dequantised fp32 matmul:
-relative Frobenius error <= 1e-3 (bf16 output rounding alone is ~2^-9 per element)."""
+"""Parity of the tcgen05 block-scaled NVFP4 GEMM with the oracle's dequantised fp32 matmul.
+
+The kernel's output type is bf16 (as the reference's).  Rounding an exact result to bf16 alone puts
+a relative Frobenius distance of ~1.6e-3 between it and the fp32 value (uniform error of half a
+7-bit-mantissa ulp), so the 1e-3 tolerance is applied where it is meaningful: between the kernel's
+output and the oracle's result rounded to the same output type - what remains is only the fp32
+accumulation order, a handful of one-ulp flips.  The raw distance to the unrounded fp32 oracle is
+bounded separately by the rounding floor."""
 import numpy as np
 import pytest
 import torch
@@ -44,8 +50,23 @@ def _run(a, sfa, b, sfb, alpha):
     return c.float().cpu().numpy()
 
 
+BF16_FLOOR = 2.2e-3     # relative Frobenius distance that bf16 rounding of the output alone may cause
+
+
 def _relerr(c, ref):
     return float(np.linalg.norm(c - ref) / max(np.linalg.norm(ref), 1e-30))
+
+
+def _to_bf16(ref):
+    return torch.from_numpy(np.ascontiguousarray(ref)).to(torch.bfloat16).float().numpy()
+
+
+def _assert_close(c, ref):
+    """c: kernel output (bf16 values as fp32); ref: fp32 oracle."""
+    refb = _to_bf16(ref)
+    assert _relerr(c, refb) <= TOL, ("vs oracle rounded to bf16", _relerr(c, refb))
+    assert (c == refb).mean() >= 0.99            # all but accumulation-order flips are bit-equal
+    assert _relerr(c, ref) <= BF16_FLOOR, ("vs fp32 oracle", _relerr(c, ref))
 
 
 def test_one_hot_operands_land_where_they_should():
@@ -94,7 +115,7 @@ def test_matches_dequantised_fp32_matmul(m, n, kq, ke):
     a, sfa, b, sfb, alpha = _operands(m, n, kq, ke, seed=m + n)
     ref = O.gemm_fast(a, sfa, b, sfb, alpha)
     c = _run(a, sfa, b, sfb, alpha)
-    assert _relerr(c, ref) <= TOL
+    _assert_close(c, ref)
 
 
 def test_tail_k_stage_and_garbage_in_scale_padding():
@@ -109,7 +130,7 @@ def test_tail_k_stage_and_garbage_in_scale_padding():
         arr[~keep] = 0x7F
     c = _run(a, sfa, b, sfb, alpha)
     assert np.isfinite(c).all()
-    assert _relerr(c, ref) <= TOL
+    _assert_close(c, ref)
 
 
 def test_device_resident_alpha():
@@ -119,7 +140,7 @@ def test_device_resident_alpha():
     sa = torch.tensor(alpha ** 0.5, dtype=torch.float32, device="cuda")
     c1 = ops.matmul_dev_alpha(t[0], t[1], t[2], t[3], sa, sa).float().cpu().numpy()
     ref = O.gemm_fast(a, sfa, b, sfb, float(np.float32(alpha ** 0.5)) ** 2)
-    assert _relerr(c1, ref) <= TOL
+    _assert_close(c1, ref)
 
 
 @pytest.mark.parametrize("m,n,kq", [(4096, 4096, 4096), (16384, 6144, 4096), (4096, 4096, 14336)])
@@ -153,7 +174,7 @@ def test_large_shapes_by_row_independence_and_samples(m, n, kq):
     csub = ops.matmul(asub, b, torch.from_numpy(sfsub).to(dev), sfb, alpha)
     assert torch.equal(csub, c[rows.to(dev)])
     ref = O.gemm_fast(asub.cpu().numpy(), sfsub, b.cpu().numpy(), sfb.cpu().numpy(), alpha)
-    assert _relerr(csub.float().cpu().numpy(), ref) <= TOL
+    _assert_close(csub.float().cpu().numpy(), ref)
     # and against the unquantised product the ARC error stays in the expected band
     y = (x[rows.to(dev)].float() @ w.float().T).cpu().numpy()
     assert _relerr(csub.float().cpu().numpy(), y) < 0.2
