@@ -97,7 +97,7 @@ int arcq_rmsnorm_quantize_x(const void* x, const void* gamma, float eps, const i
   int rc = check_quant_shape(M, KQ, KE, ARCQ_MODE_16);
   if (rc != ARCQ_OK) return rc;
   int g = KQ / 16;
-  if (g % 32 || g > 512) return ARCQ_ERR_UNSUPPORTED_K;
+  if (g % 32 || g < 64 || g > 512) return ARCQ_ERR_UNSUPPORTED_K;
   if (M == 0) return ARCQ_OK;
   if (!x || !gamma || !qx || !sfx) return ARCQ_ERR_NULL_POINTER;
   if (!aligned16(x) || !aligned16(qx)) return ARCQ_ERR_ALIGNMENT;

@@ -8,18 +8,27 @@
 //
 //  * persistent CTAs walk over PAIRS of rows.  A pair is staged in shared memory interleaved at
 //    2-byte granularity - word c = (row0[c], row1[c]) - so the random channel gather costs one
-//    32-bit shared load per TWO elements (half the bank-conflict wavefronts of a 16-bit gather);
+//    32-bit shared load per TWO elements, and everything downstream works on both rows at once:
+//    packed 16-bit max for the block amax, packed fp32x2 multiplies (FMUL2) for the scaling,
+//    cvt.rn.bf16x2 for the RMSNorm rounding;
 //  * the next pair is in flight in registers (128-bit coalesced streaming loads) while the current
-//    one is quantized (double buffer), so HBM latency is covered by arithmetic;
-//  * the channel order is turned once per CTA into a shared table of byte offsets, read back with
-//    128-bit loads (8 offsets each) instead of one global int16 load per element per row;
+//    one is quantized (double buffer); 16-byte chunks are stored XOR-swizzled so the 128-bit shared
+//    stores are conflict free;
+//  * the channel order becomes, once per CTA, a shared table of (swizzled) byte offsets read back
+//    with 128-bit loads - no per-row index traffic;
+//  * block scale: ue4m3(clamp(amax/6)) and its fp32 reciprocal come from two tiny tables indexed by
+//    the bf16 bits of the amax (built in the prologue with the IEEE slow path, so both paths agree
+//    by construction); the slow path still serves subnormal / saturated scales and critical groups;
 //  * conversions use the hardware cvt.rn.satfinite.{e2m1x2,e4m3x2}.f32 (round to nearest even,
 //    saturating), eight codes are packed per 32-bit word and stored 8 bytes per group;
 //  * RMSNorm partial sums are taken from the registers of the streaming load, in the reference's
 //    accumulation order, and the reciprocal root is the correctly rounded one.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <cstdlib>
 
 #include "arcq_internal.h"
 
@@ -46,10 +55,6 @@ struct QuantParams {
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
-__device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
-  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
-}
-
 __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -58,25 +63,32 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
   return v;
 }
 
+// (lo, hi) fp32 -> packed bf16x2, round to nearest even.
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// per-halfword unsigned max
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 // float -> ue4m3 byte: round to nearest even, saturating at 448 (input is in [2^-9, 448]).
 __device__ __forceinline__ uint32_t ue4m3_encode(float s) {
   uint16_t r;
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(s));
   return (uint32_t)r & 0xffu;
 }
-
 __device__ __forceinline__ float ue4m3_decode(uint32_t c) {
   uint32_t e = (c >> 3) & 15u, m = c & 7u;
   return e ? __uint_as_float(((e + 120u) << 23) | (m << 20)) : (float)m * 0.001953125f;
 }
 
-__device__ __forceinline__ float e2m1_decode(uint32_t c) {
-  uint32_t e = (c >> 1) & 3u, m = c & 1u;
-  float v = e ? __uint_as_float(((126u + e) << 23) | (m << 22)) : 0.5f * (float)m;
-  return (c & 8u) ? -v : v;
-}
-
-// Eight floats -> eight e2m1 codes in one word, element 0 in the lowest nibble.
+// Eight floats -> eight e2m1 codes in one word, element 0 in the lowest nibble
+// (cvt.e2m1x2 puts its first source in the high nibble).
 __device__ __forceinline__ uint32_t e2m1x8(float a0, float a1, float a2, float a3, float a4, float a5,
                                            float a6, float a7) {
   uint32_t out;
@@ -93,6 +105,14 @@ __device__ __forceinline__ uint32_t e2m1x8(float a0, float a1, float a2, float a
   return out;
 }
 
+// One byte of two e2m1 codes -> their values (exact): x = low nibble, y = high nibble.
+__device__ __forceinline__ float2 e2m1x2_decode(uint32_t byte) {
+  uint32_t h2;
+  const uint16_t b16 = (uint16_t)(byte & 0xffu);
+  asm("{\n.reg .b8 t;\nmov.b16 {t, _}, %1;\ncvt.rn.f16x2.e2m1x2 %0, t;\n}" : "=r"(h2) : "h"(b16));
+  return __half22float2(*reinterpret_cast<__half2*>(&h2));
+}
+
 struct GroupScale {
   uint32_t byte;  // ue4m3 code
   float dec;      // its value
@@ -100,7 +120,8 @@ struct GroupScale {
   float rcp;      // fp32(1/dec)
 };
 
-__device__ __forceinline__ GroupScale make_scale(float amax) {
+// IEEE path: every case, including subnormal and saturated scales.
+__device__ __noinline__ GroupScale make_scale_slow(float amax) {
   GroupScale s;
   float t = __fdiv_rn(amax, 6.0f);
   t = fminf(t, 448.0f);
@@ -111,39 +132,30 @@ __device__ __forceinline__ GroupScale make_scale(float amax) {
   return s;
 }
 
-// Quantize the 16 values held in the low (HI=false) or high (HI=true) halves of w[0..15].
-template <bool HI>
-__device__ __forceinline__ uint2 encode16(const uint32_t (&w)[16], float rcp) {
-  float v[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(HI ? bf16hi(w[i]) : bf16lo(w[i]), rcp);
-  uint2 c;
-  c.x = e2m1x8(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7]);
-  c.y = e2m1x8(v[8], v[9], v[10], v[11], v[12], v[13], v[14], v[15]);
-  return c;
-}
-
-template <bool HI>
-__device__ __forceinline__ float amax16(const uint32_t (&w)[16]) {
-  float m = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(HI ? bf16hi(w[i]) : bf16lo(w[i])));
-  return m;
-}
-
-// Residuals of one row's critical group: r[i] = bf16(x - q*s), left in the same half of w.
-template <bool HI>
-__device__ __forceinline__ void residual16(uint32_t (&w)[16], uint2 codes, const GroupScale& s, int mode) {
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    uint32_t c = ((i < 8 ? codes.x : codes.y) >> (4 * (i & 7))) & 15u;
-    float x = HI ? bf16hi(w[i]) : bf16lo(w[i]);
-    float qv = e2m1_decode(c);
-    // mode 16: against the rounded scale (the product is exact in fp32);
-    // mode 32: against the un-rounded scale, fused, as the 32-wide reference kernels compile.
-    float d = (mode == 32) ? __fmaf_rn(-qv, s.raw, x) : __fsub_rn(x, __fmul_rn(qv, s.dec));
-    uint32_t b = f32_to_bf16_bits(d);
-    w[i] = HI ? ((w[i] & 0x0000ffffu) | (b << 16)) : ((w[i] & 0xffff0000u) | b);
+// Table path.  ab = bf16 bits of the amax (15 bits).  For a normal result the scale code is
+// T[mantissa] shifted by the exponent, and 1/scale is RB[code mantissa] shifted likewise (powers
+// of two do not change any rounding).  Anything outside the normal, unsaturated range takes the
+// IEEE path.
+struct ScaleLut {
+  const uint8_t* T;     // [128] code of amax = 1.m7 (exponent field 127)
+  const uint32_t* RB;   // [8]   fp32 bits of 1/(1+m3/8), exponent pre-biased by 7
+};
+// Both rows of a pair: one (rarely taken) branch covers the IEEE fallback of either row.
+__device__ __forceinline__ void scale_of_pair(uint32_t m, const ScaleLut& lut, uint32_t& c0, uint32_t& c1, float& r0,
+                                              float& r1) {
+  const uint32_t a0 = m & 0xffffu, a1 = m >> 16;
+  const int s0 = (int)lut.T[a0 & 127u] + (int)((a0 >> 7) << 3) - 1016;
+  const int s1 = (int)lut.T[a1 & 127u] + (int)((a1 >> 7) << 3) - 1016;
+  c0 = (uint32_t)s0;
+  c1 = (uint32_t)s1;
+  r0 = __uint_as_float(lut.RB[s0 & 7] - ((uint32_t)(s0 >> 3) << 23));
+  r1 = __uint_as_float(lut.RB[s1 & 7] - ((uint32_t)(s1 >> 3) << 23));
+  // (unsigned)(s - 8) > 118  <=>  s < 8 or s > 126
+  if (__builtin_expect(((uint32_t)(s0 - 8) > 118u) | ((uint32_t)(s1 - 8) > 118u), 0)) {
+    const GroupScale g0 = make_scale_slow(__uint_as_float(a0 << 16));
+    const GroupScale g1 = make_scale_slow(__uint_as_float(a1 << 16));
+    c0 = g0.byte; r0 = g0.rcp;
+    c1 = g1.byte; r1 = g1.rcp;
   }
 }
 
@@ -152,15 +164,13 @@ __device__ __forceinline__ size_t sf_row_base(long long r, int natoms) {
 }
 __device__ __forceinline__ size_t sf_col(int c) { return (size_t)(c >> 2) * 512 + (size_t)(c & 3); }
 
-// Where a group's main / residual codes and scales go.
+// Where a critical group's main / residual codes and scales go.
 struct Slot {
   int byte_main, col_main, byte_res, col_res;
 };
 __device__ __forceinline__ Slot slot_of(int g, int G0, int mode) {
   Slot s;
-  if (g < G0) {
-    s.byte_main = 8 * g; s.col_main = g; s.byte_res = -1; s.col_res = -1;
-  } else if (mode == 32) {
+  if (mode == 32) {
     int j = g - G0, pair = j >> 1, h = j & 1;
     s.col_main = G0 + 4 * pair + h; s.col_res = s.col_main + 2;
     s.byte_main = 8 * G0 + 32 * pair + 8 * h; s.byte_res = s.byte_main + 16;
@@ -172,26 +182,91 @@ __device__ __forceinline__ Slot slot_of(int g, int G0, int mode) {
   return s;
 }
 
-template <bool HI>
-__device__ __forceinline__ void quantize_store(uint32_t (&w)[16], int g, const QuantParams& p,
-                                               uint8_t* qrow, uint8_t* sfrow) {
-  GroupScale s = make_scale(amax16<HI>(w));
-  uint2 codes = encode16<HI>(w, s.rcp);
-  Slot sl = slot_of(g, p.G0, p.mode);
-  *reinterpret_cast<uint2*>(qrow + sl.byte_main) = codes;
-  sfrow[sf_col(sl.col_main)] = (uint8_t)s.byte;
-  if (g >= p.G0) {
-    if (p.is_weight) {
-      *reinterpret_cast<uint2*>(qrow + sl.byte_res) = codes;
-      sfrow[sf_col(sl.col_res)] = (uint8_t)s.byte;
-    } else {
-      residual16<HI>(w, codes, s, p.mode);
-      GroupScale rs = make_scale(amax16<HI>(w));
-      uint2 rc = encode16<HI>(w, rs.rcp);
-      *reinterpret_cast<uint2*>(qrow + sl.byte_res) = rc;
-      sfrow[sf_col(sl.col_res)] = (uint8_t)rs.byte;
-    }
+// Both rows of a pair at once: w[i] = (row0 value, row1 value) as bf16x2.  Multiplies every value by
+// its row's reciprocal scale (one FMUL2 per word) and converts to e2m1, eight codes per word.
+__device__ __forceinline__ void encode_pair(const uint32_t (&w)[16], float rcp0, float rcp1, uint2& c0, uint2& c1) {
+  const float2 r = make_float2(rcp0, rcp1);
+  float2 v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __fmul2_rn(make_float2(bf16lo(w[i]), bf16hi(w[i])), r);
+  c0.x = e2m1x8(v[0].x, v[1].x, v[2].x, v[3].x, v[4].x, v[5].x, v[6].x, v[7].x);
+  c0.y = e2m1x8(v[8].x, v[9].x, v[10].x, v[11].x, v[12].x, v[13].x, v[14].x, v[15].x);
+  c1.x = e2m1x8(v[0].y, v[1].y, v[2].y, v[3].y, v[4].y, v[5].y, v[6].y, v[7].y);
+  c1.y = e2m1x8(v[8].y, v[9].y, v[10].y, v[11].y, v[12].y, v[13].y, v[14].y, v[15].y);
+}
+
+// Packed |.| maximum of the sixteen words: low half = row0 amax bits, high half = row1.
+__device__ __forceinline__ uint32_t amax_pair(const uint32_t (&w)[16]) {
+  uint32_t m = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m = max_u16x2(m, w[i] & 0x7fff7fffu);
+  return m;
+}
+
+// Residuals of a critical group, both rows: w[i] <- bf16(x - q*s) per half.
+// mode 16 subtracts against the rounded scale (q*s is exact in fp32, so the fused form is the same
+// number); mode 32 against the un-rounded one, fused, as the 32-wide reference kernels compile.
+__device__ __forceinline__ void residual_pair(uint32_t (&w)[16], uint2 c0, uint2 c1, float s0, float s1) {
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    const uint32_t b0 = ((i < 8 ? c0.x : c0.y) >> (4 * (i & 7))) & 0xffu;
+    const uint32_t b1 = ((i < 8 ? c1.x : c1.y) >> (4 * (i & 7))) & 0xffu;
+    const float2 q0 = e2m1x2_decode(b0), q1 = e2m1x2_decode(b1);
+    float d00 = __fmaf_rn(-q0.x, s0, bf16lo(w[i])), d01 = __fmaf_rn(-q0.y, s0, bf16lo(w[i + 1]));
+    float d10 = __fmaf_rn(-q1.x, s1, bf16hi(w[i])), d11 = __fmaf_rn(-q1.y, s1, bf16hi(w[i + 1]));
+    w[i] = pack_bf16x2_rn(d00, d10);
+    w[i + 1] = pack_bf16x2_rn(d01, d11);
   }
+}
+
+// Quantize one group of both rows and store codes + scales.  Every lane runs the same main path
+// (table scale, FMUL2 + cvt); only the residual of a critical group is a divergent extra.
+// Row 1 is stored before row 0: for the odd last row of the input the caller aliases row 1's
+// output pointers to row 0's, and the later store wins.
+__device__ __forceinline__ void quantize_group_pair(uint32_t (&w)[16], int g, const QuantParams& p,
+                                                    const ScaleLut& lut, uint8_t* q0, uint8_t* q1, uint8_t* sf0,
+                                                    uint8_t* sf1) {
+  const uint32_t m = amax_pair(w);
+  uint32_t s0, s1;
+  float r0, r1;
+  scale_of_pair(m, lut, s0, s1, r0, r1);
+  uint2 c0, c1;
+  encode_pair(w, r0, r1, c0, c1);
+  const bool critical = g >= p.G0;
+  int byte_main = 8 * g, col_main = g;
+  Slot sl;
+  if (critical) {
+    sl = slot_of(g, p.G0, p.mode);
+    byte_main = sl.byte_main;
+    col_main = sl.col_main;
+  }
+  const size_t cm = sf_col(col_main);
+  *reinterpret_cast<uint2*>(q1 + byte_main) = c1;
+  sf1[cm] = (uint8_t)s1;
+  *reinterpret_cast<uint2*>(q0 + byte_main) = c0;
+  sf0[cm] = (uint8_t)s0;
+  if (!critical) return;
+
+  // critical group: the re-quantized residual (or, for weights, a copy of the main codes)
+  uint2 e0 = c0, e1 = c1;
+  uint32_t t0 = s0, t1 = s1;
+  if (!p.is_weight) {
+    float d0 = ue4m3_decode(s0), d1 = ue4m3_decode(s1);
+    if (p.mode == 32) {   // against the un-rounded fp32 scale
+      d0 = make_scale_slow(__uint_as_float((m & 0xffffu) << 16)).raw;
+      d1 = make_scale_slow(__uint_as_float((m >> 16) << 16)).raw;
+    }
+    residual_pair(w, c0, c1, d0, d1);
+    const uint32_t rm = amax_pair(w);
+    float h0, h1;
+    scale_of_pair(rm, lut, t0, t1, h0, h1);
+    encode_pair(w, h0, h1, e0, e1);
+  }
+  const size_t cr = sf_col(sl.col_res);
+  *reinterpret_cast<uint2*>(q1 + sl.byte_res) = e1;
+  sf1[cr] = (uint8_t)t1;
+  *reinterpret_cast<uint2*>(q0 + sl.byte_res) = e0;
+  sf0[cr] = (uint8_t)t0;
 }
 
 // Sum-of-squares tree of one row in the reference's order (rmsnorm.cu:131-154 of ARCQuant), done by
@@ -215,33 +290,32 @@ __device__ __forceinline__ float rms_tree(const float* ps, int nt, int lane) {
   return s;  // valid in lane 0
 }
 
-__device__ __forceinline__ float sumsq8(uint4 a, float acc) {
-  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float lo = bf16lo(w[i]), hi = bf16hi(w[i]);
-    acc = __fmaf_rn(lo, lo, acc);
-    acc = __fmaf_rn(hi, hi, acc);
-  }
-  return acc;
-}
+// Physical position (in 16-byte units) of logical 16-byte unit j of an interleaved row pair.
+__device__ __forceinline__ uint32_t swz16(uint32_t j) { return j ^ ((j >> 3) & 1u); }
+// Byte offset of channel ch's (row0,row1) word.
+__device__ __forceinline__ uint32_t word_offset(uint32_t ch) { return (swz16(ch >> 2) << 4) | ((ch & 3u) << 2); }
 
 // CPT: 16-byte chunks per thread per row; NBUF: shared row-pair buffers; RMS: fused RMSNorm;
-// RAWIDX: the offset table holds channel numbers (rows wider than 16384) instead of byte offsets.
-// MAXT / MINB: launch bounds (threads per CTA, CTAs per SM the register budget must allow).
+// RAWIDX: the offset table holds 16-bit channel numbers (rows wider than 16384 channels) instead of
+// 32-bit byte offsets.  MAXT / MINB: launch bounds.
 template <int CPT, int NBUF, bool RMS, bool RAWIDX, int MAXT, int MINB>
 __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x, nt = blockDim.x;
   const int KQ = p.KQ;
 
-  uint16_t* offs = reinterpret_cast<uint16_t*>(smem);
-  size_t cursor = ((size_t)KQ * 2 + 15) & ~(size_t)15;
-  uint16_t* gperm = reinterpret_cast<uint16_t*>(smem + cursor);
+  // shared layout: [scale tables 160 B][offsets][gain (RMS)][partial sums, rstd (RMS)][row-pair buffers]
+  uint8_t* lutT = smem;
+  uint32_t* lutRB = reinterpret_cast<uint32_t*>(smem + 128);
+  size_t cursor = 160;
+  uint32_t* offs32 = reinterpret_cast<uint32_t*>(smem + cursor);
+  uint16_t* offs16 = reinterpret_cast<uint16_t*>(smem + cursor);
+  cursor += ((size_t)KQ * (RAWIDX ? 2 : 4) + 15) & ~(size_t)15;
+  float* gperm = reinterpret_cast<float*>(smem + cursor);
   float* psum = nullptr;
   float* rstd_s = nullptr;
   if (RMS) {
-    cursor += ((size_t)KQ * 2 + 15) & ~(size_t)15;
+    cursor += (size_t)KQ * 4;
     psum = reinterpret_cast<float*>(smem + cursor);
     cursor += (size_t)2 * nt * sizeof(float);
     rstd_s = reinterpret_cast<float*>(smem + cursor);
@@ -249,11 +323,20 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
   }
   uint32_t* bufs = reinterpret_cast<uint32_t*>(smem + cursor);
 
+  for (int j = tid; j < 128; j += nt)
+    lutT[j] = (uint8_t)make_scale_slow(__uint_as_float(((127u << 7) | (uint32_t)j) << 16)).byte;
+  if (tid < 8)
+    lutRB[tid] = tid ? (__float_as_uint(__frcp_rn(1.0f + 0.125f * (float)tid)) + (7u << 23)) : (134u << 23);
+  // Tables are laid out [vector v][group g][4]: consecutive lanes (groups) read consecutive 16 bytes,
+  // so every 128-bit table load is conflict free.
   for (int j = tid; j < KQ; j += nt) {
     int c = p.idx ? (int)p.idx[j] : j;
-    offs[j] = (uint16_t)(RAWIDX ? c : c * 4);
-    if (RMS) gperm[j] = p.gamma[c];
+    const int g = j >> 4, i = j & 15;
+    const int slot = (((i >> 2) * p.G + g) << 2) | (i & 3);
+    if (RAWIDX) offs16[j] = (uint16_t)c; else offs32[slot] = word_offset((uint32_t)c);
+    if (RMS) gperm[slot] = __uint_as_float((uint32_t)p.gamma[c] << 16);
   }
+  const ScaleLut lut{lutT, lutRB};
 
   uint4 ra[CPT], rb[CPT];
 
@@ -273,35 +356,35 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
   };
 
   auto store_pair = [&](uint32_t* buf) {
+    float2 ss = make_float2(0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < CPT; ++j) {
       int c = tid + j * nt;
       if (c < p.nchunks) {
-        uint4 lo, hi;  // words 8c..8c+3 and 8c+4..8c+7: (row0[ch], row1[ch]) per word
+        uint4 lo, hi;  // words of channels 8c..8c+3 and 8c+4..8c+7: (row0[ch], row1[ch]) per word
         lo.x = __byte_perm(ra[j].x, rb[j].x, 0x5410); lo.y = __byte_perm(ra[j].x, rb[j].x, 0x7632);
         lo.z = __byte_perm(ra[j].y, rb[j].y, 0x5410); lo.w = __byte_perm(ra[j].y, rb[j].y, 0x7632);
         hi.x = __byte_perm(ra[j].z, rb[j].z, 0x5410); hi.y = __byte_perm(ra[j].z, rb[j].z, 0x7632);
         hi.z = __byte_perm(ra[j].w, rb[j].w, 0x5410); hi.w = __byte_perm(ra[j].w, rb[j].w, 0x7632);
-        uint4* dst = reinterpret_cast<uint4*>(buf + 8 * (size_t)c);
-        // Lanes 4..7 of each quarter warp write the upper half first, so that the eight lanes of
-        // one 128-bit store wavefront land on distinct banks (byte stride 32 would fold them 2-way).
-        const bool swap = (tid & 4) != 0;
-        uint4 first, second;
-        first.x = swap ? hi.x : lo.x; first.y = swap ? hi.y : lo.y;
-        first.z = swap ? hi.z : lo.z; first.w = swap ? hi.w : lo.w;
-        second.x = swap ? lo.x : hi.x; second.y = swap ? lo.y : hi.y;
-        second.z = swap ? lo.z : hi.z; second.w = swap ? lo.w : hi.w;
-        dst[swap ? 1 : 0] = first;
-        dst[swap ? 0 : 1] = second;
+        // XOR-swizzled 16-byte units: the eight lanes of a 128-bit store wavefront hit distinct banks
+        uint4* b4 = reinterpret_cast<uint4*>(buf);
+        b4[swz16(2u * c)] = lo;
+        b4[swz16(2u * c + 1u)] = hi;
+        if (RMS) {
+          // reference thread t adds chunk t then chunk t+KQ/16, eight elements each, in order;
+          // the two rows ride in the two lanes of a packed FMA
+          const uint32_t ws[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float2 a = make_float2(bf16lo(ws[i]), bf16hi(ws[i]));
+            ss = __ffma2_rn(a, a, ss);
+          }
+        }
       }
     }
     if (RMS) {
-      // Reference thread t adds chunk t then chunk t+KQ/16, eight elements each, in order.
-      float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-      for (int j = 0; j < CPT; ++j) { s0 = sumsq8(ra[j], s0); s1 = sumsq8(rb[j], s1); }
-      psum[tid] = s0;
-      psum[nt + tid] = s1;
+      psum[tid] = ss.x;
+      psum[nt + tid] = ss.y;
     }
   };
 
@@ -316,7 +399,7 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
     const bool more = nxt < p.npairs;
     if (NBUF == 2 && more) load_pair(nxt);
 
-    float rstd0 = 1.f, rstd1 = 1.f;
+    float2 rstd = make_float2(1.f, 1.f);
     if (RMS) {
       const int warp = tid >> 5, lane = tid & 31;
       if (warp < 2) {
@@ -324,43 +407,56 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
         if (lane == 0) rstd_s[warp] = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)KQ), p.eps));
       }
       __syncthreads();
-      rstd0 = rstd_s[0];
-      rstd1 = rstd_s[1];
+      rstd = make_float2(rstd_s[0], rstd_s[1]);
     }
 
     const uint8_t* buf = reinterpret_cast<const uint8_t*>(bufs + (size_t)cur * KQ);
     const long long r0 = 2 * pair, r1 = r0 + 1;
     const bool has1 = r1 < p.rows;
     uint8_t* q0 = p.q + (size_t)r0 * row_bytes;
-    uint8_t* q1 = q0 + row_bytes;
+    uint8_t* q1 = has1 ? q0 + row_bytes : q0;          // odd last row: alias, row 0 is stored last
     uint8_t* sf0 = p.sf + sf_row_base(r0, p.natoms);
-    uint8_t* sf1 = p.sf + sf_row_base(r1, p.natoms);
+    uint8_t* sf1 = has1 ? p.sf + sf_row_base(r1, p.natoms) : sf0;
 
     for (int g = tid; g < p.G; g += nt) {
-      const uint4* op = reinterpret_cast<const uint4*>(offs + 16 * g);
-      const uint4 o0 = op[0], o1 = op[1];
-      const uint32_t ow[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
       uint32_t w[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        uint32_t o = (i & 1) ? (ow[i >> 1] >> 16) : (ow[i >> 1] & 0xffffu);
-        w[i] = *reinterpret_cast<const uint32_t*>(buf + (RAWIDX ? o * 4u : o));
-      }
-      if (RMS) {
-        const uint4* gp = reinterpret_cast<const uint4*>(gperm + 16 * g);
-        const uint4 g0 = gp[0], g1 = gp[1];
-        const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      if (RAWIDX) {
+        const uint4* op = reinterpret_cast<const uint4*>(offs16 + 16 * g);
+        const uint4 o0 = op[0], o1 = op[1];
+        const uint32_t ow[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float gm = (i & 1) ? bf16hi(gw[i >> 1]) : bf16lo(gw[i >> 1]);
-          // bf16 x bf16 is exact in fp32; then one rounding by rstd, one to bf16
-          float n0 = __fmul_rn(__fmul_rn(bf16lo(w[i]), gm), rstd0);
-          float n1 = __fmul_rn(__fmul_rn(bf16hi(w[i]), gm), rstd1);
-          w[i] = f32_to_bf16_bits(n0) | (f32_to_bf16_bits(n1) << 16);
+          uint32_t ch = (i & 1) ? (ow[i >> 1] >> 16) : (ow[i >> 1] & 0xffffu);
+          w[i] = *reinterpret_cast<const uint32_t*>(buf + word_offset(ch));
+        }
+      } else {
+        const uint4* op = reinterpret_cast<const uint4*>(offs32) + g;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 o = op[v * p.G];
+          w[4 * v + 0] = *reinterpret_cast<const uint32_t*>(buf + o.x);
+          w[4 * v + 1] = *reinterpret_cast<const uint32_t*>(buf + o.y);
+          w[4 * v + 2] = *reinterpret_cast<const uint32_t*>(buf + o.z);
+          w[4 * v + 3] = *reinterpret_cast<const uint32_t*>(buf + o.w);
         }
       }
-      quantize_store<false>(w, g, p, q0, sf0);
-      if (has1) quantize_store<true>(w, g, p, q1, sf1);
+      if (RMS) {
+        const float4* gp = reinterpret_cast<const float4*>(gperm) + g;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const float4 gm = gp[v * p.G];
+          const float gs[4] = {gm.x, gm.y, gm.z, gm.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = 4 * v + k;
+            // bf16 x bf16 is exact in fp32; then one rounding by rstd (both rows in one FMUL2), one to bf16
+            const float2 t = make_float2(__fmul_rn(bf16lo(w[i]), gs[k]), __fmul_rn(bf16hi(w[i]), gs[k]));
+            const float2 n = __fmul2_rn(t, rstd);
+            w[i] = pack_bf16x2_rn(n.x, n.y);
+          }
+        }
+      }
+      quantize_group_pair(w, g, p, lut, q0, q1, sf0, sf1);
     }
 
     if (NBUF == 2) {
@@ -377,20 +473,21 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
 
 __global__ void arcq_absmax_kernel(const uint4* __restrict__ x, long long nvec, const uint16_t* tail,
                                    int ntail, unsigned int* out) {
-  float m = 0.f;
+  uint32_t m = 0;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
     uint4 v = ldg_stream(x + i);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int k = 0; k < 4; ++k) m = fmaxf(m, fmaxf(fabsf(bf16lo(w[k])), fabsf(bf16hi(w[k]))));
+    m = max_u16x2(m, v.x & 0x7fff7fffu);
+    m = max_u16x2(m, v.y & 0x7fff7fffu);
+    m = max_u16x2(m, v.z & 0x7fff7fffu);
+    m = max_u16x2(m, v.w & 0x7fff7fffu);
   }
-  if (blockIdx.x == 0 && (int)threadIdx.x < ntail)
-    m = fmaxf(m, fabsf(__uint_as_float((uint32_t)tail[threadIdx.x] << 16)));
+  uint32_t r = max(m & 0xffffu, m >> 16);
+  if (blockIdx.x == 0 && (int)threadIdx.x < ntail) r = max(r, (uint32_t)tail[threadIdx.x] & 0x7fffu);
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  for (int d = 16; d > 0; d >>= 1) r = max(r, __shfl_xor_sync(0xffffffffu, r, d));
   // non-negative floats order like their bit patterns
-  if ((threadIdx.x & 31) == 0) atomicMax(out, __float_as_uint(m));
+  if ((threadIdx.x & 31) == 0) atomicMax(out, r << 16);
 }
 
 template <int CPT, int NBUF, bool RMS, bool RAWIDX, int MAXT, int MINB>
@@ -435,34 +532,38 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   p.eps = eps;
 
   const bool rms = gamma != nullptr;
-  const size_t table = ((size_t)KQ * 2 + 15) & ~(size_t)15;
-  int nt, cpt, nbuf;
+  int nt, cpt;
   if (rms) {
     nt = p.G;  // one reference thread per CUDA thread: keeps the accumulation order
     cpt = 2;
-    nbuf = 2;
   } else {
     int gpt = (p.G + 511) / 512;
     nt = (((p.G + gpt - 1) / gpt) + 31) / 32 * 32;
     int need = (p.nchunks + nt - 1) / nt;
-    cpt = need <= 2 ? 2 : (need <= 4 ? 4 : 8);
-    nbuf = 2;
     if (need > 8) return ARCQ_ERR_UNSUPPORTED_K;
+    cpt = need <= 2 ? 2 : (need <= 4 ? 4 : 8);
   }
   const bool rawidx = KQ > 16384;
-  size_t smem = table + (rms ? table + (size_t)2 * nt * sizeof(float) + 16 : 0) + (size_t)nbuf * KQ * 4;
+  const size_t table = 160 + (((size_t)KQ * (rawidx ? 2 : 4) + 15) & ~(size_t)15);
+  size_t smem = table + (rms ? (size_t)KQ * 4 + (size_t)2 * nt * sizeof(float) + 16 : 0) + (size_t)2 * KQ * 4;
   if (cpt == 8 || rawidx || smem > (size_t)di.max_smem_optin) {
-    nbuf = 1;
-    cpt = 8;
+    // very wide rows: one buffer, loads not overlapped with the arithmetic
     smem = table + (size_t)KQ * 4;
     if (rms || smem > (size_t)di.max_smem_optin) return ARCQ_ERR_UNSUPPORTED_K;
     return rawidx ? launch_variant<8, 1, false, true, 512, 1>(p, nt, smem, di, stream)
                   : launch_variant<8, 1, false, false, 512, 1>(p, nt, smem, di, stream);
   }
   if (nt <= 256) {
-    // narrow rows: three resident CTAs per SM keep enough loads in flight
-    if (rms) return launch_variant<2, 2, true, false, 256, 3>(p, nt, smem, di, stream);
-    if (cpt == 2) return launch_variant<2, 2, false, false, 256, 3>(p, nt, smem, di, stream);
+    // narrow rows: several resident CTAs per SM keep enough loads in flight.  ARCQ_QUANT_MINB=2
+    // trades one resident CTA for a larger register budget (tuning knob).
+    static const int minb = [] { const char* e = getenv("ARCQ_QUANT_MINB"); return e ? atoi(e) : 3; }();
+    if (minb == 2) {
+      if (rms) return launch_variant<2, 2, true, false, 256, 2>(p, nt, smem, di, stream);
+      if (cpt == 2) return launch_variant<2, 2, false, false, 256, 2>(p, nt, smem, di, stream);
+    } else {
+      if (rms) return launch_variant<2, 2, true, false, 256, 3>(p, nt, smem, di, stream);
+      if (cpt == 2) return launch_variant<2, 2, false, false, 256, 3>(p, nt, smem, di, stream);
+    }
   }
   if (rms) return launch_variant<2, 2, true, false, 512, 1>(p, nt, smem, di, stream);
   if (cpt == 2) return launch_variant<2, 2, false, false, 512, 1>(p, nt, smem, di, stream);

@@ -86,7 +86,7 @@ int arcq_reorder_quantize_x(const void* x, const int16_t* reorder_index, int64_t
  * kernels/src/rmsnorm.cu:68-281): RMSNorm with gain `gamma` (bf16 [KQ]) fused
  * in front of the mode-16 quantizer.  The sum of squares is accumulated in the
  * reference's order; the reciprocal root is the correctly rounded fp32
- * 1/sqrt(ss/KQ + eps).  KQ/16 must be a multiple of 32 and at most 512. */
+ * 1/sqrt(ss/KQ + eps).  KQ/16 must be a multiple of 32 between 64 and 512 (KQ 1024..8192). */
 int arcq_rmsnorm_quantize_x(const void* x, const void* gamma, float eps, const int16_t* reorder_index,
                             int64_t M, int KQ, int KE, uint8_t* qx, uint8_t* sfx, void* stream);
 
