@@ -1,0 +1,166 @@
+"""Llama-architecture decoder layer on ARC-NVFP4 linears, tensor-parallel over 1/2/4/8 GPUs.
+
+Call order of the reference layer (model/qLlamaLayer.py:136-178, 281-372, 423-443 of ARCQuant) with
+its two fusions made explicit: q/k/v share one quantized activation, so they are ONE GEMM over a
+fused [q;k;v] weight, and likewise gate/up; the two RMSNorms are fused into the quantizer
+(`rmsnorm_quantize_x`, as the reference's benchmark model does, benchmarks/modeling_arc.py:222-227).
+
+    x --rmsnorm+quant(q order)--> qkv GEMM --RoPE, causal GQA attention--> quant(o order) --> o GEMM
+      --all-reduce--> +x --rmsnorm+quant(up order)--> gate_up GEMM --SiLU*up--> quant(down order)
+      --> down GEMM --all-reduce--> +h
+
+Column-parallel GEMMs (qkv, gate_up) shard N, row-parallel ones (o, down) shard K (see tp.py);
+one NCCL all-reduce follows each row-parallel GEMM.  Attention itself (RoPE, SDPA) is torch.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import ops, tp
+from .qlinear import NVFP4_reorder_quantize_w, NVFP4_reorder_quantize_x
+
+
+@dataclass
+class LlamaLayerConfig:
+    hidden: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 14336
+    rope_theta: float = 500000.0
+    eps: float = 1e-5
+    select_num: int = 128
+
+
+def random_layer_weights(cfg: LlamaLayerConfig, seed: int = 0, device="cpu", std: float = 0.02):
+    """Random-init weights of one layer, identical for every TP degree (one generator, full shapes)."""
+    g = torch.Generator().manual_seed(seed)
+
+    def w(n, k):
+        return (torch.randn(n, k, generator=g) * std).to(torch.bfloat16).to(device)
+
+    hd = cfg.n_heads * cfg.head_dim
+    kvd = cfg.n_kv_heads * cfg.head_dim
+    return {
+        "wq": w(hd, cfg.hidden), "wk": w(kvd, cfg.hidden), "wv": w(kvd, cfg.hidden), "wo": w(cfg.hidden, hd),
+        "w_gate": w(cfg.ffn, cfg.hidden), "w_up": w(cfg.ffn, cfg.hidden), "w_down": w(cfg.hidden, cfg.ffn),
+        "ln1": (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g)).to(torch.bfloat16).to(device),
+        "ln2": (1.0 + 0.1 * torch.randn(cfg.hidden, generator=g)).to(torch.bfloat16).to(device),
+    }
+
+
+def random_reorder_indices(cfg: LlamaLayerConfig, seed: int = 1):
+    """Synthetic stand-in for the calibrated channel orders (one per quantize site)."""
+    g = torch.Generator().manual_seed(seed)
+    hd = cfg.n_heads * cfg.head_dim
+    return {
+        "q": torch.randperm(cfg.hidden, generator=g).to(torch.int16),
+        "o": torch.randperm(hd, generator=g).to(torch.int16),
+        "up": torch.randperm(cfg.hidden, generator=g).to(torch.int16),
+        "down": torch.randperm(cfg.ffn, generator=g).to(torch.int16),
+    }
+
+
+def rope_tables(positions: torch.Tensor, head_dim: int, theta: float):
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=positions.device, dtype=torch.float32) / head_dim))
+    ang = positions.to(torch.float32)[:, None] * inv[None, :]
+    emb = torch.cat([ang, ang], dim=-1)
+    return emb.cos(), emb.sin()
+
+
+def apply_rope(t: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """t: [B, H, S, D]; rotate-half convention of the HF Llama the reference wraps."""
+    tf = t.float()
+    half = t.shape[-1] // 2
+    rot = torch.cat([-tf[..., half:], tf[..., :half]], dim=-1)
+    return (tf * cos + rot * sin).to(t.dtype)
+
+
+class PackedLinear:
+    """Packed NVFP4 weight + the channel order / KE its activation must be quantized with."""
+
+    def __init__(self, weight: torch.Tensor, index: torch.Tensor, select_num: int):
+        dev = weight.device
+        self.index = index.to(torch.int16).to(dev).contiguous()
+        self.select_num = select_num
+        self.W, self.SFW, self.scale = NVFP4_reorder_quantize_w(weight.contiguous(), self.index, select_num, mode=16)
+        self.scale = self.scale.reshape(())
+
+    def gemm(self, qx, sfx, scale_x=None):
+        if scale_x is None:
+            return ops.matmul_dev_alpha(qx, self.W, sfx, self.SFW, self.scale, None)
+        return ops.matmul_dev_alpha(qx, self.W, sfx, self.SFW, scale_x, self.scale)
+
+
+class QLlamaDecoderLayerTP(torch.nn.Module):
+    def __init__(self, cfg: LlamaLayerConfig, weights: dict, indices: dict, tp_rank: int = 0, tp_size: int = 1,
+                 group=None, device="cuda"):
+        super().__init__()
+        self.cfg, self.rank, self.tp, self.group = cfg, tp_rank, tp_size, group
+        if cfg.n_heads % tp_size or cfg.n_kv_heads % tp_size or cfg.ffn % tp_size:
+            raise ValueError("heads / kv heads / ffn must split over the tensor-parallel group")
+        dev = torch.device(device)
+        D = cfg.head_dim
+        self.h_local = cfg.n_heads // tp_size
+        self.kv_local = cfg.n_kv_heads // tp_size
+        q0, q1 = tp.shard_range(cfg.n_heads * D, tp_size, tp_rank)
+        k0, k1 = tp.shard_range(cfg.n_kv_heads * D, tp_size, tp_rank)
+        f0, f1 = tp.shard_range(cfg.ffn, tp_size, tp_rank)
+        to = lambda t: t.to(dev)
+        # column-parallel: rows of this rank's heads / ffn slice, global channel order
+        wqkv = torch.cat([to(weights["wq"][q0:q1]), to(weights["wk"][k0:k1]), to(weights["wv"][k0:k1])], dim=0)
+        self.qkv = PackedLinear(wqkv, indices["q"], cfg.select_num)
+        wgu = torch.cat([to(weights["w_gate"][f0:f1]), to(weights["w_up"][f0:f1])], dim=0)
+        self.gate_up = PackedLinear(wgu, indices["up"], cfg.select_num)
+        # row-parallel: K slice with its local order and local KE
+        self.o = PackedLinear(to(weights["wo"][:, q0:q1]).contiguous(), tp.local_reorder_index(indices["o"], q0, q1),
+                              tp.shard_select_num(cfg.select_num, tp_size, q1 - q0))
+        self.down = PackedLinear(to(weights["w_down"][:, f0:f1]).contiguous(),
+                                 tp.local_reorder_index(indices["down"], f0, f1),
+                                 tp.shard_select_num(cfg.select_num, tp_size, f1 - f0))
+        self.ln1, self.ln2 = to(weights["ln1"]).contiguous(), to(weights["ln2"]).contiguous()
+        self.f_local = f1 - f0
+
+    # ---- halves of the layer up to (and excluding) the all-reduce: usable for in-process emulation
+    @torch.no_grad()
+    def attn_partial(self, x2d: torch.Tensor, bsz: int, seq: int, positions: torch.Tensor) -> torch.Tensor:
+        cfg, D = self.cfg, self.cfg.head_dim
+        a, sfa = ops.rmsnorm_quantize_x(x2d, self.ln1, cfg.eps, self.qkv.index, self.qkv.select_num)
+        qkv = self.qkv.gemm(a, sfa)
+        nq, nk = self.h_local * D, self.kv_local * D
+        q = qkv[:, :nq].reshape(bsz, seq, self.h_local, D).transpose(1, 2)
+        k = qkv[:, nq:nq + nk].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
+        v = qkv[:, nq + nk:].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
+        cos, sin = rope_tables(positions, D, cfg.rope_theta)
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        rep = self.h_local // self.kv_local
+        if rep > 1:
+            k = k.repeat_interleave(rep, dim=1)
+            v = v.repeat_interleave(rep, dim=1)
+        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        attn = attn.transpose(1, 2).reshape(bsz * seq, nq).contiguous()
+        qa, sfo, so = NVFP4_reorder_quantize_x(attn, self.o.index, self.o.select_num, mode=16)
+        return self.o.gemm(qa, sfo, so)
+
+    @torch.no_grad()
+    def mlp_partial(self, h2d: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        a, sfa = ops.rmsnorm_quantize_x(h2d, self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
+        gu = self.gate_up.gemm(a, sfa)
+        act = (F.silu(gu[:, :self.f_local]) * gu[:, self.f_local:]).contiguous()
+        qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16)
+        return self.down.gemm(qd, sfd, sd)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
+        bsz, seq, hidden = x.shape
+        if positions is None:
+            positions = torch.arange(seq, device=x.device)
+        x2d = x.reshape(bsz * seq, hidden).contiguous()
+        h = x2d + tp.all_reduce_sum(self.attn_partial(x2d, bsz, seq, positions), self.group)
+        out = h + tp.all_reduce_sum(self.mlp_partial(h), self.group)
+        return out.reshape(bsz, seq, hidden)

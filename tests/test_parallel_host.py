@@ -1,0 +1,142 @@
+"""Multi-rank host logic on CPU (gloo, world_size 2): the K-shard bookkeeping of the row-parallel
+linears with an all-reduce, and the expert-parallel dispatch/combine with two all-to-alls.  The
+arithmetic inside is done by the CPU oracle, so these tests need no GPU."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from arcquant_b200 import tp
+from arcquant_b200.moe_block import ExpertParallelDispatcher, route_top_k
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _init(rank, world, port):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+
+def test_shard_bookkeeping():
+    idx = torch.randperm(1024, generator=torch.Generator().manual_seed(0)).to(torch.int16)
+    seen = []
+    for r in range(4):
+        a, b = tp.shard_range(1024, 4, r)
+        loc = tp.local_reorder_index(idx, a, b)
+        assert sorted(loc.tolist()) == list(range(256))                  # a permutation of the slice
+        glob = [int(v) for v in idx.tolist() if a <= v < b]
+        assert [v + a for v in loc.tolist()] == glob                     # global importance order kept
+        seen += [v + a for v in loc.tolist()]
+    assert sorted(seen) == list(range(1024))
+    assert tp.shard_select_num(128, 1, 4096) == 128
+    assert [tp.shard_select_num(128, t, 4096 // t) for t in (2, 4, 8)] == [64, 64, 64]
+    assert tp.shard_select_num(0, 4, 1024) == 0
+    assert (14336 // 8 + tp.shard_select_num(128, 8, 14336 // 8)) % 64 == 0
+    with pytest.raises(ValueError):
+        tp.shard_range(10, 4, 0)
+
+
+def _row_parallel_worker(rank, world, port, q):
+    from oracle import oracle as O
+
+    _init(rank, world, port)
+    try:
+        g = torch.Generator().manual_seed(0)                             # same tensors on every rank
+        K, N, M, KE = 512, 64, 24, 128
+        x = (torch.randn(M, K, generator=g) * 3).to(torch.bfloat16)
+        w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+        idx = torch.randperm(K, generator=g).to(torch.int16)
+        a, b = tp.shard_range(K, world, rank)
+        loc = tp.local_reorder_index(idx, a, b).numpy()
+        ke = tp.shard_select_num(KE, world, b - a)
+        qa, sfa = O.quantize_x(x[:, a:b].contiguous(), loc, ke)
+        qb, sfb = O.quantize_w(w[:, a:b].contiguous(), loc, ke)
+        part = torch.from_numpy(O.gemm_fast(qa, sfa, qb, sfb, 1.0))
+        total = tp.all_reduce_sum(part.clone())
+        # every rank can recompute all shards locally: the collective must equal their sum
+        ref = torch.zeros(M, N)
+        for r in range(world):
+            a2, b2 = tp.shard_range(K, world, r)
+            l2 = tp.local_reorder_index(idx, a2, b2).numpy()
+            k2 = tp.shard_select_num(KE, world, b2 - a2)
+            q1, s1 = O.quantize_x(x[:, a2:b2].contiguous(), l2, k2)
+            q2, s2 = O.quantize_w(w[:, a2:b2].contiguous(), l2, k2)
+            ref += torch.from_numpy(O.gemm_fast(q1, s1, q2, s2, 1.0))
+        full = x.float() @ w.float().T
+        ok = torch.allclose(total, ref, rtol=1e-6, atol=1e-6) and \
+            float((total - full).norm() / full.norm()) < 0.2
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def _moe_worker(rank, world, port, q):
+    _init(rank, world, port)
+    try:
+        E, H, T, k = 8, 32, 50 + 7 * rank, 2                              # ragged token counts per rank
+        g = torch.Generator().manual_seed(100 + rank)
+        x = torch.randn(T, H, generator=g)
+        router = torch.randn(E, H, generator=torch.Generator().manual_seed(1))
+        ids, w = route_top_k(x, router, k)
+        d = ExpertParallelDispatcher(E, rank, world)
+        rows, per_expert, state = d.dispatch(x, ids)
+        assert rows.shape[0] == sum(per_expert)
+        # fake expert e: y = x * (e + 1)
+        y = torch.empty_like(rows)
+        s = 0
+        for j, n in enumerate(per_expert):
+            e = rank * d.e_local + j
+            y[s:s + n] = rows[s:s + n] * (e + 1)
+            s += n
+        out = d.combine(y, w, state)
+        ref = torch.zeros_like(x)
+        for t in range(T):
+            for j in range(k):
+                ref[t] += x[t] * (int(ids[t, j]) + 1) * w[t, j]
+        q.put((rank, bool(torch.allclose(out, ref, rtol=1e-5, atol=1e-5))))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("worker", [_row_parallel_worker, _moe_worker])
+def test_two_rank_gloo(worker):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(results) == [(0, True), (1, True)]
+
+
+def test_single_rank_dispatch_matches_dense():
+    E, H, T, k = 4, 16, 33, 2
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(T, H, generator=g)
+    router = torch.randn(E, H, generator=g)
+    ids, w = route_top_k(x, router, k)
+    assert torch.allclose(w.sum(1), torch.ones(T))
+    d = ExpertParallelDispatcher(E)
+    rows, per_expert, state = d.dispatch(x, ids)
+    y = torch.empty_like(rows)
+    s = 0
+    for e, n in enumerate(per_expert):
+        y[s:s + n] = rows[s:s + n] * (e + 1)
+        s += n
+    out = d.combine(y, w, state)
+    ref = sum(x * (ids[:, j:j + 1] + 1) * w[:, j:j + 1] for j in range(k))
+    assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
