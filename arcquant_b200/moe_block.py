@@ -158,9 +158,10 @@ class QMixtralMoEBlockEP(torch.nn.Module):
         return out
 
     @torch.no_grad()
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """x: this rank's tokens [T, hidden] (bf16)."""
-        ids, w = route_top_k(x, self.router, self.cfg.top_k)
+    def forward(self, x: torch.Tensor, routing=None) -> torch.Tensor:
+        """x: this rank's tokens [T, hidden] (bf16).  routing: optional precomputed
+        (expert ids [T,k], weights [T,k]) - otherwise the block's own router decides."""
+        ids, w = routing if routing is not None else route_top_k(x, self.router, self.cfg.top_k)
         rows, per_expert, state = self.dispatcher.dispatch(x, ids)
         y = self.expert_forward(rows, per_expert)
         return self.dispatcher.combine(y, w, state)

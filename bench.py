@@ -35,6 +35,9 @@ KE = 128
 TOKENS = 32768
 EPS = 1e-5
 BYTES_PER_TOKEN = 2 * HIDDEN + (HIDDEN + KE) // 2 + (HIDDEN + KE) // 16      # 10568
+# dram__bytes_read + dram__bytes_write per token of the ncu capture under profiles/ (the output mostly
+# stays dirty in L2 while the kernel runs, so the write part is small): (134.27 + 7.53) MB / 16384 tokens
+TRAFFIC_PER_TOKEN_NCU = 8655
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
@@ -203,6 +206,98 @@ def gemm_extra(dev, hbm_peak, tf_peak):
     return res
 
 
+def layer_tokens_per_s(dev, world, rank, group, steps, batch=8, seq=2048):
+    """Llama-3-8B-shape decoder layer (hidden 4096, 32/8 heads, FFN 14336, all seven linears
+    ARC-NVFP4 with select_num 128), tensor-parallel over `world` ranks, prefill of batch x seq tokens."""
+    import torch
+
+    from arcquant_b200 import synth
+    from arcquant_b200.llama_layer import (LlamaLayerConfig, QLlamaDecoderLayerTP, random_layer_weights,
+                                           random_reorder_indices)
+
+    cfg = LlamaLayerConfig()
+    layer = QLlamaDecoderLayerTP(cfg, random_layer_weights(cfg, 0), random_reorder_indices(cfg, 1), tp_rank=rank,
+                                 tp_size=world, group=group, device=dev)
+    out = synth.outlier_channels(cfg.hidden, 41, 1)
+    x = synth.activations(batch * seq, cfg.hidden, 7, out, device=dev).reshape(batch, seq, cfg.hidden)
+    pos = torch.arange(seq, device=dev)
+    for _ in range(3):
+        y = layer(x, pos)
+    torch.cuda.synchronize()
+    if group is not None or world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        y = layer(x, pos)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return batch * seq / (ms * 1e-3), ms
+
+
+def run_side_workload(args):
+    """--workload gemm / layer: one JSON line for that workload alone (profiling and tuning runs)."""
+    import torch
+
+    from arcquant_b200 import ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    hbm_peak, tf_peak, peak_kind = measured_peaks()
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "layer":
+        tps, ms = layer_tokens_per_s(dev, world, rank, None, args.steps)
+        if world > 1:
+            dist.destroy_process_group()
+        if rank == 0:
+            print(json.dumps({"metric": "llama3_8b_shape_tp_layer_throughput", "value": tps, "unit": "tokens/s",
+                              "n_gpus": world, "steps": args.steps, "ms_per_step": ms, "scaling": "strong",
+                              "config": {"workload": "llama-3-8b-shape decoder layer, batch 8 x seq 2048, ARC-NVFP4 "
+                                                     "linears, select_num 128", "parallelism": f"tp{world}"}}), flush=True)
+        return
+    m, n, kq = (int(v) for v in args.shape.split(","))
+    k_eff = kq + KE
+    g = torch.Generator(device=dev).manual_seed(m + n)
+    a = torch.randint(0, 256, (m, k_eff // 2), dtype=torch.uint8, device=dev, generator=g)
+    b = torch.randint(0, 256, (n, k_eff // 2), dtype=torch.uint8, device=dev, generator=g)
+    sfa = torch.randint(0x20, 0x41, (ops.sf_bytes(m, k_eff),), dtype=torch.uint8, device=dev, generator=g)
+    sfb = torch.randint(0x20, 0x41, (ops.sf_bytes(n, k_eff),), dtype=torch.uint8, device=dev, generator=g)
+    for _ in range(max(args.warmup, 3)):
+        c = ops.matmul(a, b, sfa, sfb, 1.0)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        c = ops.matmul(a, b, sfa, sfb, 1.0)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    tf = 2.0 * m * n * k_eff / (ms * 1e-3) / 1e12
+    err = ops.gemm_poll_error()
+    if rank == 0:
+        print(json.dumps({"metric": "arc_nvfp4_gemm_throughput", "value": tf, "unit": "TFLOP/s", "n_gpus": 1,
+                          "steps": args.steps, "ms_per_step": ms, "device_wait_error": err,
+                          "config": {"workload": f"block-scaled NVFP4 GEMM M {m} N {n} K_eff {k_eff}"},
+                          "roofline": {"bound": "tensor", "achieved": tf, "peak": 4 * tf_peak, "unit": "TFLOP/s",
+                                       "frac": tf / (4 * tf_peak), "peak_kind": f"4 x {peak_kind} bf16 cuBLAS peak",
+                                       "frac_of_nominal_9000": tf / 9000.0},
+                          "gpu_launches": args.steps}), flush=True)
+
+
 def run_ours(args):
     import torch
 
@@ -226,9 +321,13 @@ def run_ours(args):
     import agemm
 
     hbm_peak, tf_peak, peak_kind = measured_peaks()
-    x, gamma, idx = make_inputs(dev, TOKENS, seed=2 + rank)
+    tokens = args.tokens
+    plain = args.workload == "quantize_plain"
+    x, gamma, idx = make_inputs(dev, tokens, seed=2 + rank)
 
     def step():
+        if plain:
+            return ops.reorder_quantize_x(x, idx, KE)
         return ops.rmsnorm_quantize_x(x, gamma, EPS, idx, KE)
 
     for _ in range(max(args.warmup, 3)):
@@ -244,7 +343,7 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     # keep the device busy long enough for the clock sampler to see it under load
-    t_end = time.time() + 0.6
+    t_end = time.time() + (0.0 if args.lean else 0.6)
     while time.time() < t_end:
         for _ in range(20):
             step()
@@ -264,7 +363,7 @@ def run_ours(args):
         ms_total = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
     ms_step = ms_total / args.steps
-    value = world * TOKENS * BYTES_PER_TOKEN / (ms_step * 1e-3) / 1e9
+    value = world * tokens * BYTES_PER_TOKEN / (ms_step * 1e-3) / 1e9
 
     # per-launch duration of the dominant kernel, measured live on its stream
     lat = []
@@ -276,11 +375,24 @@ def run_ours(args):
         torch.cuda.synchronize()
         lat.append(a0.elapsed_time(a1))
     launch_ms = sum(lat) / len(lat)
-    algo_bytes = TOKENS * BYTES_PER_TOKEN + 4 * HIDDEN
+    algo_bytes = tokens * BYTES_PER_TOKEN + (2 if plain else 4) * HIDDEN
     achieved = algo_bytes / (launch_ms * 1e-3) / 1e9
 
+    if args.lean:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        if rank == 0:
+            print(json.dumps({"metric": "arc_nvfp4_quantize_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world,
+                              "steps": args.steps, "ms_per_step": ms_step, "lean": True,
+                              "config": {"workload": args.workload, "tokens_per_gpu": tokens},
+                              "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                                           "frac": achieved / hbm_peak, "launch_ms": launch_ms},
+                              "gpu_launches": args.steps}), flush=True)
+        return
+
     # end to end through the reference-facing operator with host buffers
-    hx = torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    hx = torch.empty((tokens, HIDDEN), dtype=torch.bfloat16).pin_memory()
     hx.copy_(x.cpu())
     hq = torch.empty(q.shape, dtype=torch.uint8).pin_memory()
     hsf = torch.empty(sf.shape, dtype=torch.uint8).pin_memory()
@@ -288,7 +400,7 @@ def run_ours(args):
 
     def e2e_step():
         dx.copy_(hx, non_blocking=True)
-        a, s = agemm.rmsnorm_quantize_x(dx, gamma, EPS, idx, KE)
+        a, s = agemm.reorder_quantize_x(dx, idx, KE) if plain else agemm.rmsnorm_quantize_x(dx, gamma, EPS, idx, KE)
         hq.copy_(a, non_blocking=True)
         hsf.copy_(s, non_blocking=True)
 
@@ -305,15 +417,22 @@ def run_ours(args):
         t = torch.tensor([e2e_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-    e2e_val = world * TOKENS * BYTES_PER_TOKEN / e2e_s / 1e9
+    e2e_val = world * tokens * BYTES_PER_TOKEN / e2e_s / 1e9
 
-    extra = None
+    extra = {}
     cpu = None
+    # the third quantity the contract names: Llama-3-8B-shape decoder layer, tensor-parallel over the ranks
+    try:
+        tps, lms = layer_tokens_per_s(dev, world, rank, None, steps=5)
+        extra["llama_layer"] = {"tokens_per_s": tps, "ms": lms, "parallelism": f"tp{world}", "tokens": 8 * 2048,
+                                "scaling": "strong"}
+    except Exception as exc:  # the headline must survive a failure of the side measurements
+        extra["llama_layer_error"] = repr(exc)[:200]
     if rank == 0:
         try:
-            extra = {"gemm": gemm_extra(dev, hbm_peak, tf_peak)}
-        except Exception as exc:  # the headline must survive a failure of the side measurements
-            extra = {"gemm_error": repr(exc)[:200]}
+            extra["gemm"] = gemm_extra(dev, hbm_peak, tf_peak)
+        except Exception as exc:
+            extra["gemm_error"] = repr(exc)[:200]
         if world == 1:
             gbs, dt, threads = cpu_arm(8192, 5, 1)
             cpu = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
@@ -326,14 +445,17 @@ def run_ours(args):
     if rank != 0:
         return
     line = {
-        "metric": "arc_nvfp4_rmsnorm_quantize_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world,
+        "metric": "arc_nvfp4_rmsnorm_quantize_bandwidth" if not plain else "arc_nvfp4_reorder_quantize_bandwidth",
+        "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"fused rmsnorm+reorder+nvfp4+arc quantize, hidden {HIDDEN}, KE {KE}, "
-                               f"{TOKENS} tokens per GPU", "tokens_per_gpu": TOKENS, "hidden": HIDDEN, "select_num": KE,
+        "config": {"workload": f"{'reorder' if plain else 'fused rmsnorm+reorder'}+nvfp4+arc quantize, hidden {HIDDEN}, "
+                               f"KE {KE}, {tokens} tokens per GPU", "tokens_per_gpu": tokens, "hidden": HIDDEN,
+                   "select_num": KE,
                    "l2": "step touches 346 MB > 126 MB L2, no flush needed", "parallelism": f"tokens sharded x{world}"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "arcq_quantize_kernel<2,2,RMS>",
+                     "traffic": TRAFFIC_PER_TOKEN_NCU * tokens, "traffic_source": "ncu capture of a 16384-token launch "
+                     "(profiles/), scaled by tokens", "peak_kind": peak_kind, "kernel": "arcq_quantize_kernel<2,2,RMS>",
                      "launch_ms": launch_ms, "algorithmic_bytes_per_launch": algo_bytes},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": int(hx.numel() * 2),
@@ -351,9 +473,19 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="quantize", choices=["quantize", "quantize_plain", "gemm", "layer"],
+                    help="quantize (default, the headline): fused RMSNorm+reorder+NVFP4+ARC; quantize_plain: "
+                         "without RMSNorm; gemm: one block-scaled GEMM shape; layer: Llama-3-8B-shape decoder layer")
+    ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per GPU for the quantize workloads")
+    ap.add_argument("--shape", default="4096,6144,4096", help="M,N,KQ of --workload gemm (K_eff = KQ+128)")
+    ap.add_argument("--lean", action="store_true",
+                    help="only the timed kernel loop: no e2e arm, no CPU baseline, no side measurements "
+                         "(what the ncu captures under profiles/ run)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload in ("gemm", "layer"):
+        run_side_workload(args)
     else:
         run_ours(args)
 

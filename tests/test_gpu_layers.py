@@ -59,6 +59,32 @@ def _reference_layer(cfg, W, I, x, positions):
     return out.reshape(B, S, H)
 
 
+def _fp32_layer(cfg, W, x, positions):
+    """The same layer without any quantization, fp32 on the GPU."""
+    from arcquant_b200.llama_layer import apply_rope, rope_tables
+
+    g = lambda k: W[k].cuda().float()
+    B, S, H = x.shape
+    D = cfg.head_dim
+    xf = x.float().reshape(B * S, H)
+
+    def rms(t, w):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + cfg.eps) * w
+
+    n = rms(xf, g("ln1"))
+    q = (n @ g("wq").T).reshape(B, S, cfg.n_heads, D).transpose(1, 2)
+    k = (n @ g("wk").T).reshape(B, S, cfg.n_kv_heads, D).transpose(1, 2)
+    v = (n @ g("wv").T).reshape(B, S, cfg.n_kv_heads, D).transpose(1, 2)
+    cos, sin = rope_tables(positions, D, cfg.rope_theta)
+    q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+    rep = cfg.n_heads // cfg.n_kv_heads
+    a = F.scaled_dot_product_attention(q, k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1), is_causal=True)
+    h = xf + a.transpose(1, 2).reshape(B * S, -1) @ g("wo").T
+    n2 = rms(h, g("ln2"))
+    out = h + (F.silu(n2 @ g("w_gate").T) * (n2 @ g("w_up").T)) @ g("w_down").T
+    return out.reshape(B, S, H)
+
+
 def _rel(a, b):
     a, b = a.float(), b.float()
     return float((a - b).norm() / b.norm())
@@ -97,8 +123,15 @@ def test_tensor_parallel_emulated_in_one_process(tp_size):
     ranks = [QLlamaDecoderLayerTP(cfg, W, I, tp_rank=r, tp_size=tp_size) for r in range(tp_size)]
     x2 = x.reshape(64, cfg.hidden)
     h = x2 + sum(r.attn_partial(x2, 1, 64, pos).float() for r in ranks).to(torch.bfloat16)
-    y = h + sum(r.mlp_partial(h).float() for r in ranks).to(torch.bfloat16)
-    assert _rel(y.reshape(1, 64, -1), full) < 3e-2
+    y = (h + sum(r.mlp_partial(h).float() for r in ranks).to(torch.bfloat16)).reshape(1, 64, -1)
+    # Sharding K changes which channels share a 16-group and which residuals are kept, so the
+    # sharded result is a different - equally valid - quantization: judge both against the
+    # unquantized fp32 layer.
+    exact = _fp32_layer(cfg, W, x, pos)
+    e_full, e_tp = _rel(full, exact), _rel(y, exact)
+    assert e_full < 0.08
+    assert e_tp < 1.3 * e_full + 0.01
+    assert _rel(y, full) < 0.1
     # shards really are shards
     assert ranks[0].qkv.W.shape[0] == (cfg.n_heads + 2 * cfg.n_kv_heads) * cfg.head_dim // tp_size
     assert ranks[0].o.W.shape[1] * 2 == cfg.n_heads * cfg.head_dim // tp_size + ranks[0].o.select_num
@@ -111,9 +144,12 @@ def test_moe_block_matches_cpu_restatement_and_expert_parallel_emulation():
     W = random_moe_weights(cfg, 0)
     x = synth.activations(96, cfg.hidden, 5, synth.outlier_channels(cfg.hidden, 10, 3))
     block = QMixtralMoEBlockEP(cfg, W)
-    y = block(x.cuda()).cpu()
-    # CPU restatement with the reference block's semantics (per-expert loop, per-expert global scales)
+    # one routing decision for both sides: near-tied router logits may round differently on the two
+    # devices, and a flipped expert choice is not what this test is about
     ids, w = route_top_k(x, W["router"], cfg.top_k)
+    y = block(x.cuda(), routing=(ids.cuda(), w.cuda())).cpu()
+    assert block(x.cuda()).shape == y.shape            # the block's own router runs too
+    # CPU restatement with the reference block's semantics (per-expert loop, per-expert global scales)
     ref = torch.zeros(96, cfg.hidden)
     for e in range(cfg.n_experts):
         tok, slot = torch.where(ids == e)
