@@ -69,6 +69,7 @@ struct GemmParams {
   int natoms;         // ceil((K_eff/16)/4): scale atoms per 128-row tile
   int tiles_m, tiles_n;
   int sfb_tiles;      // ceil(N/128): 128-row scale tiles of B that exist
+  int dbg;            // timing experiments only (ARCQ_GEMM_DBG): 1 = skip scale copies, 2 = skip MMAs
 };
 
 // ----------------------------------------------------------------------------- PTX wrappers
@@ -282,6 +283,7 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint32_t sfa_s = b_s + C::B_BYTES, sfb_s = sfa_s + C::SFA_BYTES;
           const uint32_t t_sfa = tmem_sf + (it & 1u) * C::SF_COLS;
           const uint32_t t_sfb = t_sfa + KSTEPS * 4;
+          if (!(p.dbg & 1))
           for (int k = 0; k < nk; ++k) {
             tc_cp_sf(t_sfa + k * 4, smem_desc(sfa_s + k * ATOM, 128, LAYOUT_NONE));
 #pragma unroll
@@ -289,6 +291,7 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               tc_cp_sf(t_sfb + k * 4 * C::NB + a * 4,
                        smem_desc(sfb_s + a * (KSTEPS * ATOM) + k * ATOM, 128, LAYOUT_NONE));
           }
+          if (!(p.dbg & 2))
           for (int k = 0; k < nk; ++k) {
             const uint64_t adesc = smem_desc(a_s + k * 32, 1024, LAYOUT_SW128);
             const uint64_t bdesc = smem_desc(b_s + k * 32, 1024, LAYOUT_SW128);
@@ -322,7 +325,7 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
         tc_wait_ld();
         const int col = tn * BN + c0;
-        if (row < p.M && col < p.N) {
+        if (row < p.M && col < p.N && !(p.dbg & 4)) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             if (col + v * 8 < p.N) {   // N is a multiple of 8: whole 16-byte pieces are in or out
@@ -348,6 +351,307 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ----------------------------------------------------------------------------- 2-CTA kernel
+//
+// Same dataflow on a pair of SMs (cluster of two CTAs, cta_group::2): the pair owns a 256 x 256
+// output tile.  Each CTA loads its own 128 rows of A, its own 128 rows of B (half of N), its own
+// scale atoms of A and all scale atoms of B; the even CTA (leader) issues one
+// tcgen05.mma.cta_group::2 (M256 x N256 x K64) per K step, which reads A from both CTAs' shared
+// memory, the two halves of B likewise, and accumulates 128 rows x 256 columns in each CTA's TMEM.
+// Per SM this is 9.5 KB of operands per K step instead of 13.5 KB, and the smaller stage
+// (38 KB) lets five stages fit.
+//
+// Scale factors do not go through tcgen05.cp here: measured on this kernel, the twelve copies of
+// a stage execute strictly in sequence with its MMAs in the tensor pipe and cost as much as the
+// MMAs themselves.  Instead four "scale" warps per CTA (one per TMEM lane quadrant) read the
+// stage's atoms from shared memory and write them to TMEM with tcgen05.st, off the tensor pipe,
+// one stage ahead of the MMAs; each stage owns its own 48 TMEM columns.
+//
+// Synchronisation: A/B loads of either CTA complete on the LEADER's "full" barrier
+// (.cta_group::2 form; the barrier address is the CTA-local one with the pair's rank bit cleared);
+// scale loads complete on a CTA-local barrier; the scale warps of both CTAs arrive on the leader's
+// "scales ready" barrier; tcgen05.commit with a two-CTA mask releases the stage in both CTAs and
+// publishes the accumulator to both epilogues; the epilogue warps of both CTAs arrive on the
+// leader's "accumulator free" barrier.  No load uses cluster multicast.
+
+constexpr int C2_STAGES = 5;
+constexpr int C2_THREADS = 320;                     // producer, MMA, 4 epilogue, 4 scale warps
+constexpr int C2_A_BYTES = 128 * BK_BYTES;          // 16 KB
+constexpr int C2_B_BYTES = 128 * BK_BYTES;          // 16 KB: this CTA's half of the 256 B rows
+constexpr int C2_SFA_BYTES = KSTEPS * ATOM;         // 2 KB
+constexpr int C2_SFB_BYTES = 2 * KSTEPS * ATOM;     // 4 KB: both 128-row scale tiles of B
+constexpr int C2_STAGE_BYTES = C2_A_BYTES + C2_B_BYTES + C2_SFA_BYTES + C2_SFB_BYTES;   // 38 KB
+constexpr int C2_SF_COLS = KSTEPS * 4 + KSTEPS * 8;  // 48 TMEM columns of scales per stage
+constexpr int C2_TMEM_COLS = 512;                    // 256 accumulator + 5 x 48 scale columns
+constexpr int C2_SMEM_BYTES = 1024 + C2_STAGES * C2_STAGE_BYTES + 256;
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;      // clears the pair-rank bit of a shared address
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Tiled TMA load whose completion is counted on the leader CTA's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {   // arrives on `bar` in both CTAs of the pair
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t tsfa, uint32_t tsfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%4], [%5], p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tsfa), "r"(tsfb), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {   // remote arrive on the leader's barrier
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & PEER_BIT_MASK) : "memory");
+}
+// 32 lanes x 16 columns of 32 bits, registers -> this warp's TMEM lane quadrant.
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+struct Gemm2Params {
+  __nv_bfloat16* c;
+  const float* alpha_a;
+  const float* alpha_b;
+  float alpha;
+  int M, N;
+  int ksteps_total;   // K_eff / 64
+  int natoms;         // scale atoms per 128-row tile
+  int tiles_m, tiles_n;   // 256 x 256 tiles
+  int dbg;                // timing experiments only (ARCQ_GEMM_DBG)
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C2_THREADS, 1)
+arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                  const Gemm2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar_base = base + C2_STAGES * C2_STAGE_BYTES;
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(base_ptr + C2_STAGES * C2_STAGE_BYTES + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 1);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };                       // A/B landed (leader's is used)
+  auto empty_bar = [&](int s) { return bar_base + 8u * (C2_STAGES + s); };        // stage reusable
+  auto sf_full_bar = [&](int s) { return bar_base + 8u * (2 * C2_STAGES + s); };  // this CTA's scale atoms landed
+  auto sf_ready_bar = [&](int s) { return bar_base + 8u * (3 * C2_STAGES + s); }; // scales in TMEM (leader's is used)
+  const uint32_t tmem_full_bar = bar_base + 8u * (4 * C2_STAGES);
+  const uint32_t tmem_empty_bar = tmem_full_bar + 8u;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();        // 0 = leader (issues the MMAs), 1 = peer
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C2_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(sf_full_bar(s), 1);
+      mbar_init(sf_ready_bar(s), 8);              // four scale warps in each of the two CTAs
+    }
+    mbar_init(tmem_full_bar, 1);
+    mbar_init(tmem_empty_bar, 8);                 // four epilogue warps in each of the two CTAs
+    misc[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)misc)),
+                 "r"((uint32_t)C2_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                             // both CTAs' barriers exist before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = misc[0];
+  const uint32_t tmem_sf = tmem_base + 256;       // stage s: scale columns [256 + 48 s, 256 + 48 s + 48)
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int kstages = (p.ksteps_total + KSTEPS - 1) / KSTEPS;
+  constexpr uint32_t AB_TX = 2u * (C2_A_BYTES + C2_B_BYTES);   // A/B bytes both CTAs deliver per stage
+  constexpr uint32_t SF_TX = C2_SFA_BYTES + C2_SFB_BYTES;      // scale bytes of one CTA per stage
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        const int row_a = tm * 256 + (int)rank * 128;        // this CTA's rows of A (and of the output)
+        const int row_b = tn * 256 + (int)rank * 128;        // this CTA's rows of B (half of the N tile)
+        const int sfa_tile = tm * 2 + (int)rank;             // 128-row scale tiles
+        const int sfb_tile = tn * 2;
+        for (int ks = 0; ks < kstages; ++ks, ++it) {
+          const int s = it % C2_STAGES;
+          const uint32_t ph = (it / C2_STAGES) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t st = base + s * C2_STAGE_BYTES;
+          const uint32_t lbar = full_bar(s) & PEER_BIT_MASK;
+          if (rank == 0) mbar_expect_tx(full_bar(s), AB_TX);
+          mbar_expect_tx(sf_full_bar(s), SF_TX);
+          // scale atoms first (the scale warps work one hop ahead of the MMAs): rows of the map are
+          // atoms (128 words each); one box = the four K atoms of this stage
+          tma_load_2d(st + C2_A_BYTES + C2_B_BYTES, &map_sfa, sf_full_bar(s), 0, sfa_tile * p.natoms + ks * KSTEPS);
+          tma_load_2d(st + C2_A_BYTES + C2_B_BYTES + C2_SFA_BYTES, &map_sfb, sf_full_bar(s), 0,
+                      sfb_tile * p.natoms + ks * KSTEPS);
+          tma_load_2d(st + C2_A_BYTES + C2_B_BYTES + C2_SFA_BYTES + KSTEPS * ATOM, &map_sfb, sf_full_bar(s), 0,
+                      (sfb_tile + 1) * p.natoms + ks * KSTEPS);
+          tma_load_2d_pair(st, &map_a, lbar, ks * BK_BYTES, row_a);
+          tma_load_2d_pair(st + C2_A_BYTES, &map_b, lbar, ks * BK_BYTES, row_b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tile_it) {
+        if (!mbar_wait(tmem_empty_bar, (tile_it & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        for (int ks = 0; ks < kstages; ++ks, ++it) {
+          const int s = it % C2_STAGES;
+          const uint32_t ph = (it / C2_STAGES) & 1u;
+          if (!mbar_wait(sf_ready_bar(s), ph, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const int nk = min(KSTEPS, p.ksteps_total - ks * KSTEPS);
+          const uint32_t st = base + s * C2_STAGE_BYTES;
+          const uint32_t a_s = st, b_s = st + C2_A_BYTES;
+          const uint32_t t_sfa = tmem_sf + s * C2_SF_COLS;
+          const uint32_t t_sfb = t_sfa + KSTEPS * 4;
+          if (!(p.dbg & 2))
+          for (int k = 0; k < nk; ++k) {
+            const uint64_t adesc = smem_desc(a_s + k * 32, 1024, LAYOUT_SW128);
+            const uint64_t bdesc = smem_desc(b_s + k * 32, 1024, LAYOUT_SW128);
+            tc_mma_nvf4_pair(tmem_base, adesc, bdesc, idesc, t_sfa + k * 4, t_sfb + k * 8, (ks | k) ? 1u : 0u);
+          }
+          tc_commit_pair(empty_bar(s));
+        }
+        if (ok) tc_commit_pair(tmem_full_bar);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int quad = warp & 3;
+    float alpha = p.alpha;
+    if (p.alpha_a) alpha *= __ldg(p.alpha_a);
+    if (p.alpha_b) alpha *= __ldg(p.alpha_b);
+    uint32_t tile_it = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tile_it) {
+      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      ok = mbar_wait(tmem_full_bar, tile_it & 1u, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = tm * 256 + (int)rank * 128 + quad * 32 + lane;
+      __nv_bfloat16* crow = p.c + (size_t)row * p.N;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 256; c0 += 32) {
+        uint32_t r[32];
+        tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
+        tc_wait_ld();
+        const int col = tn * 256 + c0;
+        if (row < p.M && col < p.N && !(p.dbg & 4)) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col + v * 8 < p.N) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * alpha, __uint_as_float(r[v * 8 + 1]) * alpha);
+              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * alpha, __uint_as_float(r[v * 8 + 3]) * alpha);
+              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * alpha, __uint_as_float(r[v * 8 + 5]) * alpha);
+              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * alpha, __uint_as_float(r[v * 8 + 7]) * alpha);
+              *reinterpret_cast<uint4*>(crow + col + v * 8) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(tmem_empty_bar);
+    }
+  } else {
+    // ------------------------------------------------------------------ scale warps (both CTAs)
+    // Warp q writes TMEM lanes 32q..32q+31.  An atom is 32 rows x 16 bytes: lane l's 16 bytes are
+    // its four TMEM columns (rows l, l+32, l+64, l+96 of the 128-row tile, four K blocks each);
+    // every quadrant holds the same copy.
+    const int quad = warp & 3;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (int ks = 0; ks < kstages; ++ks, ++it) {
+        const int s = it % C2_STAGES;
+        const uint32_t ph = (it / C2_STAGES) & 1u;
+        ok = mbar_wait(sf_full_bar(s), ph, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint4* sf = reinterpret_cast<const uint4*>(base_ptr + s * C2_STAGE_BYTES + C2_A_BYTES + C2_B_BYTES);
+        const uint32_t taddr = tmem_sf + s * C2_SF_COLS + ((uint32_t)(quad * 32) << 16);
+        // TMEM columns: [SFA k0..k3 (4 each)] [SFB k0: tile0, tile1][k1: ...] ...
+        // shared:       [SFA k0..k3][SFB tile0 k0..k3][SFB tile1 k0..k3], 512 bytes each
+#pragma unroll
+        for (int part = 0; part < 3; ++part) {
+          uint32_t r[16];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            int atom;
+            if (part == 0) atom = j;                                        // SFA k = j
+            else {
+              const int k = (part - 1) * 2 + (j >> 1), t = j & 1;           // SFB k, tile t
+              atom = KSTEPS + t * KSTEPS + k;
+            }
+            const uint4 v = sf[atom * 32 + lane];
+            r[4 * j + 0] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
+          }
+          tc_st16(taddr + part * 16, r);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_leader(sf_ready_bar(s));
+      }
+    }
+  }
+
+  // Neither CTA may leave (or give back tensor memory) while the other can still touch it.
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C2_TMEM_COLS)
                  : "memory");
   }
 }
@@ -389,6 +693,56 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t kb
   return ARCQ_OK;
 }
 
+// Scale-factor buffer as a 2-D tensor of 32-bit words: one row per 512-byte atom; box = four atoms
+// (the four K steps of one stage of one 128-row tile).
+int make_sf_map(CUtensorMap* map, const void* ptr, int64_t total_atoms) {
+  EncodeTiledFn fn;
+  int rc = get_encode_fn(&fn);
+  if (rc != ARCQ_OK) return rc;
+  cuuint64_t dims[2] = {128, (cuuint64_t)total_atoms};
+  cuuint64_t strides[1] = {(cuuint64_t)ATOM};
+  cuuint32_t box[2] = {128, (cuuint32_t)KSTEPS};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  return ARCQ_OK;
+}
+
+int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M, int64_t N,
+                int64_t K_eff, const GemmParams& gp, int num_sms, cudaStream_t stream) {
+  Gemm2Params p;
+  p.c = gp.c;
+  p.alpha_a = gp.alpha_a;
+  p.alpha_b = gp.alpha_b;
+  p.alpha = gp.alpha;
+  p.M = gp.M;
+  p.N = gp.N;
+  p.ksteps_total = gp.ksteps_total;
+  p.natoms = gp.natoms;
+  p.tiles_m = (int)((M + 255) / 256);
+  p.tiles_n = (int)((N + 255) / 256);
+  p.dbg = gp.dbg;
+  CUtensorMap ma, mb, msa, msb;
+  int rc = make_operand_map(&ma, A, M, K_eff / 2, 128);
+  if (rc != ARCQ_OK) return rc;
+  rc = make_operand_map(&mb, B, N, K_eff / 2, 128);
+  if (rc != ARCQ_OK) return rc;
+  rc = make_sf_map(&msa, SFA, ((M + 127) / 128) * (int64_t)gp.natoms);
+  if (rc != ARCQ_OK) return rc;
+  rc = make_sf_map(&msb, SFB, ((N + 127) / 128) * (int64_t)gp.natoms);
+  if (rc != ARCQ_OK) return rc;
+  auto kern = arcq_gemm2_kernel;
+  ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C2_SMEM_BYTES));
+  long long tiles = (long long)p.tiles_m * p.tiles_n;
+  long long clusters = num_sms / 2;
+  if (clusters > tiles) clusters = tiles;
+  kern<<<(unsigned)(2 * clusters), C2_THREADS, C2_SMEM_BYTES, stream>>>(ma, mb, msa, msb, p);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
+
 template <int BN>
 int launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int num_sms, cudaStream_t stream) {
   using C = Cfg<BN>;
@@ -425,6 +779,8 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   p.tiles_m = (int)((M + BM - 1) / BM);
   p.tiles_n = 0;
   p.sfb_tiles = (int)((N + 127) / 128);
+  p.dbg = 0;
+  if (const char* e = getenv("ARCQ_GEMM_DBG")) p.dbg = atoi(e);
 
   // Widest tile that still gives every SM work; narrow tiles for skinny problems.  Partial tiles
   // are clipped by the TMA box (zero fill) and by the store guards.  ARCQ_GEMM_BN=32|64|128|256
@@ -435,6 +791,12 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
     int v = atoi(e);
     if (v == 64 || v == 128 || v == 256) bn = v;
   }
+
+  // Problems with enough 256 x 256 tiles to occupy at least half of the SM pairs run on CTA pairs
+  // (about 1.4x the throughput of the single-CTA kernel).  ARCQ_GEMM_PAIR=0/1 overrides the choice.
+  bool pair = (long long)((M + 255) / 256) * ((N + 255) / 256) >= di.num_sms / 4 && M > 128;
+  if (const char* e = getenv("ARCQ_GEMM_PAIR")) pair = atoi(e) != 0;
+  if (pair) return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream);
 
   CUtensorMap ma, mb;
   rc = make_operand_map(&ma, A, M, K_eff / 2, BM);
