@@ -50,6 +50,7 @@ struct QuantParams {
   int mode;       // 16 or 32 (placement of critical groups, residual flavour)
   int is_weight;  // residual slot = copy of the main codes
   float eps;
+  int dbg;        // timing experiments only (ARCQ_QUANT_DBG): 1 = no global loads, 2 = no quantize, 4 = no fill
 };
 
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
@@ -295,14 +296,17 @@ __device__ __forceinline__ uint32_t swz16(uint32_t j) { return j ^ ((j >> 3) & 1
 // Byte offset of channel ch's (row0,row1) word.
 __device__ __forceinline__ uint32_t word_offset(uint32_t ch) { return (swz16(ch >> 2) << 4) | ((ch & 3u) << 2); }
 
-// CPT: 16-byte chunks per thread per row; NBUF: shared row-pair buffers; RMS: fused RMSNorm;
-// RAWIDX: the offset table holds 16-bit channel numbers (rows wider than 16384 channels) instead of
-// 32-bit byte offsets.  MAXT / MINB: launch bounds.
-template <int CPT, int NBUF, bool RMS, bool RAWIDX, int MAXT, int MINB>
+// CPT: 16-byte chunks per thread per row; NBUF: shared buffers (2 = the next unit streams in while
+// the current one is quantized); PAIRS: row pairs per loop iteration ("unit") - two pairs halve the
+// per-row cost of the table reads, the barrier and the loop bookkeeping and double the independent
+// shared loads in flight; RMS: fused RMSNorm; RAWIDX: the offset table holds 16-bit channel numbers
+// (rows wider than 16384 channels) instead of 32-bit byte offsets.  MAXT / MINB: launch bounds.
+template <int CPT, int NBUF, int PAIRS, bool RMS, bool RAWIDX, int MAXT, int MINB>
 __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x, nt = blockDim.x;
-  const int KQ = p.KQ;
+  const int KQ = p.KQ, G = p.G, nchunks = p.nchunks;
+  const long long rows = p.rows, npairs = p.npairs;
 
   // shared layout: [scale tables 160 B][offsets][gain (RMS)][partial sums, rstd (RMS)][row-pair buffers]
   uint8_t* lutT = smem;
@@ -317,11 +321,11 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
   if (RMS) {
     cursor += (size_t)KQ * 4;
     psum = reinterpret_cast<float*>(smem + cursor);
-    cursor += (size_t)2 * nt * sizeof(float);
+    cursor += (size_t)2 * PAIRS * nt * sizeof(float);
     rstd_s = reinterpret_cast<float*>(smem + cursor);
     cursor += 16;
   }
-  uint32_t* bufs = reinterpret_cast<uint32_t*>(smem + cursor);
+  uint32_t* bufs = reinterpret_cast<uint32_t*>(smem + cursor);   // [NBUF][PAIRS][KQ] words
 
   for (int j = tid; j < 128; j += nt)
     lutT[j] = (uint8_t)make_scale_slow(__uint_as_float(((127u << 7) | (uint32_t)j) << 16)).byte;
@@ -332,140 +336,182 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
   for (int j = tid; j < KQ; j += nt) {
     int c = p.idx ? (int)p.idx[j] : j;
     const int g = j >> 4, i = j & 15;
-    const int slot = (((i >> 2) * p.G + g) << 2) | (i & 3);
+    const int slot = (((i >> 2) * G + g) << 2) | (i & 3);
     if (RAWIDX) offs16[j] = (uint16_t)c; else offs32[slot] = word_offset((uint32_t)c);
     if (RMS) gperm[slot] = __uint_as_float((uint32_t)p.gamma[c] << 16);
   }
   const ScaleLut lut{lutT, lutRB};
 
-  uint4 ra[CPT], rb[CPT];
+  uint4 ra[PAIRS][CPT], rb[PAIRS][CPT];
 
-  auto load_pair = [&](long long pair) {
-    const long long r0 = 2 * pair;
-    const bool has1 = (r0 + 1) < p.rows;
-    const uint4* x0 = reinterpret_cast<const uint4*>(p.x + r0 * (long long)KQ);
-    const uint4* x1 = reinterpret_cast<const uint4*>(p.x + (r0 + 1) * (long long)KQ);
+  auto load_unit = [&](long long unit) {
 #pragma unroll
-    for (int j = 0; j < CPT; ++j) {
-      int c = tid + j * nt;
-      if (c < p.nchunks) {
-        ra[j] = ldg_stream(x0 + c);
-        rb[j] = has1 ? ldg_stream(x1 + c) : make_uint4(0, 0, 0, 0);
-      }
-    }
-  };
-
-  auto store_pair = [&](uint32_t* buf) {
-    float2 ss = make_float2(0.f, 0.f);
+    for (int u = 0; u < PAIRS; ++u) {
+      const long long r0 = 2 * (unit * PAIRS + u);
+      const bool has0 = r0 < rows, has1 = (r0 + 1) < rows;
+      const uint4* x0 = reinterpret_cast<const uint4*>(p.x + r0 * (long long)KQ);
+      const uint4* x1 = reinterpret_cast<const uint4*>(p.x + (r0 + 1) * (long long)KQ);
 #pragma unroll
-    for (int j = 0; j < CPT; ++j) {
-      int c = tid + j * nt;
-      if (c < p.nchunks) {
-        uint4 lo, hi;  // words of channels 8c..8c+3 and 8c+4..8c+7: (row0[ch], row1[ch]) per word
-        lo.x = __byte_perm(ra[j].x, rb[j].x, 0x5410); lo.y = __byte_perm(ra[j].x, rb[j].x, 0x7632);
-        lo.z = __byte_perm(ra[j].y, rb[j].y, 0x5410); lo.w = __byte_perm(ra[j].y, rb[j].y, 0x7632);
-        hi.x = __byte_perm(ra[j].z, rb[j].z, 0x5410); hi.y = __byte_perm(ra[j].z, rb[j].z, 0x7632);
-        hi.z = __byte_perm(ra[j].w, rb[j].w, 0x5410); hi.w = __byte_perm(ra[j].w, rb[j].w, 0x7632);
-        // XOR-swizzled 16-byte units: the eight lanes of a 128-bit store wavefront hit distinct banks
-        uint4* b4 = reinterpret_cast<uint4*>(buf);
-        b4[swz16(2u * c)] = lo;
-        b4[swz16(2u * c + 1u)] = hi;
-        if (RMS) {
-          // reference thread t adds chunk t then chunk t+KQ/16, eight elements each, in order;
-          // the two rows ride in the two lanes of a packed FMA
-          const uint32_t ws[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float2 a = make_float2(bf16lo(ws[i]), bf16hi(ws[i]));
-            ss = __ffma2_rn(a, a, ss);
-          }
+      for (int j = 0; j < CPT; ++j) {
+        int c = tid + j * nt;
+        if (c < nchunks) {
+          ra[u][j] = (has0 && !(p.dbg & 1)) ? ldg_stream(x0 + c) : make_uint4(0, 0, 0, 0);
+          rb[u][j] = (has1 && !(p.dbg & 1)) ? ldg_stream(x1 + c) : make_uint4(0, 0, 0, 0);
         }
       }
     }
-    if (RMS) {
-      psum[tid] = ss.x;
-      psum[nt + tid] = ss.y;
+  };
+
+  auto store_unit = [&](uint32_t* buf) {
+#pragma unroll
+    for (int u = 0; u < PAIRS; ++u) {
+      float2 ss = make_float2(0.f, 0.f);
+      uint4* b4 = reinterpret_cast<uint4*>(buf + (size_t)u * KQ);
+#pragma unroll
+      for (int j = 0; j < CPT; ++j) {
+        int c = tid + j * nt;
+        if (c < nchunks) {
+          const uint4 a = ra[u][j], b = rb[u][j];
+          uint4 lo, hi;  // words of channels 8c..8c+3 and 8c+4..8c+7: (row0[ch], row1[ch]) per word
+          lo.x = __byte_perm(a.x, b.x, 0x5410); lo.y = __byte_perm(a.x, b.x, 0x7632);
+          lo.z = __byte_perm(a.y, b.y, 0x5410); lo.w = __byte_perm(a.y, b.y, 0x7632);
+          hi.x = __byte_perm(a.z, b.z, 0x5410); hi.y = __byte_perm(a.z, b.z, 0x7632);
+          hi.z = __byte_perm(a.w, b.w, 0x5410); hi.w = __byte_perm(a.w, b.w, 0x7632);
+          // XOR-swizzled 16-byte units: the eight lanes of a 128-bit store wavefront hit distinct banks
+          b4[swz16(2u * c)] = lo;
+          b4[swz16(2u * c + 1u)] = hi;
+          if (RMS) {
+            // reference thread t adds chunk t then chunk t+KQ/16, eight elements each, in order;
+            // the two rows ride in the two lanes of a packed FMA
+            const uint32_t ws[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float2 v = make_float2(bf16lo(ws[i]), bf16hi(ws[i]));
+              ss = __ffma2_rn(v, v, ss);
+            }
+          }
+        }
+      }
+      if (RMS) {
+        psum[(2 * u) * nt + tid] = ss.x;
+        psum[(2 * u + 1) * nt + tid] = ss.y;
+      }
     }
   };
 
-  long long pair = blockIdx.x;
-  if (pair < p.npairs) { load_pair(pair); store_pair(bufs); }
+  // The register prefetch above is scheduled late by the assembler (it holds 16+ registers), so its
+  // latency is partly exposed; pulling the rows of the unit after next into L2 ahead of time turns
+  // that exposed latency from an HBM access into an L2 hit.
+  auto prefetch_unit_l2 = [&](long long unit) {
+    if (tid < 2 * PAIRS) {
+      const long long r = 2 * unit * PAIRS + tid;
+      if (r < rows)
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.x + r * (long long)KQ), "r"(KQ * 2)
+                     : "memory");
+    }
+  };
+
+  const long long nunits = (npairs + PAIRS - 1) / PAIRS;
+  long long unit = blockIdx.x;
+  if (unit < nunits) { load_unit(unit); store_unit(bufs); }
+  if (unit + gridDim.x < nunits) prefetch_unit_l2(unit + gridDim.x);
   __syncthreads();
 
   int cur = 0;
   const size_t row_bytes = (size_t)(KQ + p.KE) / 2;
-  for (; pair < p.npairs; pair += gridDim.x) {
-    const long long nxt = pair + gridDim.x;
-    const bool more = nxt < p.npairs;
-    if (NBUF == 2 && more) load_pair(nxt);
+  const size_t buf_words = (size_t)PAIRS * KQ;
+  for (; unit < nunits; unit += gridDim.x) {
+    const long long nxt = unit + gridDim.x;
+    const bool more = nxt < nunits;
+    if (NBUF == 2 && more) load_unit(nxt);
+    if (nxt + gridDim.x < nunits) prefetch_unit_l2(nxt + gridDim.x);
 
-    float2 rstd = make_float2(1.f, 1.f);
+    float2 rstd[PAIRS];
     if (RMS) {
       const int warp = tid >> 5, lane = tid & 31;
-      if (warp < 2) {
+      if (warp < 2 * PAIRS) {
         float ss = rms_tree(psum + warp * nt, nt, lane);
         if (lane == 0) rstd_s[warp] = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)KQ), p.eps));
       }
       __syncthreads();
-      rstd = make_float2(rstd_s[0], rstd_s[1]);
+#pragma unroll
+      for (int u = 0; u < PAIRS; ++u) rstd[u] = make_float2(rstd_s[2 * u], rstd_s[2 * u + 1]);
     }
 
-    const uint8_t* buf = reinterpret_cast<const uint8_t*>(bufs + (size_t)cur * KQ);
-    const long long r0 = 2 * pair, r1 = r0 + 1;
-    const bool has1 = r1 < p.rows;
-    uint8_t* q0 = p.q + (size_t)r0 * row_bytes;
-    uint8_t* q1 = has1 ? q0 + row_bytes : q0;          // odd last row: alias, row 0 is stored last
-    uint8_t* sf0 = p.sf + sf_row_base(r0, p.natoms);
-    uint8_t* sf1 = has1 ? p.sf + sf_row_base(r1, p.natoms) : sf0;
+    const uint8_t* buf = reinterpret_cast<const uint8_t*>(bufs + (size_t)cur * buf_words);
+    uint8_t *q0[PAIRS], *q1[PAIRS], *sf0[PAIRS], *sf1[PAIRS];
+    bool live[PAIRS];
+#pragma unroll
+    for (int u = 0; u < PAIRS; ++u) {
+      const long long r0 = 2 * (unit * PAIRS + u), r1 = r0 + 1;
+      live[u] = r0 < rows;
+      const bool has1 = r1 < rows;
+      q0[u] = p.q + (size_t)r0 * row_bytes;
+      q1[u] = has1 ? q0[u] + row_bytes : q0[u];          // odd last row: alias, row 0 is stored last
+      sf0[u] = p.sf + sf_row_base(r0, p.natoms);
+      sf1[u] = has1 ? p.sf + sf_row_base(r1, p.natoms) : sf0[u];
+    }
 
-    for (int g = tid; g < p.G; g += nt) {
-      uint32_t w[16];
+    for (int g = tid; g < G; g += nt) {
+      uint32_t w[PAIRS][16];
       if (RAWIDX) {
         const uint4* op = reinterpret_cast<const uint4*>(offs16 + 16 * g);
         const uint4 o0 = op[0], o1 = op[1];
         const uint32_t ow[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          uint32_t ch = (i & 1) ? (ow[i >> 1] >> 16) : (ow[i >> 1] & 0xffffu);
-          w[i] = *reinterpret_cast<const uint32_t*>(buf + word_offset(ch));
+          const uint32_t ch = (i & 1) ? (ow[i >> 1] >> 16) : (ow[i >> 1] & 0xffffu);
+          const uint32_t o = word_offset(ch);
+#pragma unroll
+          for (int u = 0; u < PAIRS; ++u)
+            w[u][i] = *reinterpret_cast<const uint32_t*>(buf + (size_t)u * KQ * 4 + o);
         }
       } else {
         const uint4* op = reinterpret_cast<const uint4*>(offs32) + g;
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-          const uint4 o = op[v * p.G];
-          w[4 * v + 0] = *reinterpret_cast<const uint32_t*>(buf + o.x);
-          w[4 * v + 1] = *reinterpret_cast<const uint32_t*>(buf + o.y);
-          w[4 * v + 2] = *reinterpret_cast<const uint32_t*>(buf + o.z);
-          w[4 * v + 3] = *reinterpret_cast<const uint32_t*>(buf + o.w);
+          const uint4 o = op[v * G];
+#pragma unroll
+          for (int u = 0; u < PAIRS; ++u) {
+            const uint8_t* bu = buf + (size_t)u * KQ * 4;
+            w[u][4 * v + 0] = *reinterpret_cast<const uint32_t*>(bu + o.x);
+            w[u][4 * v + 1] = *reinterpret_cast<const uint32_t*>(bu + o.y);
+            w[u][4 * v + 2] = *reinterpret_cast<const uint32_t*>(bu + o.z);
+            w[u][4 * v + 3] = *reinterpret_cast<const uint32_t*>(bu + o.w);
+          }
         }
       }
       if (RMS) {
         const float4* gp = reinterpret_cast<const float4*>(gperm) + g;
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-          const float4 gm = gp[v * p.G];
+          const float4 gm = gp[v * G];
           const float gs[4] = {gm.x, gm.y, gm.z, gm.w};
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const int i = 4 * v + k;
-            // bf16 x bf16 is exact in fp32; then one rounding by rstd (both rows in one FMUL2), one to bf16
-            const float2 t = make_float2(__fmul_rn(bf16lo(w[i]), gs[k]), __fmul_rn(bf16hi(w[i]), gs[k]));
-            const float2 n = __fmul2_rn(t, rstd);
-            w[i] = pack_bf16x2_rn(n.x, n.y);
+#pragma unroll
+            for (int u = 0; u < PAIRS; ++u) {
+              // bf16 x bf16 is exact in fp32; then one rounding by rstd (both rows in one FMUL2), one to bf16
+              const float2 t = make_float2(__fmul_rn(bf16lo(w[u][i]), gs[k]), __fmul_rn(bf16hi(w[u][i]), gs[k]));
+              const float2 n = __fmul2_rn(t, rstd[u]);
+              w[u][i] = pack_bf16x2_rn(n.x, n.y);
+            }
           }
         }
       }
-      quantize_group_pair(w, g, p, lut, q0, q1, sf0, sf1);
+#pragma unroll
+      for (int u = 0; u < PAIRS; ++u)
+        if (live[u] && !(p.dbg & 2)) quantize_group_pair(w[u], g, p, lut, q0[u], q1[u], sf0[u], sf1[u]);
     }
 
     if (NBUF == 2) {
-      if (more) store_pair(bufs + (size_t)(cur ^ 1) * KQ);
+      if (more && !(p.dbg & 4)) store_unit(bufs + (size_t)(cur ^ 1) * buf_words);
       __syncthreads();
       cur ^= 1;
     } else {
       __syncthreads();
-      if (more) { load_pair(nxt); store_pair(bufs); }
+      if (more) { load_unit(nxt); store_unit(bufs); }
       __syncthreads();
     }
   }
@@ -490,15 +536,16 @@ __global__ void arcq_absmax_kernel(const uint4* __restrict__ x, long long nvec, 
   if ((threadIdx.x & 31) == 0) atomicMax(out, r << 16);
 }
 
-template <int CPT, int NBUF, bool RMS, bool RAWIDX, int MAXT, int MINB>
+template <int CPT, int NBUF, int PAIRS, bool RMS, bool RAWIDX, int MAXT, int MINB>
 int launch_variant(const QuantParams& p, int nt, size_t smem, const DeviceInfo& di, cudaStream_t stream) {
-  auto kern = arcq_quantize_kernel<CPT, NBUF, RMS, RAWIDX, MAXT, MINB>;
+  auto kern = arcq_quantize_kernel<CPT, NBUF, PAIRS, RMS, RAWIDX, MAXT, MINB>;
   ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int occ = 0;
   ARCQ_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, nt, smem));
   if (occ < 1) return ARCQ_ERR_UNSUPPORTED_K;
+  const long long nunits = (p.npairs + PAIRS - 1) / PAIRS;
   long long grid = (long long)di.num_sms * occ;
-  if (grid > p.npairs) grid = p.npairs;
+  if (grid > nunits) grid = nunits;
   kern<<<(unsigned)grid, nt, smem, stream>>>(p);
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
@@ -530,6 +577,8 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   p.mode = mode;
   p.is_weight = is_weight;
   p.eps = eps;
+  p.dbg = 0;
+  if (const char* e = getenv("ARCQ_QUANT_DBG")) p.dbg = atoi(e);
 
   const bool rms = gamma != nullptr;
   int nt, cpt;
@@ -545,29 +594,35 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   }
   const bool rawidx = KQ > 16384;
   const size_t table = 160 + (((size_t)KQ * (rawidx ? 2 : 4) + 15) & ~(size_t)15);
-  size_t smem = table + (rms ? (size_t)KQ * 4 + (size_t)2 * nt * sizeof(float) + 16 : 0) + (size_t)2 * KQ * 4;
+  auto smem_for = [&](int nbuf, int pairs) {
+    return table + (rms ? (size_t)KQ * 4 + (size_t)2 * pairs * nt * sizeof(float) + 16 : 0) +
+           (size_t)nbuf * pairs * KQ * 4;
+  };
+  size_t smem = smem_for(2, 1);
   if (cpt == 8 || rawidx || smem > (size_t)di.max_smem_optin) {
     // very wide rows: one buffer, loads not overlapped with the arithmetic
-    smem = table + (size_t)KQ * 4;
+    smem = smem_for(1, 1);
     if (rms || smem > (size_t)di.max_smem_optin) return ARCQ_ERR_UNSUPPORTED_K;
-    return rawidx ? launch_variant<8, 1, false, true, 512, 1>(p, nt, smem, di, stream)
-                  : launch_variant<8, 1, false, false, 512, 1>(p, nt, smem, di, stream);
+    return rawidx ? launch_variant<8, 1, 1, false, true, 512, 1>(p, nt, smem, di, stream)
+                  : launch_variant<8, 1, 1, false, false, 512, 1>(p, nt, smem, di, stream);
   }
-  if (nt <= 256) {
-    // narrow rows: several resident CTAs per SM keep enough loads in flight.  ARCQ_QUANT_MINB=2
-    // trades one resident CTA for a larger register budget (tuning knob).
-    static const int minb = [] { const char* e = getenv("ARCQ_QUANT_MINB"); return e ? atoi(e) : 3; }();
-    if (minb == 2) {
-      if (rms) return launch_variant<2, 2, true, false, 256, 2>(p, nt, smem, di, stream);
-      if (cpt == 2) return launch_variant<2, 2, false, false, 256, 2>(p, nt, smem, di, stream);
-    } else {
-      if (rms) return launch_variant<2, 2, true, false, 256, 3>(p, nt, smem, di, stream);
-      if (cpt == 2) return launch_variant<2, 2, false, false, 256, 3>(p, nt, smem, di, stream);
+  if (nt <= 256 && cpt == 2) {
+    // Narrow rows (the common case).  Default: one row pair per iteration, three resident CTAs per
+    // SM.  ARCQ_QUANT_PAIRS=2 selects two pairs per iteration with two resident CTAs and a
+    // 128-register budget (tuning knob; measured slower on B200: fewer warps to hide latency).
+    static const int pairs_env = [] { const char* e = getenv("ARCQ_QUANT_PAIRS"); return e ? atoi(e) : 1; }();
+    const bool two = pairs_env == 2 && p.npairs >= 4LL * di.num_sms;
+    if (two) {
+      smem = smem_for(2, 2);
+      if (rms) return launch_variant<2, 2, 2, true, false, 256, 2>(p, nt, smem, di, stream);
+      return launch_variant<2, 2, 2, false, false, 256, 2>(p, nt, smem, di, stream);
     }
+    if (rms) return launch_variant<2, 2, 1, true, false, 256, 3>(p, nt, smem, di, stream);
+    return launch_variant<2, 2, 1, false, false, 256, 3>(p, nt, smem, di, stream);
   }
-  if (rms) return launch_variant<2, 2, true, false, 512, 1>(p, nt, smem, di, stream);
-  if (cpt == 2) return launch_variant<2, 2, false, false, 512, 1>(p, nt, smem, di, stream);
-  return launch_variant<4, 2, false, false, 512, 1>(p, nt, smem, di, stream);
+  if (rms) return launch_variant<2, 2, 1, true, false, 512, 1>(p, nt, smem, di, stream);
+  if (cpt == 2) return launch_variant<2, 2, 1, false, false, 512, 1>(p, nt, smem, di, stream);
+  return launch_variant<4, 2, 1, false, false, 512, 1>(p, nt, smem, di, stream);
 }
 
 int launch_absmax(const void* x, int64_t n, float* out, int accumulate, cudaStream_t stream) {
