@@ -35,6 +35,8 @@ SIGNATURES = {
     "arcq_reorder_quantize_w": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
     "arcq_matmul_nvfp4": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp]),
     "arcq_matmul_nvfp4_dev_alpha": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "arcq_matmul_workspace_bytes": (C.c_size_t, [_i64, _i64, _i64]),
+    "arcq_matmul_nvfp4_ws": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
     "arcq_gemm_poll_error": (_i32, []),
     "arcq_absmax_bf16": (_i32, [_vp, _i64, _vp, _i32, _vp]),
 }

@@ -131,7 +131,7 @@ int arcq_matmul_nvfp4(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, co
                       int64_t N, int64_t K_eff, float alpha, void* C, void* stream) {
   int rc = check_gemm(A, B, SFA, SFB, M, N, K_eff, C);
   if (rc != ARCQ_OK || M == 0) return rc;
-  return launch_gemm(A, B, SFA, SFB, M, N, K_eff, alpha, nullptr, nullptr, C, (cudaStream_t)stream);
+  return launch_gemm(A, B, SFA, SFB, M, N, K_eff, alpha, nullptr, nullptr, C, nullptr, 0, (cudaStream_t)stream);
 }
 
 int arcq_matmul_nvfp4_dev_alpha(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
@@ -140,7 +140,22 @@ int arcq_matmul_nvfp4_dev_alpha(const uint8_t* A, const uint8_t* B, const uint8_
   int rc = check_gemm(A, B, SFA, SFB, M, N, K_eff, C);
   if (rc != ARCQ_OK || M == 0) return rc;
   if (!alpha_a) return ARCQ_ERR_NULL_POINTER;
-  return launch_gemm(A, B, SFA, SFB, M, N, K_eff, 1.0f, alpha_a, alpha_b, C, (cudaStream_t)stream);
+  return launch_gemm(A, B, SFA, SFB, M, N, K_eff, 1.0f, alpha_a, alpha_b, C, nullptr, 0, (cudaStream_t)stream);
+}
+
+size_t arcq_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K_eff) {
+  if (M <= 0 || N <= 0 || K_eff <= 0) return 0;
+  return gemm_workspace_bytes(M, N, K_eff);
+}
+
+int arcq_matmul_nvfp4_ws(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                         int64_t N, int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* C,
+                         void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_gemm(A, B, SFA, SFB, M, N, K_eff, C);
+  if (rc != ARCQ_OK || M == 0) return rc;
+  if (workspace != nullptr && !aligned16(workspace)) return ARCQ_ERR_ALIGNMENT;
+  return launch_gemm(A, B, SFA, SFB, M, N, K_eff, alpha, alpha_a, alpha_b, C, workspace, workspace_bytes,
+                     (cudaStream_t)stream);
 }
 
 int arcq_gemm_poll_error(void) { return gemm_poll_error(); }

@@ -70,6 +70,8 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int sfb_tiles;      // ceil(N/128): 128-row scale tiles of B that exist
   int dbg;            // timing experiments only (ARCQ_GEMM_DBG): 1 = skip scale copies, 2 = skip MMAs
+  float* ws;          // split-K: fp32 partial sums [splits][M][N] (scratch), else nullptr
+  int splits;         // K is cut into this many ranges of whole stages (1 = no split)
 };
 
 // ----------------------------------------------------------------------------- PTX wrappers
@@ -221,18 +223,22 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const uint32_t tmem_base = misc[0];
   const uint32_t tmem_sf = tmem_base + BN;   // two stage-parity buffers of SF_COLS columns each
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
-  const int kstages = (p.ksteps_total + KSTEPS - 1) / KSTEPS;
+  // A work item is (output tile, K range).  Without split-K there is one range per tile.
+  const int num_tiles = p.tiles_m * p.tiles_n * p.splits;
+  const int kstages_all = (p.ksteps_total + KSTEPS - 1) / KSTEPS;
+  const int kstages_per = (kstages_all + p.splits - 1) / p.splits;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_tiles && ok; item += gridDim.x) {
+        const int tile = item / p.splits, split = item - tile * p.splits;
         const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
         const int rtb = (tn * BN) / 128;   // first 128-row scale tile of B this output tile touches
-        for (int ks = 0; ks < kstages; ++ks, ++it) {
+        const int ks_end = min(kstages_all, (split + 1) * kstages_per);
+        for (int ks = split * kstages_per; ks < ks_end; ++ks, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
@@ -264,15 +270,17 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       constexpr uint32_t idesc = instr_desc<BN>();
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+      for (int item = blockIdx.x; item < num_tiles && ok; item += gridDim.x, ++tile_it) {
+        const int tile = item / p.splits, split = item - tile * p.splits;
         const int tn = tile / p.tiles_m;
+        const int ks_begin = split * kstages_per, ks_end = min(kstages_all, (split + 1) * kstages_per);
         // sub-atom column offset when BN = 64: rows 32j..32j+31 of an atom live in TMEM column j, so
         // the upper half of a 128-row scale atom starts two columns in.  (Tiles narrower than 64
         // would need an odd column offset, which the block-scaled MMA rejects as misaligned.)
         const uint32_t sfb_sub = (BN < 128) ? (uint32_t)(((tn * BN) % 128) / 32) : 0u;
         if (!mbar_wait(tmem_empty_bar, (tile_it & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        for (int ks = 0; ks < kstages; ++ks, ++it) {
+        for (int ks = ks_begin; ks < ks_end; ++ks, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1u;
           if (!mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
@@ -296,7 +304,7 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const uint64_t adesc = smem_desc(a_s + k * 32, 1024, LAYOUT_SW128);
             const uint64_t bdesc = smem_desc(b_s + k * 32, 1024, LAYOUT_SW128);
             tc_mma_nvf4(tmem_base, adesc, bdesc, idesc, t_sfa + k * 4, t_sfb + k * 4 * C::NB + sfb_sub,
-                        (ks | k) ? 1u : 0u);
+                        ((ks - ks_begin) | k) ? 1u : 0u);
           }
           tc_commit(empty_bar(s));   // stage reusable once these MMAs have read it
         }
@@ -311,7 +319,8 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (p.alpha_b) alpha *= __ldg(p.alpha_b);
     uint32_t tile_it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_it) {
+    for (int item = blockIdx.x; item < num_tiles && ok; item += gridDim.x, ++tile_it) {
+      const int tile = item / p.splits, split = item - tile * p.splits;
       const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
       ok = mbar_wait(tmem_full_bar, tile_it & 1u, abort_flag);
       ok = __all_sync(0xffffffffu, ok);   // keep the warp converged for the .sync.aligned loads
@@ -325,7 +334,16 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
         tc_wait_ld();
         const int col = tn * BN + c0;
-        if (row < p.M && col < p.N && !(p.dbg & 4)) {
+        if (p.ws != nullptr) {
+          // split-K: raw fp32 partial sums of this K range; the reduction kernel applies alpha
+          if (row < p.M && col < p.N) {
+            float* wrow = p.ws + ((size_t)split * p.M + row) * p.N + col;
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              if (col + v * 4 < p.N)   // N is a multiple of 8, so groups of four are in or out
+                *reinterpret_cast<uint4*>(wrow + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+          }
+        } else if (row < p.M && col < p.N && !(p.dbg & 4)) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             if (col + v * 8 < p.N) {   // N is a multiple of 8: whole 16-byte pieces are in or out
@@ -656,6 +674,29 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
 }
 
+// Sum of the split-K partials in a fixed order, times alpha, to bf16.  Eight outputs per thread.
+__global__ void arcq_splitk_reduce_kernel(const float* __restrict__ ws, int splits, long long mn, float alpha,
+                                          const float* alpha_a, const float* alpha_b, __nv_bfloat16* __restrict__ c) {
+  if (alpha_a) alpha *= __ldg(alpha_a);
+  if (alpha_b) alpha *= __ldg(alpha_b);
+  const long long nvec = mn / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < splits; ++s) {
+      const float4* src = reinterpret_cast<const float4*>(ws + (size_t)s * mn + i * 8);
+      const float4 a = src[0], b = src[1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0] * alpha, acc[1] * alpha);
+    o.y = pack_bf16x2(acc[2] * alpha, acc[3] * alpha);
+    o.z = pack_bf16x2(acc[4] * alpha, acc[5] * alpha);
+    o.w = pack_bf16x2(acc[6] * alpha, acc[7] * alpha);
+    reinterpret_cast<uint4*>(c)[i] = o;
+  }
+}
+
 // ----------------------------------------------------------------------------- host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -749,7 +790,7 @@ int launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int nu
   auto kern = arcq_gemm_kernel<BN>;
   ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   p.tiles_n = (p.N + BN - 1) / BN;
-  long long tiles = (long long)p.tiles_m * p.tiles_n;
+  long long tiles = (long long)p.tiles_m * p.tiles_n * p.splits;
   int grid = (int)(tiles < num_sms ? tiles : num_sms);
   kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, p);
   ARCQ_CUDA_TRY(cudaGetLastError());
@@ -758,9 +799,37 @@ int launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int nu
 
 }  // namespace
 
+// Narrowest tile width and K split the launcher would use for a skinny problem.
+static void plan_splitk(int64_t M, int64_t N, int64_t K_eff, int num_sms, int* bn_out, int* splits_out) {
+  const int tiles_m = (int)((M + BM - 1) / BM);
+  int bn = 256;
+  while (bn > 64 && (long long)tiles_m * ((N + bn - 1) / bn) < num_sms) bn >>= 1;
+  const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn);
+  const int kstages = (int)((K_eff / 64 + KSTEPS - 1) / KSTEPS);
+  int splits = 1;
+  if (tiles * 2 <= num_sms) {
+    splits = (int)(num_sms / tiles);
+    if (splits > 8) splits = 8;
+    if (splits > kstages / 2) splits = kstages / 2;   // at least two stages per range
+    if (splits < 1) splits = 1;
+    // ranges of ceil(kstages/splits) stages must all be non-empty
+    while (splits > 1 && (splits - 1) * ((kstages + splits - 1) / splits) >= kstages) --splits;
+  }
+  *bn_out = bn;
+  *splits_out = splits;
+}
+
+size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K_eff) {
+  DeviceInfo di;
+  if (get_device_info(&di) != ARCQ_OK) return 0;
+  int bn, splits;
+  plan_splitk(M, N, K_eff, di.num_sms, &bn, &splits);
+  return splits > 1 ? (size_t)splits * (size_t)M * (size_t)N * sizeof(float) : 0;
+}
+
 int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M, int64_t N,
                 int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* Cout,
-                cudaStream_t stream) {
+                void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   DeviceInfo di;
   int rc = get_device_info(&di);
   if (rc != ARCQ_OK) return rc;
@@ -781,6 +850,8 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   p.sfb_tiles = (int)((N + 127) / 128);
   p.dbg = 0;
   if (const char* e = getenv("ARCQ_GEMM_DBG")) p.dbg = atoi(e);
+  p.ws = nullptr;
+  p.splits = 1;
 
   // Widest tile that still gives every SM work; narrow tiles for skinny problems.  Partial tiles
   // are clipped by the TMA box (zero fill) and by the store guards.  ARCQ_GEMM_BN=32|64|128|256
@@ -798,6 +869,18 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   if (const char* e = getenv("ARCQ_GEMM_PAIR")) pair = atoi(e) != 0;
   if (pair) return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream);
 
+  // Skinny problems (few output tiles, long K): split K over otherwise idle SMs when the caller
+  // provided scratch for the fp32 partial sums.
+  if (workspace != nullptr && !getenv("ARCQ_GEMM_BN")) {
+    int bn2, splits;
+    plan_splitk(M, N, K_eff, di.num_sms, &bn2, &splits);
+    if (splits > 1 && workspace_bytes >= (size_t)splits * (size_t)M * (size_t)N * sizeof(float)) {
+      bn = bn2;
+      p.ws = static_cast<float*>(workspace);
+      p.splits = splits;
+    }
+  }
+
   CUtensorMap ma, mb;
   rc = make_operand_map(&ma, A, M, K_eff / 2, BM);
   if (rc != ARCQ_OK) return rc;
@@ -805,10 +888,17 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   if (rc != ARCQ_OK) return rc;
 
   switch (bn) {
-    case 256: return launch_bn<256>(ma, mb, p, di.num_sms, stream);
-    case 128: return launch_bn<128>(ma, mb, p, di.num_sms, stream);
-    default: return launch_bn<64>(ma, mb, p, di.num_sms, stream);
+    case 256: rc = launch_bn<256>(ma, mb, p, di.num_sms, stream); break;
+    case 128: rc = launch_bn<128>(ma, mb, p, di.num_sms, stream); break;
+    default: rc = launch_bn<64>(ma, mb, p, di.num_sms, stream); break;
   }
+  if (rc != ARCQ_OK || p.splits == 1) return rc;
+  const long long mn = (long long)M * N;
+  long long blocks = (mn / 8 + 255) / 256;
+  if (blocks > (long long)di.num_sms * 8) blocks = (long long)di.num_sms * 8;
+  arcq_splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.ws, p.splits, mn, alpha, alpha_a, alpha_b, p.c);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
 }
 
 int gemm_poll_error() {

@@ -29,9 +29,11 @@ int get_device_info(DeviceInfo* out);
 int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* idx, int64_t rows, int KQ,
                     int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream);
 int launch_absmax(const void* x, int64_t n, float* out, int accumulate, cudaStream_t stream);
+// workspace (may be null): scratch for split-K partial sums, see gemm_workspace_bytes().
 int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                 int64_t N, int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* C,
-                cudaStream_t stream);
+                void* workspace, size_t workspace_bytes, cudaStream_t stream);
+size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K_eff);
 int gemm_poll_error();
 
 }  // namespace arcq

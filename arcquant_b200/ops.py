@@ -79,10 +79,7 @@ def rmsnorm_quantize_x(x, weight, eps: float, reorder_index, ke: int):
     return _quantize("rms", x, weight, eps, reorder_index, ke, _lib.MODE_16)
 
 
-def matmul(a, b, sfa, sfb, scale) -> torch.Tensor:
-    """bf16 [M,N] = scale * (A.SFA)(B.SFB)^T.  ``scale`` may be a Python float or
-    a 0-dim tensor; a CUDA 0-dim fp32 tensor is consumed on the device (no
-    host synchronisation)."""
+def _matmul(a, b, sfa, sfb, alpha: float, alpha_a, alpha_b) -> torch.Tensor:
     lib = _lib.load()
     for t, n in ((a, "A"), (b, "B"), (sfa, "SFA"), (sfb, "SFB")):
         _require(t, torch.uint8, n)
@@ -92,28 +89,29 @@ def matmul(a, b, sfa, sfb, scale) -> torch.Tensor:
         raise RuntimeError("A and B disagree on K")
     c = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
     with torch.cuda.device(a.device):
-        if isinstance(scale, torch.Tensor) and scale.is_cuda and scale.dtype == torch.float32:
-            rc = lib.arcq_matmul_nvfp4_dev_alpha(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n,
-                                                 kb * 2, scale.data_ptr(), None, c.data_ptr(), _stream())
-        else:
-            rc = lib.arcq_matmul_nvfp4(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, kb * 2,
-                                       float(scale), c.data_ptr(), _stream())
+        # skinny problems split K over idle SMs; the fp32 partial sums need scratch
+        ws_bytes = int(lib.arcq_matmul_workspace_bytes(m, n, kb * 2))
+        ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=a.device) if ws_bytes else None
+        rc = lib.arcq_matmul_nvfp4_ws(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, kb * 2,
+                                      float(alpha), None if alpha_a is None else alpha_a.data_ptr(),
+                                      None if alpha_b is None else alpha_b.data_ptr(), c.data_ptr(),
+                                      None if ws is None else ws.data_ptr(), ws_bytes, _stream())
     _lib.check(rc, f"matmul M={m} N={n} K={kb * 2}")
     return c
+
+
+def matmul(a, b, sfa, sfb, scale) -> torch.Tensor:
+    """bf16 [M,N] = scale * (A.SFA)(B.SFB)^T.  ``scale`` may be a Python float or
+    a 0-dim tensor; a CUDA 0-dim fp32 tensor is consumed on the device (no
+    host synchronisation)."""
+    if isinstance(scale, torch.Tensor) and scale.is_cuda and scale.dtype == torch.float32:
+        return _matmul(a, b, sfa, sfb, 1.0, scale, None)
+    return _matmul(a, b, sfa, sfb, float(scale), None, None)
 
 
 def matmul_dev_alpha(a, b, sfa, sfb, alpha_a: torch.Tensor, alpha_b: torch.Tensor | None = None) -> torch.Tensor:
     """matmul with alpha = alpha_a * alpha_b, both fp32 scalars in device memory."""
-    lib = _lib.load()
-    m, kb = a.shape
-    n = b.shape[0]
-    c = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
-    with torch.cuda.device(a.device):
-        rc = lib.arcq_matmul_nvfp4_dev_alpha(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, kb * 2,
-                                             alpha_a.data_ptr(), None if alpha_b is None else alpha_b.data_ptr(),
-                                             c.data_ptr(), _stream())
-    _lib.check(rc, f"matmul M={m} N={n} K={kb * 2}")
-    return c
+    return _matmul(a, b, sfa, sfb, 1.0, alpha_a, alpha_b)
 
 
 def absmax(x: torch.Tensor) -> torch.Tensor:

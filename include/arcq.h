@@ -113,6 +113,19 @@ int arcq_matmul_nvfp4_dev_alpha(const uint8_t* A, const uint8_t* B, const uint8_
                                 int64_t M, int64_t N, int64_t K_eff, const float* alpha_a,
                                 const float* alpha_b, void* C, void* stream);
 
+/* Skinny problems (M <= 128 with a long K leave most SMs without an output tile) run faster when K
+ * is split over the idle SMs; that needs scratch for the fp32 partial sums.
+ * arcq_matmul_workspace_bytes: how much scratch the split-K path would use for this shape on the
+ * current device (0 = the shape is not split).  arcq_matmul_nvfp4_ws: arcq_matmul_nvfp4 /
+ * _dev_alpha (alpha = alpha * *alpha_a * *alpha_b, the pointers may be NULL) with caller-provided
+ * scratch; with workspace == NULL or too small it behaves exactly like arcq_matmul_nvfp4.  The
+ * partials are summed in a fixed order, so results are reproducible.  Same reference interface
+ * as arcq_matmul_nvfp4 (kernels/src/bindings.cpp:99-120). */
+size_t arcq_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K_eff);
+int arcq_matmul_nvfp4_ws(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                         int64_t M, int64_t N, int64_t K_eff, float alpha, const float* alpha_a,
+                         const float* alpha_b, void* C, void* workspace, size_t workspace_bytes, void* stream);
+
 /* The GEMM kernel bounds every wait on a barrier; if one ever expires the
  * kernel records it and returns.  This reads (and clears) that record for the
  * current device: ARCQ_OK or ARCQ_ERR_TIMEOUT.  Synchronises the device. */

@@ -178,3 +178,40 @@ def test_large_shapes_by_row_independence_and_samples(m, n, kq):
     # and against the unquantised product the ARC error stays in the expected band
     y = (x[rows.to(dev)].float() @ w.float().T).cpu().numpy()
     assert _relerr(csub.float().cpu().numpy(), y) < 0.2
+
+
+@pytest.mark.parametrize("m,n,kq,ke", [(1, 4096, 4096, 128), (16, 4096, 4096, 128), (128, 4096, 14336, 128), (100, 1000, 1984, 64)])
+def test_split_k_for_skinny_problems(m, n, kq, ke):
+    """M <= 128: K is cut over otherwise idle SMs, fp32 partials in caller-provided scratch, summed in
+    a fixed order.  Same answer as the unsplit kernel up to fp32 summation order, and bit-stable."""
+    import ctypes
+
+    from arcquant_b200 import _lib
+
+    O = _oracle()
+    a, sfa, b, sfb, alpha = _operands(m, n, kq, ke, seed=m + n + 1)
+    ref = O.gemm_fast(a, sfa, b, sfb, alpha)
+    L = _lib.load()
+    t = [torch.from_numpy(v).cuda() for v in (a, b, sfa, sfb)]
+    k_eff = kq + ke
+    ws_bytes = int(L.arcq_matmul_workspace_bytes(m, n, k_eff))
+    assert ws_bytes > 0 and ws_bytes % (m * n * 4) == 0          # these shapes are split
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    outs = []
+    for wsp, wsb in ((ws.data_ptr(), ws_bytes), (ws.data_ptr(), ws_bytes), (None, 0)):
+        c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        rc = L.arcq_matmul_nvfp4_ws(t[0].data_ptr(), t[1].data_ptr(), t[2].data_ptr(), t[3].data_ptr(), m, n, k_eff,
+                                    alpha, None, None, c.data_ptr(), wsp, wsb, None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        outs.append(c.float().cpu().numpy())
+    assert _ops().gemm_poll_error() == 0
+    assert np.array_equal(outs[0], outs[1])                       # deterministic
+    for c in outs:
+        _assert_close(c, ref)
+    # too small a workspace silently falls back to the unsplit kernel
+    c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    assert L.arcq_matmul_nvfp4_ws(t[0].data_ptr(), t[1].data_ptr(), t[2].data_ptr(), t[3].data_ptr(), m, n, k_eff,
+                                  alpha, None, None, c.data_ptr(), ws.data_ptr(), 16, None) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(c.float().cpu().numpy(), outs[2])

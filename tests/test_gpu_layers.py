@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 def _small_cfg():
     from arcquant_b200.llama_layer import LlamaLayerConfig
-    return LlamaLayerConfig(hidden=1024, n_heads=8, n_kv_heads=2, head_dim=128, ffn=2048, select_num=64)
+    return LlamaLayerConfig(hidden=1024, n_heads=8, n_kv_heads=4, head_dim=128, ffn=2048, select_num=64)
 
 
 def _oracle_linear(x_bf16, w_bf16, idx, ke, gamma=None, eps=0.0, global_scale=True):
