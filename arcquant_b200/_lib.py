@@ -18,6 +18,8 @@ ERR_NULL_POINTER = 3
 ERR_CUDA = 4
 ERR_ALIGNMENT = 5
 ERR_TIMEOUT = 6
+ERR_SCRATCH_LIMIT = 7
+STATIC_SCRATCH_BYTES = 2 << 20
 
 MODE_16 = 16
 MODE_32 = 32
@@ -37,6 +39,7 @@ SIGNATURES = {
     "arcq_matmul_nvfp4_dev_alpha": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "arcq_matmul_workspace_bytes": (C.c_size_t, [_i64, _i64, _i64]),
     "arcq_matmul_nvfp4_ws": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "arcq_matmul_nvfp4_static": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp, _vp]),
     "arcq_gemm_poll_error": (_i32, []),
     "arcq_absmax_bf16": (_i32, [_vp, _i64, _vp, _i32, _vp]),
 }

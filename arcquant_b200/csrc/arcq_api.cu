@@ -62,6 +62,9 @@ const char* arcq_status_string(int status) {
     case ARCQ_ERR_CUDA: return "CUDA error";
     case ARCQ_ERR_ALIGNMENT: return "pointer not 16-byte aligned";
     case ARCQ_ERR_TIMEOUT: return "device-side wait timed out";
+    case ARCQ_ERR_SCRATCH_LIMIT:
+      return "problem needs more scratch than the built-in 2 MiB block of arcq_matmul_nvfp4_static; "
+             "use arcq_matmul_nvfp4_ws with caller-provided scratch";
     default: return "unknown status";
   }
 }
@@ -156,6 +159,14 @@ int arcq_matmul_nvfp4_ws(const uint8_t* A, const uint8_t* B, const uint8_t* SFA,
   if (workspace != nullptr && !aligned16(workspace)) return ARCQ_ERR_ALIGNMENT;
   return launch_gemm(A, B, SFA, SFB, M, N, K_eff, alpha, alpha_a, alpha_b, C, workspace, workspace_bytes,
                      (cudaStream_t)stream);
+}
+
+int arcq_matmul_nvfp4_static(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                             int64_t N, int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b,
+                             void* C, void* stream) {
+  int rc = check_gemm(A, B, SFA, SFB, M, N, K_eff, C);
+  if (rc != ARCQ_OK || M == 0) return rc;
+  return launch_gemm_static(A, B, SFA, SFB, M, N, K_eff, alpha, alpha_a, alpha_b, C, (cudaStream_t)stream);
 }
 
 int arcq_gemm_poll_error(void) { return gemm_poll_error(); }

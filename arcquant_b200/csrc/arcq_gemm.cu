@@ -901,6 +901,43 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   return ARCQ_OK;
 }
 
+// ----------------------------------------------------------------------------- no-allocation entry point
+//
+// Scratch for arcq_matmul_nvfp4_static: a fixed block of device memory that is part of the loaded
+// library image (every GPU that loads libarcq.so carries these 2 MiB until the process exits).
+// In host code the name below is only a handle; the device address is looked up once per device
+// with cudaGetSymbolAddress and that address is what the kernels receive.
+constexpr size_t STATIC_SCRATCH_BYTES = (size_t)ARCQ_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+static int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* addr[64] = {};
+  int dev = 0;
+  ARCQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return ARCQ_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    ARCQ_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));   // with device `dev` current
+    if (ptr == nullptr) return cuda_fail(cudaErrorInvalidSymbol);
+    addr[dev] = ptr;
+  }
+  *out = addr[dev];
+  return ARCQ_OK;
+}
+
+int launch_gemm_static(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                       int64_t N, int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* Cout,
+                       cudaStream_t stream) {
+  const size_t need = gemm_workspace_bytes(M, N, K_eff);
+  if (need > STATIC_SCRATCH_BYTES) return ARCQ_ERR_SCRATCH_LIMIT;
+  void* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc != ARCQ_OK) return rc;
+  return launch_gemm(A, B, SFA, SFB, M, N, K_eff, alpha, alpha_a, alpha_b, Cout, scratch, STATIC_SCRATCH_BYTES, stream);
+}
+
 int gemm_poll_error() {
   ARCQ_CUDA_TRY(cudaDeviceSynchronize());
   int v = 0;

@@ -42,6 +42,7 @@ extern "C" {
 #define ARCQ_ERR_CUDA 4           /* a CUDA runtime/driver call failed; see arcq_last_cuda_error() */
 #define ARCQ_ERR_ALIGNMENT 5      /* a pointer is not 16-byte aligned */
 #define ARCQ_ERR_TIMEOUT 6        /* a bounded device-side wait expired (reported by arcq_gemm_poll_error) */
+#define ARCQ_ERR_SCRATCH_LIMIT 7  /* arcq_matmul_nvfp4_static: the shape needs more than its built-in scratch */
 
 /* Channel-layout family of the critical groups.
  * 16: one group per slot  - [main][residual] per critical group
@@ -125,6 +126,29 @@ size_t arcq_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K_eff);
 int arcq_matmul_nvfp4_ws(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
                          int64_t M, int64_t N, int64_t K_eff, float alpha, const float* alpha_a,
                          const float* alpha_b, void* C, void* workspace, size_t workspace_bytes, void* stream);
+
+/* No counterpart in the reference.  The split-K GEMM for callers that must not allocate device
+ * memory: code that runs where an allocation would fail or stall - an inference-server plugin
+ * whose enqueue hook is forbidden to call the allocator, a process whose whole device memory has
+ * been handed to another framework's pool, a latency-critical loop where a cudaMalloc would
+ * serialise the device.  Same arithmetic and same split as arcq_matmul_nvfp4_ws, but the fp32
+ * partial sums live in a block of ARCQ_STATIC_SCRATCH_BYTES (2 MiB) that is part of the library
+ * image itself; every GPU that loads the library holds that block until the process exits.  Inputs
+ * and the output are still the caller's.  The call allocates nothing: no cudaMalloc / cudaFree, no
+ * allocating library routine.
+ *   - Shapes whose partial sums exceed the block (arcq_matmul_workspace_bytes(M,N,K_eff) >
+ *     ARCQ_STATIC_SCRATCH_BYTES, e.g. M 128 x N 4096 x K_eff 14464) are refused with
+ *     ARCQ_ERR_SCRATCH_LIMIT; shapes that are not split at all run without touching the block.
+ *   - The first call on each device looks up the block's device address (one cudaGetSymbolAddress,
+ *     with that device current); make that first call outside any stream capture.
+ *   - All calls share the one block and it keeps whatever the previous call left.  Nothing in it
+ *     needs clearing: every partial sum that is read was written earlier in the same call.  For the
+ *     same reason two calls that overlap on the GPU (different streams, or different host threads
+ *     on one device) race on it - serialise them on one stream. */
+#define ARCQ_STATIC_SCRATCH_BYTES (2u << 20)
+int arcq_matmul_nvfp4_static(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                             int64_t M, int64_t N, int64_t K_eff, float alpha, const float* alpha_a,
+                             const float* alpha_b, void* C, void* stream);
 
 /* The GEMM kernel bounds every wait on a barrier; if one ever expires the
  * kernel records it and returns.  This reads (and clears) that record for the
