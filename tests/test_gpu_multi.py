@@ -1,0 +1,76 @@
+"""Two-GPU runs of the tensor-parallel layer and the expert-parallel MoE block over NCCL (one process
+per GPU).  Skipped on a single-GPU machine; the CPU suite covers the same bookkeeping with gloo."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from arcquant_b200 import synth
+        from arcquant_b200.llama_layer import (LlamaLayerConfig, QLlamaDecoderLayerTP, random_layer_weights,
+                                               random_reorder_indices)
+        from arcquant_b200.moe_block import MoEConfig, QMixtralMoEBlockEP, random_moe_weights, route_top_k
+
+        dev = torch.device("cuda", rank)
+        # --- tensor-parallel layer: the NCCL all-reduce must give what adding the partials by hand gives
+        cfg = LlamaLayerConfig(hidden=1024, n_heads=8, n_kv_heads=4, head_dim=128, ffn=2048, select_num=64)
+        W, I = random_layer_weights(cfg, 0), random_reorder_indices(cfg, 1)
+        x = synth.activations(64, cfg.hidden, 4, synth.outlier_channels(cfg.hidden, 10, 3)).reshape(1, 64, -1).to(dev)
+        pos = torch.arange(64, device=dev)
+        y = QLlamaDecoderLayerTP(cfg, W, I, tp_rank=rank, tp_size=world, device=dev)(x, pos)
+        ranks = [QLlamaDecoderLayerTP(cfg, W, I, tp_rank=r, tp_size=world, device=dev) for r in range(world)]
+        x2 = x.reshape(64, -1)
+        h = x2 + sum(r.attn_partial(x2, 1, 64, pos).float() for r in ranks).to(torch.bfloat16)
+        ref = (h + sum(r.mlp_partial(h).float() for r in ranks).to(torch.bfloat16)).reshape(1, 64, -1)
+        err_tp = float((y.float() - ref.float()).norm() / ref.float().norm())
+        # --- expert-parallel MoE block: same per-expert batches as one rank owning every expert
+        mcfg = MoEConfig(hidden=1024, ffn=2048, n_experts=4, top_k=2, select_num=64)
+        MW = random_moe_weights(mcfg, 0)
+        xt = synth.activations(96, mcfg.hidden, 5, synth.outlier_channels(mcfg.hidden, 10, 3)).to(dev)
+        ids, w = route_top_k(xt, MW["router"].to(dev), mcfg.top_k)
+        full = QMixtralMoEBlockEP(mcfg, MW, device=dev)(xt, routing=(ids, w))
+        lo, hi = rank * 96 // world, (rank + 1) * 96 // world
+        part = QMixtralMoEBlockEP(mcfg, MW, ep_rank=rank, ep_size=world, device=dev)(
+            xt[lo:hi].contiguous(), routing=(ids[lo:hi].contiguous(), w[lo:hi].contiguous()))
+        err_ep = float((part.float() - full[lo:hi].float()).norm() / full[lo:hi].float().norm())
+        q.put((rank, err_tp, err_ep))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp_layer_and_ep_moe_over_nccl():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=600) for _ in procs)
+    for p in procs:
+        p.join(timeout=120)
+    for rank, err_tp, err_ep in res:
+        assert err_tp < 1e-2, (rank, err_tp)      # bf16 all-reduce vs fp32 hand sum
+        assert err_ep < 1e-2, (rank, err_ep)      # identical expert batches, different row grouping in transit
