@@ -169,7 +169,11 @@ int arcq_matmul_nvfp4_static(const uint8_t* A, const uint8_t* B, const uint8_t* 
   return launch_gemm_static(A, B, SFA, SFB, M, N, K_eff, alpha, alpha_a, alpha_b, C, (cudaStream_t)stream);
 }
 
-int arcq_gemm_poll_error(void) { return gemm_poll_error(); }
+int arcq_gemm_poll_error(void) {
+  const int g = gemm_poll_error();
+  const int q = quant_poll_error();   // read (and cleared) as well, whatever the first says
+  return g != ARCQ_OK ? g : q;
+}
 
 int arcq_absmax_bf16(const void* x, int64_t n, float* out, int accumulate, void* stream) {
   if (n < 0) return ARCQ_ERR_BAD_SHAPE;

@@ -39,5 +39,7 @@ int launch_gemm_static(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, c
                        int64_t N, int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* C,
                        cudaStream_t stream);
 int gemm_poll_error();
+// Same for the bounded waits of the warp-specialised quantizer.
+int quant_poll_error();
 
 }  // namespace arcq

@@ -187,13 +187,17 @@ __device__ __forceinline__ Slot slot_of(int g, int G0, int mode) {
 // its row's reciprocal scale (one FMUL2 per word) and converts to e2m1, eight codes per word.
 __device__ __forceinline__ void encode_pair(const uint32_t (&w)[16], float rcp0, float rcp1, uint2& c0, uint2& c1) {
   const float2 r = make_float2(rcp0, rcp1);
-  float2 v[16];
+  uint32_t o0[2], o1[2];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __fmul2_rn(make_float2(bf16lo(w[i]), bf16hi(w[i])), r);
-  c0.x = e2m1x8(v[0].x, v[1].x, v[2].x, v[3].x, v[4].x, v[5].x, v[6].x, v[7].x);
-  c0.y = e2m1x8(v[8].x, v[9].x, v[10].x, v[11].x, v[12].x, v[13].x, v[14].x, v[15].x);
-  c1.x = e2m1x8(v[0].y, v[1].y, v[2].y, v[3].y, v[4].y, v[5].y, v[6].y, v[7].y);
-  c1.y = e2m1x8(v[8].y, v[9].y, v[10].y, v[11].y, v[12].y, v[13].y, v[14].y, v[15].y);
+  for (int h = 0; h < 2; ++h) {   // eight words (one output word per row) at a time: fewer values live
+    float2 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __fmul2_rn(make_float2(bf16lo(w[8 * h + i]), bf16hi(w[8 * h + i])), r);
+    o0[h] = e2m1x8(v[0].x, v[1].x, v[2].x, v[3].x, v[4].x, v[5].x, v[6].x, v[7].x);
+    o1[h] = e2m1x8(v[0].y, v[1].y, v[2].y, v[3].y, v[4].y, v[5].y, v[6].y, v[7].y);
+  }
+  c0 = make_uint2(o0[0], o0[1]);
+  c1 = make_uint2(o1[0], o1[1]);
 }
 
 // Packed |.| maximum of the sixteen words: low half = row0 amax bits, high half = row1.
@@ -273,21 +277,16 @@ __device__ __forceinline__ void quantize_group_pair(uint32_t (&w)[16], int g, co
 // Sum-of-squares tree of one row in the reference's order (rmsnorm.cu:131-154 of ARCQuant), done by
 // one warp: lane l owns the partials of reference threads l, l+32, ... (zero where none exists).
 __device__ __forceinline__ float rms_tree(const float* ps, int nt, int lane) {
-  float v[16];
+  // slot t = lane + 32k, k < 16; the tree adds slots 256, 128, 64 and 32 apart, in that order
+  auto slot = [&](int k) { const int t = lane + 32 * k; return t < nt ? ps[t] : 0.f; };
+  auto b = [&](int k) { return __fadd_rn(slot(k), slot(k + 8)); };       // +256
+  auto c = [&](int k) { return __fadd_rn(b(k), b(k + 4)); };             // +128
+  float d[2];
+#pragma unroll 1
+  for (int h = 0; h < 2; ++h) d[h] = __fadd_rn(c(h), c(h + 2));          // +64 (rolled: keeps few values live)
+  float s = __fadd_rn(d[0], d[1]);                                       // +32
 #pragma unroll
-  for (int k = 0; k < 16; ++k) {
-    int t = lane + 32 * k;
-    v[k] = t < nt ? ps[t] : 0.f;
-  }
-#pragma unroll
-  for (int k = 0; k < 8; ++k) v[k] = __fadd_rn(v[k], v[k + 8]);   // +256
-#pragma unroll
-  for (int k = 0; k < 4; ++k) v[k] = __fadd_rn(v[k], v[k + 4]);   // +128
-  v[0] = __fadd_rn(v[0], v[2]);                                   // +64
-  v[1] = __fadd_rn(v[1], v[3]);
-  float s = __fadd_rn(v[0], v[1]);                                // +32
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, d));
+  for (int d2 = 16; d2 > 0; d2 >>= 1) s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, d2));
   return s;  // valid in lane 0
 }
 
@@ -517,6 +516,359 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Warp-specialised variant (rows of 1024..8192 channels, the hidden sizes of decoder layers).
+//
+// Producer warps stream row pairs from global memory, (RMSNorm them,) interleave them and fill a ring
+// of shared stages; consumer warps gather their groups from a full stage, release it as soon as the
+// gather has landed in registers, and quantize.  Stages are handed over with mbarriers, so there is
+// no CTA-wide barrier in the loop and the warp that carries the critical (residual) groups - a
+// different warp for every row pair - does not hold the others back.  Producers keep the next pair in
+// flight in registers while they fill the current one.
+//
+// Block scales are computed without tables or branches: amax/6 by a multiply and one FMA correction
+// (exact for every bf16 amax), the ue4m3 code of both rows by one packed conversion, and 1/scale by
+// the approximate reciprocal plus one Newton step (exact here: a scale is k*2^e with k <= 15, so its
+// reciprocal lies far from every fp32 rounding boundary).
+
+__device__ int g_quant_error = 0;   // sticky until polled
+constexpr unsigned long long QUANT_WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if this wait (or another warp's) gave up; the CTA then winds down.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*abort_flag) return false;
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+      if (t1 - t0 > QUANT_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        atomicExch(&g_quant_error, ARCQ_ERR_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+// Named barrier over `nthreads` threads that also ORs a flag across them.
+__device__ __forceinline__ bool named_barrier_or(int id, int nthreads, bool flag) {
+  uint32_t out;
+  asm volatile(
+      "{\n.reg .pred p, q;\n"
+      "setp.ne.u32 q, %3, 0;\n"
+      "bar.red.or.pred p, %1, %2, q;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(out)
+      : "r"(id), "r"(nthreads), "r"((uint32_t)flag)
+      : "memory");
+  return out != 0;
+}
+
+__device__ __forceinline__ uint32_t min_u16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("min.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// Scales of both rows from the packed amax bits (low half row 0, high half row 1).
+// codes = ue4m3(row0) | ue4m3(row1) << 8; dec = their values; rcp = fp32(1/dec).
+__device__ __forceinline__ void scale_of_pair_fma(uint32_t m, uint32_t& codes, float2& dec, float2& rcp) {
+  m = min_u16x2(m, 0x7f7f7f7fu);                       // inf/NaN amax -> largest finite (saturates to 448)
+  const float2 a = make_float2(bf16lo(m), bf16hi(m));
+  const float sixth = 0.16666667163372039794921875f;   // fp32(1/6)
+  const float2 c = make_float2(sixth, sixth);
+  const float2 q = __fmul2_rn(a, c);
+  const float2 r = __ffma2_rn(make_float2(-6.0f, -6.0f), q, a);
+  float2 t = __ffma2_rn(r, c, q);                      // = fp32(amax / 6), correctly rounded
+  t.x = fmaxf(t.x, 0.001953125f);
+  t.y = fmaxf(t.y, 0.001953125f);                      // values above 448 saturate in the conversion
+  uint16_t c2;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(c2) : "f"(t.y), "f"(t.x));
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(c2));
+  dec = __half22float2(*reinterpret_cast<__half2*>(&h2));
+  float2 r0;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0.x) : "f"(dec.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0.y) : "f"(dec.y));
+  const float2 e = __ffma2_rn(make_float2(-dec.x, -dec.y), r0, make_float2(1.0f, 1.0f));
+  rcp = __ffma2_rn(r0, e, r0);
+  codes = c2;
+}
+
+// As quantize_group_pair, with the branch-free scales; row 1's outputs sit `q1off` / `sf1off` bytes
+// after row 0's (0 for the odd last row: row 1 is stored first and row 0 overwrites it).
+__device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g, const QuantParams& p, uint8_t* q0,
+                                                       uint32_t q1off, uint8_t* sf0, uint32_t sf1off) {
+  const uint32_t m = amax_pair(w);
+  uint32_t codes;
+  float2 dec, rcp;
+  scale_of_pair_fma(m, codes, dec, rcp);
+  uint2 c0, c1;
+  encode_pair(w, rcp.x, rcp.y, c0, c1);
+  const bool critical = g >= p.G0;
+  int byte_main = 8 * g, col_main = g;
+  Slot sl;
+  if (critical) {
+    sl = slot_of(g, p.G0, p.mode);
+    byte_main = sl.byte_main;
+    col_main = sl.col_main;
+  }
+  const size_t cm = sf_col(col_main);
+  *reinterpret_cast<uint2*>(q0 + q1off + byte_main) = c1;
+  sf0[sf1off + cm] = (uint8_t)(codes >> 8);
+  *reinterpret_cast<uint2*>(q0 + byte_main) = c0;
+  sf0[cm] = (uint8_t)codes;
+  if (!critical) return;
+
+  uint2 e0 = c0, e1 = c1;
+  uint32_t rcodes = codes;
+  if (!p.is_weight) {
+    float d0 = dec.x, d1 = dec.y;
+    if (p.mode == 32) {   // against the un-rounded fp32 scale
+      d0 = make_scale_slow(__uint_as_float((m & 0xffffu) << 16)).raw;
+      d1 = make_scale_slow(__uint_as_float((m >> 16) << 16)).raw;
+    }
+    residual_pair(w, c0, c1, d0, d1);
+    const uint32_t rm = amax_pair(w);
+    float2 rdec, rrcp;
+    scale_of_pair_fma(rm, rcodes, rdec, rrcp);
+    encode_pair(w, rrcp.x, rrcp.y, e0, e1);
+  }
+  const size_t cr = sf_col(sl.col_res);
+  *reinterpret_cast<uint2*>(q0 + q1off + sl.byte_res) = e1;
+  sf0[sf1off + cr] = (uint8_t)(rcodes >> 8);
+  *reinterpret_cast<uint2*>(q0 + sl.byte_res) = e0;
+  sf0[cr] = (uint8_t)rcodes;
+}
+
+// 16-byte chunks of one row pair held by a producer thread.
+template <int CPP>
+struct PairRegs {
+  uint4 a[CPP], b[CPP];
+};
+
+// S: ring stages.  RMS: fused RMSNorm.  There are KQ/16 producer threads with two 16-byte chunks of
+// each row apiece - chunk t and chunk t + KQ/16, the reference's assignment and summation order.
+// Threads [0, nct) are consumers, [nct, nct + npt) producers; both counts are multiples of 32.
+template <bool RMS, int S>
+__global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantParams p, const int nct, const int npt) {
+  constexpr int CPP = 2;
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int tid = threadIdx.x;
+  const int KQ = p.KQ, G = p.G, nchunks = p.nchunks;
+  const uint32_t rows = (uint32_t)p.rows, npairs = (uint32_t)p.npairs;
+
+  // shared layout: [full[S], empty[S] barriers, abort flag: 160 B][offsets][gain][partial sums, rstd][stages]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 128);
+  size_t cursor = 160;
+  uint32_t* offs32 = reinterpret_cast<uint32_t*>(smem + cursor);
+  cursor += (size_t)KQ * 4;
+  float* gain = reinterpret_cast<float*>(smem + cursor);   // natural channel order
+  float* psum = nullptr;
+  float* rstd_s = nullptr;
+  if (RMS) {
+    cursor += (size_t)KQ * 4;
+    psum = reinterpret_cast<float*>(smem + cursor);
+    cursor += (size_t)2 * npt * sizeof(float);
+    rstd_s = reinterpret_cast<float*>(smem + cursor);
+    cursor += 16;
+  }
+  uint8_t* stages = smem + cursor;
+  const uint32_t stage_bytes = (uint32_t)KQ * 4;
+  const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + S);
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full0 + 8 * s, (uint32_t)(npt >> 5));    // one arrival per producer warp
+      mbar_init(empty0 + 8 * s, (uint32_t)(nct >> 5));   // one arrival per consumer warp
+    }
+    *abort_flag = 0;
+  }
+  for (int j = tid; j < KQ; j += blockDim.x) {
+    const int c = p.idx ? (int)p.idx[j] : j;
+    const int g = j >> 4, i = j & 15;
+    offs32[(((i >> 2) * G + g) << 2) | (i & 3)] = word_offset((uint32_t)c);
+    if (RMS) gain[j] = __uint_as_float((uint32_t)p.gamma[j] << 16);
+  }
+  __syncthreads();
+
+  const uint32_t stride = gridDim.x;
+  if (tid >= nct) {
+    // ------------------------------------------------------------------ producers
+    const int ptid = tid - nct, lane = tid & 31, pwarp = ptid >> 5;
+    const uint4* xg = reinterpret_cast<const uint4*>(p.x);
+    auto load_pair = [&](uint32_t unit, PairRegs<CPP>& r) {
+      const uint32_t r0 = 2 * unit;
+      const bool has0 = unit < npairs, has1 = has0 && (r0 + 1) < rows;
+      const uint4* x0 = xg + (size_t)r0 * (size_t)nchunks;
+      const uint4* x1 = x0 + nchunks;
+#pragma unroll
+      for (int j = 0; j < CPP; ++j) {
+        const int c = ptid + j * npt;
+        r.a[j] = has0 ? ldg_stream(x0 + c) : make_uint4(0, 0, 0, 0);
+        r.b[j] = has1 ? ldg_stream(x1 + c) : make_uint4(0, 0, 0, 0);
+      }
+    };
+    auto prefetch_l2 = [&](uint32_t unit) {
+      if (ptid < 2) {
+        const uint32_t r = 2 * unit + ptid;
+        if (unit < npairs && r < rows)
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.x + (size_t)r * (size_t)KQ), "r"(KQ * 2)
+                       : "memory");
+      }
+    };
+    bool failed = false;
+    // Fills stage (it % S) with the pair held in `cur` while `nxt` streams in.
+    auto produce = [&](uint32_t unit, uint32_t it, PairRegs<CPP>& cur, PairRegs<CPP>& nxt) {
+      load_pair(unit + stride, nxt);
+      prefetch_l2(unit + 2 * stride);
+      const uint32_t s = it % S, ph = (it / S) & 1u;
+      uint4* b4 = reinterpret_cast<uint4*>(stages + (size_t)s * stage_bytes);
+      if (!failed && !mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) failed = true;
+      if (!RMS) {
+        if (failed) return false;
+#pragma unroll
+        for (int j = 0; j < CPP; ++j) {
+          const int c = ptid + j * npt;
+          const uint4 a = cur.a[j], b = cur.b[j];
+          uint4 lo, hi;  // words of channels 8c..8c+3 and 8c+4..8c+7: (row0[ch], row1[ch]) per word
+          lo.x = __byte_perm(a.x, b.x, 0x5410); lo.y = __byte_perm(a.x, b.x, 0x7632);
+          lo.z = __byte_perm(a.y, b.y, 0x5410); lo.w = __byte_perm(a.y, b.y, 0x7632);
+          hi.x = __byte_perm(a.z, b.z, 0x5410); hi.y = __byte_perm(a.z, b.z, 0x7632);
+          hi.z = __byte_perm(a.w, b.w, 0x5410); hi.w = __byte_perm(a.w, b.w, 0x7632);
+          b4[swz16(2u * c)] = lo;
+          b4[swz16(2u * c + 1u)] = hi;
+        }
+      } else {
+        // Pass 1: sum of squares from the registers; the raw chunks are parked in this thread's own
+        // 32 bytes of the stage (so they need not stay in registers across the reduction).
+        // Reference thread t adds chunk t, then chunk t + KQ/16, eight elements each, in order.
+        float2 ss = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < CPP; ++j) {
+          const int c = ptid + j * npt;
+          const uint32_t wa[4] = {cur.a[j].x, cur.a[j].y, cur.a[j].z, cur.a[j].w};
+          const uint32_t wb[4] = {cur.b[j].x, cur.b[j].y, cur.b[j].z, cur.b[j].w};
+          if (!failed) {
+            b4[swz16(2u * c)] = cur.a[j];
+            b4[swz16(2u * c + 1u)] = cur.b[j];
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 lo = make_float2(bf16lo(wa[i]), bf16lo(wb[i]));
+            const float2 hi = make_float2(bf16hi(wa[i]), bf16hi(wb[i]));
+            ss = __ffma2_rn(lo, lo, ss);
+            ss = __ffma2_rn(hi, hi, ss);
+          }
+        }
+        psum[ptid] = ss.x;
+        psum[npt + ptid] = ss.y;
+        if (named_barrier_or(1, npt, failed)) return false;   // every producer leaves together
+        if (pwarp < 2) {
+          const float t = rms_tree(psum + pwarp * npt, npt, lane);
+          if (lane == 0) rstd_s[pwarp] = __frsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)KQ), p.eps));
+        }
+        named_barrier_or(2, npt, false);
+        const float2 rstd = make_float2(rstd_s[0], rstd_s[1]);
+        // Pass 2: normalise and interleave in place.
+#pragma unroll
+        for (int j = 0; j < CPP; ++j) {
+          const int c = ptid + j * npt;
+          const uint4 a = b4[swz16(2u * c)], b = b4[swz16(2u * c + 1u)];
+          const float4 g0 = reinterpret_cast<const float4*>(gain)[2 * c];
+          const float4 g1 = reinterpret_cast<const float4*>(gain)[2 * c + 1];
+          // bf16 x bf16 is exact in fp32; then one rounding by rstd (both rows in one FMUL2), one to bf16
+          auto norm = [&](uint32_t wa, uint32_t wb, float ga, float gb, uint32_t& o0, uint32_t& o1) {
+            const float2 t0 = make_float2(__fmul_rn(bf16lo(wa), ga), __fmul_rn(bf16lo(wb), ga));
+            const float2 t1 = make_float2(__fmul_rn(bf16hi(wa), gb), __fmul_rn(bf16hi(wb), gb));
+            const float2 n0 = __fmul2_rn(t0, rstd), n1 = __fmul2_rn(t1, rstd);
+            o0 = pack_bf16x2_rn(n0.x, n0.y);
+            o1 = pack_bf16x2_rn(n1.x, n1.y);
+          };
+          uint4 lo, hi;
+          norm(a.x, b.x, g0.x, g0.y, lo.x, lo.y);
+          norm(a.y, b.y, g0.z, g0.w, lo.z, lo.w);
+          norm(a.z, b.z, g1.x, g1.y, hi.x, hi.y);
+          norm(a.w, b.w, g1.z, g1.w, hi.z, hi.w);
+          b4[swz16(2u * c)] = lo;
+          b4[swz16(2u * c + 1u)] = hi;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full0 + 8 * s);
+      return true;
+    };
+
+    PairRegs<CPP> ra, rb;
+    uint32_t unit = blockIdx.x, it = 0;
+    load_pair(unit, ra);
+    prefetch_l2(unit + stride);
+    while (unit < npairs) {
+      if (!produce(unit, it, ra, rb)) break;
+      unit += stride; ++it;
+      if (unit >= npairs) break;
+      if (!produce(unit, it, rb, ra)) break;
+      unit += stride; ++it;
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    const int warp = tid >> 5, lane = tid & 31, ncw = nct >> 5;
+    const size_t row_bytes = (size_t)(KQ + p.KE) / 2;
+    uint32_t it = 0;
+    int slot = warp;   // which 32 groups this warp takes; rotates so the critical groups move around
+    for (uint32_t unit = blockIdx.x; unit < npairs; unit += stride, ++it) {
+      const uint32_t s = it % S, ph = (it / S) & 1u;
+      const uint32_t r0 = 2 * unit;
+      const bool has1 = (r0 + 1) < rows;
+      uint8_t* q0 = p.q + (size_t)r0 * row_bytes;
+      uint8_t* sf0 = p.sf + sf_row_base((long long)r0, p.natoms);
+      const uint32_t q1off = has1 ? (uint32_t)row_bytes : 0u, sf1off = has1 ? 16u : 0u;
+      const uint8_t* buf = stages + (size_t)s * stage_bytes;
+      if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) break;
+      for (int g = slot * 32 + lane; g < G; g += nct) {
+        uint32_t w[16];
+        const uint4* op = reinterpret_cast<const uint4*>(offs32) + g;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 o = op[v * G];
+          w[4 * v + 0] = *reinterpret_cast<const uint32_t*>(buf + o.x);
+          w[4 * v + 1] = *reinterpret_cast<const uint32_t*>(buf + o.y);
+          w[4 * v + 2] = *reinterpret_cast<const uint32_t*>(buf + o.z);
+          w[4 * v + 3] = *reinterpret_cast<const uint32_t*>(buf + o.w);
+        }
+        if (g + nct >= G) {   // last group of this thread: the stage can be refilled (warp-uniform)
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty0 + 8 * s);
+        }
+        quantize_group_pair_ws(w, g, p, q0, q1off, sf0, sf1off);
+      }
+      slot = slot + 1 == ncw ? 0 : slot + 1;
+    }
+  }
+}
+
 __global__ void arcq_absmax_kernel(const uint4* __restrict__ x, long long nvec, const uint16_t* tail,
                                    int ntail, unsigned int* out) {
   uint32_t m = 0;
@@ -534,6 +886,20 @@ __global__ void arcq_absmax_kernel(const uint4* __restrict__ x, long long nvec, 
   for (int d = 16; d > 0; d >>= 1) r = max(r, __shfl_xor_sync(0xffffffffu, r, d));
   // non-negative floats order like their bit patterns
   if ((threadIdx.x & 31) == 0) atomicMax(out, r << 16);
+}
+
+template <bool RMS, int S>
+int launch_ws(const QuantParams& p, int nct, int npt, size_t smem, const DeviceInfo& di, cudaStream_t stream) {
+  auto kern = arcq_quantize_ws_kernel<RMS, S>;
+  ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int occ = 0;
+  ARCQ_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, nct + npt, smem));
+  if (occ < 1) return ARCQ_ERR_UNSUPPORTED_K;
+  long long grid = (long long)di.num_sms * occ;
+  if (grid > p.npairs) grid = p.npairs;
+  kern<<<(unsigned)grid, nct + npt, smem, stream>>>(p, nct, npt);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
 }
 
 template <int CPT, int NBUF, int PAIRS, bool RMS, bool RAWIDX, int MAXT, int MINB>
@@ -593,6 +959,31 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
     cpt = need <= 2 ? 2 : (need <= 4 ? 4 : 8);
   }
   const bool rawidx = KQ > 16384;
+
+  // Warp-specialised kernel for decoder-layer widths (ARCQ_QUANT_WS=0 falls back to the general one).
+  static const int ws_env = [] { const char* e = getenv("ARCQ_QUANT_WS"); return e ? atoi(e) : 1; }();
+  static const int stages_env = [] { const char* e = getenv("ARCQ_QUANT_STAGES"); return e ? atoi(e) : 0; }();
+  if (ws_env && p.dbg == 0 && p.G % 32 == 0 && p.G >= 64 && p.G <= 512 && rows < (1LL << 30)) {
+    const int nct = p.G < 256 ? p.G : 256;
+    const int npt = p.G;   // two 16-byte chunks of each row per producer thread
+    const size_t fixed = 160 + (size_t)KQ * 4 + (rms ? (size_t)KQ * 4 + (size_t)2 * npt * sizeof(float) + 16 : 0);
+    const size_t stage = (size_t)KQ * 4;
+    // as many stages (up to 4) as still leave room for two CTAs per SM; at least 2
+    int S = 4;
+    while (S > 2 && 2 * (fixed + S * stage + 1024) > (size_t)227 * 1024) --S;
+    if (stages_env >= 2 && stages_env <= 4) S = stages_env;
+    const size_t smem = fixed + S * stage;
+    if (smem <= (size_t)di.max_smem_optin) {
+      if (rms) {
+        if (S == 4) return launch_ws<true, 4>(p, nct, npt, smem, di, stream);
+        if (S == 3) return launch_ws<true, 3>(p, nct, npt, smem, di, stream);
+        return launch_ws<true, 2>(p, nct, npt, smem, di, stream);
+      }
+      if (S == 4) return launch_ws<false, 4>(p, nct, npt, smem, di, stream);
+      if (S == 3) return launch_ws<false, 3>(p, nct, npt, smem, di, stream);
+      return launch_ws<false, 2>(p, nct, npt, smem, di, stream);
+    }
+  }
   const size_t table = 160 + (((size_t)KQ * (rawidx ? 2 : 4) + 15) & ~(size_t)15);
   auto smem_for = [&](int nbuf, int pairs) {
     return table + (rms ? (size_t)KQ * 4 + (size_t)2 * pairs * nt * sizeof(float) + 16 : 0) +
@@ -623,6 +1014,14 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   if (rms) return launch_variant<2, 2, 1, true, false, 512, 1>(p, nt, smem, di, stream);
   if (cpt == 2) return launch_variant<2, 2, 1, false, false, 512, 1>(p, nt, smem, di, stream);
   return launch_variant<4, 2, 1, false, false, 512, 1>(p, nt, smem, di, stream);
+}
+
+int quant_poll_error() {
+  int v = 0, zero = 0;
+  ARCQ_CUDA_TRY(cudaDeviceSynchronize());
+  ARCQ_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_quant_error, sizeof(int)));
+  if (v) ARCQ_CUDA_TRY(cudaMemcpyToSymbol(g_quant_error, &zero, sizeof(int)));
+  return v;
 }
 
 int launch_absmax(const void* x, int64_t n, float* out, int accumulate, cudaStream_t stream) {

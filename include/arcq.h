@@ -150,9 +150,10 @@ int arcq_matmul_nvfp4_static(const uint8_t* A, const uint8_t* B, const uint8_t* 
                              int64_t M, int64_t N, int64_t K_eff, float alpha, const float* alpha_a,
                              const float* alpha_b, void* C, void* stream);
 
-/* The GEMM kernel bounds every wait on a barrier; if one ever expires the
- * kernel records it and returns.  This reads (and clears) that record for the
- * current device: ARCQ_OK or ARCQ_ERR_TIMEOUT.  Synchronises the device. */
+/* The GEMM kernels and the quantizer bound every wait on a barrier; if one
+ * ever expires the kernel records it and returns.  This reads (and clears)
+ * those records for the current device: ARCQ_OK or ARCQ_ERR_TIMEOUT.
+ * Synchronises the device. */
 int arcq_gemm_poll_error(void);
 
 /* One pass max|x| over n bf16 elements into *out (fp32, device memory; the

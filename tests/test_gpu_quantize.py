@@ -78,6 +78,28 @@ def test_rounding_boundaries_and_signed_zeros():
     _check("x", adversarial_rows(3584), None, 64, 32)
 
 
+@pytest.mark.parametrize("kq,ke,mode", [(1024, 64, 16), (4096, 128, 16), (3584, 64, 32), (1792, 64, 16)])
+def test_every_block_maximum(kq, ke, mode):
+    """Every finite bf16 magnitude (all 32640 bit patterns) as the maximum of some block: covers every
+    block scale the format has, the subnormal and the saturated ones included, in main and residual
+    slots."""
+    g = torch.Generator().manual_seed(kq)
+    groups = kq // 16
+    rows = (0x7f80 + groups - 1) // groups
+    bits = (torch.arange(rows * groups, dtype=torch.int32) % 0x7f80).reshape(rows, groups)
+    amax = (bits.to(torch.int16)).view(torch.bfloat16).float()                       # [rows, groups]
+    frac = torch.rand(rows, groups, 16, generator=g)
+    frac[..., 0] = 1.0
+    perm = torch.argsort(torch.rand(rows, groups, 16, generator=g), dim=-1)          # position of the maximum
+    frac = torch.gather(frac, -1, perm)
+    sign = torch.where(torch.rand(rows, groups, 16, generator=g) < 0.5, -1.0, 1.0)
+    x = (amax[..., None] * frac).to(torch.bfloat16).float() * sign
+    x = x.reshape(rows, kq).to(torch.bfloat16).contiguous()
+    _check("x", x, None, ke, mode)
+    idx = torch.randperm(kq, generator=g).to(torch.int16)
+    _check("x", x, idx, ke, mode)
+
+
 @pytest.mark.parametrize("kq", [2048, 3072, 3584, 4096, 5120, 8192])
 @pytest.mark.parametrize("tokens", [1, 130])
 def test_rmsnorm_quantize_x(kq, tokens):
