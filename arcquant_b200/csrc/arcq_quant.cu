@@ -70,6 +70,15 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+// a * b + c with a, b bf16 and c, result fp32 (one rounding): the mixed-precision FMA of sm_100.
+// With c = -0.0f it is the exact product a * b, signed zeros included.
+__device__ __forceinline__ float fma_bf16(uint16_t a, uint16_t b, float c) {
+  float d;
+  asm("fma.rn.f32.bf16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint16_t half_lo(uint32_t w) { return (uint16_t)(w & 0xffffu); }
+__device__ __forceinline__ uint16_t half_hi(uint32_t w) { return (uint16_t)(w >> 16); }
 // per-halfword unsigned max
 __device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
   uint32_t r;
@@ -281,10 +290,8 @@ __device__ __forceinline__ float rms_tree(const float* ps, int nt, int lane) {
   auto slot = [&](int k) { const int t = lane + 32 * k; return t < nt ? ps[t] : 0.f; };
   auto b = [&](int k) { return __fadd_rn(slot(k), slot(k + 8)); };       // +256
   auto c = [&](int k) { return __fadd_rn(b(k), b(k + 4)); };             // +128
-  float d[2];
-#pragma unroll 1
-  for (int h = 0; h < 2; ++h) d[h] = __fadd_rn(c(h), c(h + 2));          // +64 (rolled: keeps few values live)
-  float s = __fadd_rn(d[0], d[1]);                                       // +32
+  const float d0 = __fadd_rn(c(0), c(2)), d1 = __fadd_rn(c(1), c(3));    // +64
+  float s = __fadd_rn(d0, d1);                                           // +32
 #pragma unroll
   for (int d2 = 16; d2 > 0; d2 >>= 1) s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, d2));
   return s;  // valid in lane 0
@@ -531,6 +538,9 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
 // the approximate reciprocal plus one Newton step (exact here: a scale is k*2^e with k <= 15, so its
 // reciprocal lies far from every fp32 rounding boundary).
 
+#ifndef ARCQ_WAIT_HINT_NS
+#define ARCQ_WAIT_HINT_NS 0u
+#endif
 __device__ int g_quant_error = 0;   // sticky until polled
 constexpr unsigned long long QUANT_WAIT_LIMIT_NS = 2000000000ull;
 
@@ -543,6 +553,15 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#if ARCQ_WAIT_HINT_NS > 0
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"   // may sleep up to the hint (ns)
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ARCQ_WAIT_HINT_NS)
+      : "memory");
+#else
   asm volatile(
       "{\n.reg .pred p;\n"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
@@ -550,9 +569,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
+#endif
   return ok != 0;
 }
 // Bounded wait: false if this wait (or another warp's) gave up; the CTA then winds down.
+// (Polling from one lane with sleeps in between was measured slower: the hand-over latency counts.)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0;
@@ -662,183 +683,236 @@ __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g,
   sf0[cr] = (uint8_t)rcodes;
 }
 
-// 16-byte chunks of one row pair held by a producer thread.
-template <int CPP>
-struct PairRegs {
-  uint4 a[CPP], b[CPP];
-};
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completing on `bar`.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
 
-// S: ring stages.  RMS: fused RMSNorm.  There are KQ/16 producer threads with two 16-byte chunks of
-// each row apiece - chunk t and chunk t + KQ/16, the reference's assignment and summation order.
-// Threads [0, nct) are consumers, [nct, nct + npt) producers; both counts are multiples of 32.
-template <bool RMS, int S>
-__global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantParams p, const int nct, const int npt) {
-  constexpr int CPP = 2;
+// S: stages of the gather ring (interleaved row pairs).  R: stages of the raw ring (row pairs as they
+// lie in global memory, filled by bulk copies - this is what keeps enough bytes in flight to cover
+// the HBM latency).  RMS: fused RMSNorm.
+// Threads [0, nteams*nct) are consumers in teams of nct threads - team k takes the row pairs
+// k, k + nteams, ... of this CTA, so several pairs are being quantized at once.  After them come
+// npteams producer teams of npt = KQ/16 threads (more than one only with RMSNorm, whose producers carry
+// real arithmetic), sharing the pairs the same way; producer t of a team owns the 16-byte chunks t and
+// t + KQ/16 of each row, the reference's assignment and summation order for RMSNorm.
+template <bool RMS, int S, int R>
+__global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantParams p, const int nct, const int npt, const int nteams,
+                                                                        const int npteams) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x;
-  const int KQ = p.KQ, G = p.G, nchunks = p.nchunks;
+  const int KQ = p.KQ, G = p.G;
   const uint32_t rows = (uint32_t)p.rows, npairs = (uint32_t)p.npairs;
 
-  // shared layout: [full[S], empty[S] barriers, abort flag: 160 B][offsets][gain][partial sums, rstd][stages]
+  // shared layout: [barriers full[S] empty[S] raw[R], abort flag: 256 B][offsets][partial sums, rstd][gather ring][raw ring]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 128);
-  size_t cursor = 160;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 192);
+  size_t cursor = 256;
   uint32_t* offs32 = reinterpret_cast<uint32_t*>(smem + cursor);
   cursor += (size_t)KQ * 4;
-  float* gain = reinterpret_cast<float*>(smem + cursor);   // natural channel order
   float* psum = nullptr;
   float* rstd_s = nullptr;
   if (RMS) {
-    cursor += (size_t)KQ * 4;
     psum = reinterpret_cast<float*>(smem + cursor);
-    cursor += (size_t)2 * npt * sizeof(float);
+    cursor += (size_t)4 * npt * npteams * sizeof(float);   // per producer team: two buffers of two rows
     rstd_s = reinterpret_cast<float*>(smem + cursor);
-    cursor += 16;
+    cursor += (size_t)16 * npteams;
   }
   uint8_t* stages = smem + cursor;
   const uint32_t stage_bytes = (uint32_t)KQ * 4;
-  const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + S);
+  uint8_t* raw = stages + (size_t)S * stage_bytes;
+  const uint32_t row_in_bytes = (uint32_t)KQ * 2;
+  const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + S), raw0 = smem_addr(bars + 2 * S);
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, (uint32_t)(npt >> 5));    // one arrival per producer warp
-      mbar_init(empty0 + 8 * s, (uint32_t)(nct >> 5));   // one arrival per consumer warp
+      mbar_init(empty0 + 8 * s, (uint32_t)(nct >> 5));   // one arrival per warp of the consuming team
     }
-    *abort_flag = 0;
+    for (int r = 0; r < R; ++r) mbar_init(raw0 + 8 * r, 1);   // the thread that issues the copies
+    abort_flag[0] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int j = tid; j < KQ; j += blockDim.x) {
     const int c = p.idx ? (int)p.idx[j] : j;
     const int g = j >> 4, i = j & 15;
     offs32[(((i >> 2) * G + g) << 2) | (i & 3)] = word_offset((uint32_t)c);
-    if (RMS) gain[j] = __uint_as_float((uint32_t)p.gamma[j] << 16);
   }
   __syncthreads();
 
   const uint32_t stride = gridDim.x;
-  if (tid >= nct) {
+  const int ncons = nteams * nct;
+  if (tid >= ncons) {
     // ------------------------------------------------------------------ producers
-    const int ptid = tid - nct, lane = tid & 31, pwarp = ptid >> 5;
-    const uint4* xg = reinterpret_cast<const uint4*>(p.x);
-    auto load_pair = [&](uint32_t unit, PairRegs<CPP>& r) {
+    const int pteam = (tid - ncons) / npt, ptid = (tid - ncons) - pteam * npt;
+    const int lane = tid & 31, pwarp = ptid >> 5, bar_id = 1 + pteam;
+    const uint32_t NP = (uint32_t)npteams;
+    const int c0 = ptid, c1 = ptid + npt;   // this thread's 16-byte chunks
+    if (RMS) { psum += (size_t)pteam * 4 * npt; rstd_s += 4 * pteam; }
+    // Bulk copies of the rows of `unit` into raw stage `rs` (one thread).
+    auto issue = [&](uint32_t unit, uint32_t rs) {
+      if (unit >= npairs) return;
       const uint32_t r0 = 2 * unit;
-      const bool has0 = unit < npairs, has1 = has0 && (r0 + 1) < rows;
-      const uint4* x0 = xg + (size_t)r0 * (size_t)nchunks;
-      const uint4* x1 = x0 + nchunks;
-#pragma unroll
-      for (int j = 0; j < CPP; ++j) {
-        const int c = ptid + j * npt;
-        r.a[j] = has0 ? ldg_stream(x0 + c) : make_uint4(0, 0, 0, 0);
-        r.b[j] = has1 ? ldg_stream(x1 + c) : make_uint4(0, 0, 0, 0);
-      }
+      const bool has1 = (r0 + 1) < rows;
+      const uint32_t bar = raw0 + 8 * rs;
+      const uint32_t dst = smem_addr(raw + (size_t)rs * stage_bytes);
+      const uint16_t* src = p.x + (size_t)r0 * (size_t)KQ;
+      mbar_expect_tx(bar, has1 ? 2 * row_in_bytes : row_in_bytes);
+      bulk_load(dst, src, row_in_bytes, bar);
+      if (has1) bulk_load(dst + row_in_bytes, src + KQ, row_in_bytes, bar);
     };
-    auto prefetch_l2 = [&](uint32_t unit) {
-      if (ptid < 2) {
-        const uint32_t r = 2 * unit + ptid;
-        if (unit < npairs && r < rows)
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.x + (size_t)r * (size_t)KQ), "r"(KQ * 2)
-                       : "memory");
-      }
+    // RMSNorm gains of this thread's sixteen channels, kept packed (two bf16 per register)
+    uint4 gn0 = make_uint4(0, 0, 0, 0), gn1 = gn0;
+    if (RMS) {
+      gn0 = reinterpret_cast<const uint4*>(p.gamma)[c0];
+      gn1 = reinterpret_cast<const uint4*>(p.gamma)[c1];
+    }
+    if (ptid == 0)   // this team's pairs among the first R (R is a multiple of the number of teams)
+      for (uint32_t r = (uint32_t)pteam; r < (uint32_t)R; r += NP) issue(blockIdx.x + r * stride, r);
+
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    auto read_raw = [&](uint32_t j, bool has1, uint4& a0, uint4& a1, uint4& b0, uint4& b1) {
+      const uint4* rw = reinterpret_cast<const uint4*>(raw + (size_t)(j % R) * stage_bytes);
+      a0 = rw[c0]; a1 = rw[c1];
+      b0 = has1 ? rw[2 * npt + c0] : zero;
+      b1 = has1 ? rw[2 * npt + c1] : zero;
     };
-    bool failed = false;
-    // Fills stage (it % S) with the pair held in `cur` while `nxt` streams in.
-    auto produce = [&](uint32_t unit, uint32_t it, PairRegs<CPP>& cur, PairRegs<CPP>& nxt) {
-      load_pair(unit + stride, nxt);
-      prefetch_l2(unit + 2 * stride);
-      const uint32_t s = it % S, ph = (it / S) & 1u;
+    // Interleaves (and, with RMSNorm, normalises) this thread's chunks of pair j into its gather stage.
+    auto fill_stage = [&](uint32_t j, const uint4& a0, const uint4& a1, const uint4& b0, const uint4& b1,
+                          const float2 rstd) {
+      const uint32_t s = j % S;
       uint4* b4 = reinterpret_cast<uint4*>(stages + (size_t)s * stage_bytes);
-      if (!failed && !mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) failed = true;
-      if (!RMS) {
-        if (failed) return false;
-#pragma unroll
-        for (int j = 0; j < CPP; ++j) {
-          const int c = ptid + j * npt;
-          const uint4 a = cur.a[j], b = cur.b[j];
-          uint4 lo, hi;  // words of channels 8c..8c+3 and 8c+4..8c+7: (row0[ch], row1[ch]) per word
-          lo.x = __byte_perm(a.x, b.x, 0x5410); lo.y = __byte_perm(a.x, b.x, 0x7632);
-          lo.z = __byte_perm(a.y, b.y, 0x5410); lo.w = __byte_perm(a.y, b.y, 0x7632);
-          hi.x = __byte_perm(a.z, b.z, 0x5410); hi.y = __byte_perm(a.z, b.z, 0x7632);
-          hi.z = __byte_perm(a.w, b.w, 0x5410); hi.w = __byte_perm(a.w, b.w, 0x7632);
-          b4[swz16(2u * c)] = lo;
-          b4[swz16(2u * c + 1u)] = hi;
-        }
-      } else {
-        // Pass 1: sum of squares from the registers; the raw chunks are parked in this thread's own
-        // 32 bytes of the stage (so they need not stay in registers across the reduction).
-        // Reference thread t adds chunk t, then chunk t + KQ/16, eight elements each, in order.
-        float2 ss = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int j = 0; j < CPP; ++j) {
-          const int c = ptid + j * npt;
-          const uint32_t wa[4] = {cur.a[j].x, cur.a[j].y, cur.a[j].z, cur.a[j].w};
-          const uint32_t wb[4] = {cur.b[j].x, cur.b[j].y, cur.b[j].z, cur.b[j].w};
-          if (!failed) {
-            b4[swz16(2u * c)] = cur.a[j];
-            b4[swz16(2u * c + 1u)] = cur.b[j];
-          }
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 lo = make_float2(bf16lo(wa[i]), bf16lo(wb[i]));
-            const float2 hi = make_float2(bf16hi(wa[i]), bf16hi(wb[i]));
-            ss = __ffma2_rn(lo, lo, ss);
-            ss = __ffma2_rn(hi, hi, ss);
-          }
-        }
-        psum[ptid] = ss.x;
-        psum[npt + ptid] = ss.y;
-        if (named_barrier_or(1, npt, failed)) return false;   // every producer leaves together
-        if (pwarp < 2) {
-          const float t = rms_tree(psum + pwarp * npt, npt, lane);
-          if (lane == 0) rstd_s[pwarp] = __frsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)KQ), p.eps));
-        }
-        named_barrier_or(2, npt, false);
-        const float2 rstd = make_float2(rstd_s[0], rstd_s[1]);
-        // Pass 2: normalise and interleave in place.
-#pragma unroll
-        for (int j = 0; j < CPP; ++j) {
-          const int c = ptid + j * npt;
-          const uint4 a = b4[swz16(2u * c)], b = b4[swz16(2u * c + 1u)];
-          const float4 g0 = reinterpret_cast<const float4*>(gain)[2 * c];
-          const float4 g1 = reinterpret_cast<const float4*>(gain)[2 * c + 1];
+      auto fill = [&](int c, const uint4& a, const uint4& b, const uint4& g8) {
+        uint4 lo, hi;  // words of channels 8c..8c+3 and 8c+4..8c+7: (row0[ch], row1[ch]) per word
+        if (RMS) {
           // bf16 x bf16 is exact in fp32; then one rounding by rstd (both rows in one FMUL2), one to bf16
-          auto norm = [&](uint32_t wa, uint32_t wb, float ga, float gb, uint32_t& o0, uint32_t& o1) {
-            const float2 t0 = make_float2(__fmul_rn(bf16lo(wa), ga), __fmul_rn(bf16lo(wb), ga));
-            const float2 t1 = make_float2(__fmul_rn(bf16hi(wa), gb), __fmul_rn(bf16hi(wb), gb));
+          auto norm = [&](uint32_t wa, uint32_t wb, uint32_t gw, uint32_t& o0, uint32_t& o1) {
+            const uint16_t ga = half_lo(gw), gb = half_hi(gw);
+            const float2 t0 = make_float2(fma_bf16(half_lo(wa), ga, -0.0f), fma_bf16(half_lo(wb), ga, -0.0f));
+            const float2 t1 = make_float2(fma_bf16(half_hi(wa), gb, -0.0f), fma_bf16(half_hi(wb), gb, -0.0f));
             const float2 n0 = __fmul2_rn(t0, rstd), n1 = __fmul2_rn(t1, rstd);
             o0 = pack_bf16x2_rn(n0.x, n0.y);
             o1 = pack_bf16x2_rn(n1.x, n1.y);
           };
-          uint4 lo, hi;
-          norm(a.x, b.x, g0.x, g0.y, lo.x, lo.y);
-          norm(a.y, b.y, g0.z, g0.w, lo.z, lo.w);
-          norm(a.z, b.z, g1.x, g1.y, hi.x, hi.y);
-          norm(a.w, b.w, g1.z, g1.w, hi.z, hi.w);
-          b4[swz16(2u * c)] = lo;
-          b4[swz16(2u * c + 1u)] = hi;
+          norm(a.x, b.x, g8.x, lo.x, lo.y);
+          norm(a.y, b.y, g8.y, lo.z, lo.w);
+          norm(a.z, b.z, g8.z, hi.x, hi.y);
+          norm(a.w, b.w, g8.w, hi.z, hi.w);
+        } else {
+          lo.x = __byte_perm(a.x, b.x, 0x5410); lo.y = __byte_perm(a.x, b.x, 0x7632);
+          lo.z = __byte_perm(a.y, b.y, 0x5410); lo.w = __byte_perm(a.y, b.y, 0x7632);
+          hi.x = __byte_perm(a.z, b.z, 0x5410); hi.y = __byte_perm(a.z, b.z, 0x7632);
+          hi.z = __byte_perm(a.w, b.w, 0x5410); hi.w = __byte_perm(a.w, b.w, 0x7632);
         }
-      }
+        // XOR-swizzled 16-byte units: the eight lanes of a 128-bit store wavefront hit distinct banks
+        b4[swz16(2u * c)] = lo;
+        b4[swz16(2u * c + 1u)] = hi;
+      };
+      fill(c0, a0, b0, gn0);
+      fill(c1, a1, b1, gn1);
       __syncwarp();
       if (lane == 0) mbar_arrive(full0 + 8 * s);
-      return true;
     };
 
-    PairRegs<CPP> ra, rb;
-    uint32_t unit = blockIdx.x, it = 0;
-    load_pair(unit, ra);
-    prefetch_l2(unit + stride);
-    while (unit < npairs) {
-      if (!produce(unit, it, ra, rb)) break;
-      unit += stride; ++it;
-      if (unit >= npairs) break;
-      if (!produce(unit, it, rb, ra)) break;
-      unit += stride; ++it;
+    const uint32_t n = (npairs - blockIdx.x + stride - 1) / stride;   // row pairs of this CTA
+    // Copies in flight are tracked by pair number (this team's pairs: pteam, pteam + NP, ...):
+    uint32_t issued = (uint32_t)pteam;   // first pair of this team whose copies were NOT started yet
+    while (issued < n && issued < (uint32_t)R) issued += NP;
+    uint32_t landed = (uint32_t)pteam;   // first pair of this team whose copies were not waited for yet
+    bool failed = false;
+    if (!RMS) {
+      for (uint32_t it = 0; it < n; ++it) {
+        const uint32_t unit = blockIdx.x + it * stride;
+        const bool has1 = (2 * unit + 1) < rows;
+        if (!failed && !mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) failed = true;
+        if (!failed) landed = it + 1;
+        uint4 a0, a1, b0, b1;
+        read_raw(it, has1, a0, a1, b0, b1);
+        // Producers meet once per pair: every one of them has taken its chunks out of the raw stage,
+        // so it is refilled; and all leave together if any wait gave up.
+        if (named_barrier_or(bar_id, npt, failed)) break;
+        if (ptid == 0 && it + R < n) { issue(unit + R * stride, it % R); issued = it + R + 1; }
+        if (!mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag)) { failed = true; continue; }
+        fill_stage(it, a0, a1, b0, b1, make_float2(0.f, 0.f));
+      }
+    } else {
+      // Software pipeline with one meeting per iteration: sum of squares of this team's m-th pair
+      // (pass 1), then - while two warps finish that reduction - normalisation of its (m-1)-th pair
+      // (pass 2), whose chunks are read from the raw stage a second time rather than held in registers.
+      const uint32_t nt = n > (uint32_t)pteam ? (n - pteam + NP - 1) / NP : 0;   // pairs of this team
+      for (uint32_t m = 0; m <= nt; ++m) {
+        const uint32_t it = pteam + m * NP;               // pair number within the CTA
+        const uint32_t unit = blockIdx.x + it * stride;   // (only used when it exists)
+        if (m < nt) {
+          const bool has1 = (2 * unit + 1) < rows;
+          if (!failed && !mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) failed = true;
+          if (!failed) landed = it + NP;
+          uint4 a0, a1, b0, b1;
+          read_raw(it, has1, a0, a1, b0, b1);
+          // reference thread t adds chunk t, then chunk t + KQ/16, eight elements each, in order
+          float ss0 = 0.f, ss1 = 0.f;   // x*x is exact in fp32, so each step rounds once, like the fp32 FMA
+          const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+          const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            ss0 = fma_bf16(half_lo(wa[i]), half_lo(wa[i]), ss0);
+            ss1 = fma_bf16(half_lo(wb[i]), half_lo(wb[i]), ss1);
+            ss0 = fma_bf16(half_hi(wa[i]), half_hi(wa[i]), ss0);
+            ss1 = fma_bf16(half_hi(wb[i]), half_hi(wb[i]), ss1);
+          }
+          float* ps = psum + (size_t)(m & 1u) * 2 * npt;
+          ps[ptid] = ss0;
+          ps[npt + ptid] = ss1;
+        }
+        if (named_barrier_or(bar_id, npt, failed)) break;
+        // the raw stage of this team's pair m-2 was read for the second time in the previous
+        // iteration: refill it (with the pair R further on, which is this team's as well)
+        if (ptid == 0 && m >= 2) {
+          const uint32_t old = it - 2 * NP;
+          if (old + R < n) { issue(blockIdx.x + (old + R) * stride, old % R); issued = old + R + NP; }
+        }
+        if (m < nt && pwarp < 2) {
+          const float t = rms_tree(psum + (size_t)(m & 1u) * 2 * npt + pwarp * npt, npt, lane);
+          if (lane == 0) rstd_s[(m & 1u) * 2 + pwarp] = __frsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)KQ), p.eps));
+        }
+        if (m >= 1) {
+          const uint32_t j = it - NP;
+          const bool has1 = (2 * (blockIdx.x + j * stride) + 1) < rows;
+          const float2 rstd = make_float2(rstd_s[((m - 1) & 1u) * 2], rstd_s[((m - 1) & 1u) * 2 + 1]);
+          if (!mbar_wait(empty0 + 8 * (j % S), ((j / S) & 1u) ^ 1u, abort_flag)) { failed = true; continue; }
+          uint4 a0, a1, b0, b1;
+          read_raw(j, has1, a0, a1, b0, b1);
+          fill_stage(j, a0, a1, b0, b1, rstd);
+        }
+      }
+    }
+    // Giving up with bulk copies possibly in flight: wait (bounded) for those this CTA started, so that
+    // none lands in shared memory after the CTA has gone.
+    if (failed && ptid == 0) {
+      for (uint32_t j = landed; j < issued; j += NP) {
+        unsigned long long t0, t1;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+        while (!mbar_try_wait(raw0 + 8 * (j % R), (j / R) & 1u)) {
+          __nanosleep(256);
+          asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+          if (t1 - t0 > QUANT_WAIT_LIMIT_NS) break;
+        }
+      }
     }
   } else {
     // ------------------------------------------------------------------ consumers
-    const int warp = tid >> 5, lane = tid & 31, ncw = nct >> 5;
+    const int team = tid / nct, ctid = tid - team * nct;
+    const int warp = ctid >> 5, lane = tid & 31, ncw = nct >> 5;
     const size_t row_bytes = (size_t)(KQ + p.KE) / 2;
-    uint32_t it = 0;
     int slot = warp;   // which 32 groups this warp takes; rotates so the critical groups move around
-    for (uint32_t unit = blockIdx.x; unit < npairs; unit += stride, ++it) {
+    // (npairs < 2^29 and at most a few grid strides beyond it: 32-bit unit numbers do not wrap)
+    uint32_t it = (uint32_t)team;
+    for (uint32_t unit = blockIdx.x + it * stride; unit < npairs; unit += (uint32_t)nteams * stride, it += (uint32_t)nteams) {
       const uint32_t s = it % S, ph = (it / S) & 1u;
       const uint32_t r0 = 2 * unit;
       const bool has1 = (r0 + 1) < rows;
@@ -888,16 +962,18 @@ __global__ void arcq_absmax_kernel(const uint4* __restrict__ x, long long nvec, 
   if ((threadIdx.x & 31) == 0) atomicMax(out, r << 16);
 }
 
-template <bool RMS, int S>
-int launch_ws(const QuantParams& p, int nct, int npt, size_t smem, const DeviceInfo& di, cudaStream_t stream) {
-  auto kern = arcq_quantize_ws_kernel<RMS, S>;
+template <bool RMS, int S, int R>
+int launch_ws(const QuantParams& p, int nct, int npt, int nteams, int npteams, size_t smem, const DeviceInfo& di,
+              cudaStream_t stream) {
+  auto kern = arcq_quantize_ws_kernel<RMS, S, R>;
   ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int occ = 0;
-  ARCQ_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, nct + npt, smem));
+  const int threads = nteams * nct + npteams * npt;
+  ARCQ_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, smem));
   if (occ < 1) return ARCQ_ERR_UNSUPPORTED_K;
   long long grid = (long long)di.num_sms * occ;
   if (grid > p.npairs) grid = p.npairs;
-  kern<<<(unsigned)grid, nct + npt, smem, stream>>>(p, nct, npt);
+  kern<<<(unsigned)grid, threads, smem, stream>>>(p, nct, npt, nteams, npteams);
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
 }
@@ -962,26 +1038,47 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
 
   // Warp-specialised kernel for decoder-layer widths (ARCQ_QUANT_WS=0 falls back to the general one).
   static const int ws_env = [] { const char* e = getenv("ARCQ_QUANT_WS"); return e ? atoi(e) : 1; }();
-  static const int stages_env = [] { const char* e = getenv("ARCQ_QUANT_STAGES"); return e ? atoi(e) : 0; }();
-  if (ws_env && p.dbg == 0 && p.G % 32 == 0 && p.G >= 64 && p.G <= 512 && rows < (1LL << 30)) {
+  static const int raw_env = [] { const char* e = getenv("ARCQ_QUANT_RAW"); return e ? atoi(e) : 0; }();
+  const bool gamma_ok = !rms || (reinterpret_cast<uintptr_t>(gamma) & 15u) == 0;   // read with 128-bit loads
+  if (ws_env && p.dbg == 0 && gamma_ok && p.G % 32 == 0 && p.G >= 64 && p.G <= 512 && rows < (1LL << 30)) {
     const int nct = p.G < 256 ? p.G : 256;
     const int npt = p.G;   // two 16-byte chunks of each row per producer thread
-    const size_t fixed = 160 + (size_t)KQ * 4 + (rms ? (size_t)KQ * 4 + (size_t)2 * npt * sizeof(float) + 16 : 0);
     const size_t stage = (size_t)KQ * 4;
-    // as many stages (up to 4) as still leave room for two CTAs per SM; at least 2
-    int S = 4;
-    while (S > 2 && 2 * (fixed + S * stage + 1024) > (size_t)227 * 1024) --S;
-    if (stages_env >= 2 && stages_env <= 4) S = stages_env;
-    const size_t smem = fixed + S * stage;
+    // One CTA per SM, up to 1024 threads.  Plain: one producer team (it only moves data) and up to three
+    // consumer teams.  RMSNorm: two producer teams if two consumer teams still fit beside them.
+    static const int stages_env = [] { const char* e = getenv("ARCQ_QUANT_STAGES"); return e ? atoi(e) : 0; }();
+    static const int teams_env = [] { const char* e = getenv("ARCQ_QUANT_TEAMS"); return e ? atoi(e) : 0; }();
+    static const int pteams_env = [] { const char* e = getenv("ARCQ_QUANT_PTEAMS"); return e ? atoi(e) : 0; }();
+    // Measured best on B200 for hidden 4096: RMSNorm 2 producer + 1 consumer team, plain 1 + 3.
+    int npteams = (rms && 2 * npt + nct <= 1024) ? 2 : 1;
+    if (rms && (pteams_env == 1 || pteams_env == 2) && pteams_env * npt + nct <= 1024) npteams = pteams_env;
+    int nteams = rms ? 1 : (1024 - npteams * npt) / nct;
+    if (nteams > 3) nteams = 3;
+    if (teams_env >= 1 && teams_env <= 3 && teams_env * nct + npteams * npt <= 1024) nteams = teams_env;
+    // gather stages: 2 for a single consumer team, else 4.  Raw stages: a multiple of the number of
+    // producer teams; the RMSNorm pipeline keeps two pairs per team resident and refills a stage two
+    // iterations after its first use, so it needs at least three stages per team to make progress.
+    int S = nteams > 1 ? 4 : 2;
+    if (stages_env == 2 || stages_env == 4) S = stages_env;
+    const int r_min = rms ? (npteams == 2 ? 6 : 4) : 2;
+    size_t fixed = 256 + (size_t)KQ * 4 + (rms ? ((size_t)4 * npt * sizeof(float) + 16) * npteams : 0);
+    if (rms && npteams == 2 && fixed + (S + r_min) * stage > (size_t)di.max_smem_optin) {
+      npteams = 1;   // not enough shared memory for two pipelines
+      fixed = 256 + (size_t)KQ * 4 + (size_t)4 * npt * sizeof(float) + 16;
+    }
+    const int r_floor = rms ? (npteams == 2 ? 6 : 4) : 2;
+    int R = 8;
+    while (R > r_floor && fixed + (S + R) * stage > (size_t)di.max_smem_optin) R -= 2;
+    if ((raw_env == 2 || raw_env == 4 || raw_env == 6 || raw_env == 8) && raw_env >= r_floor) R = raw_env;
+    const size_t smem = fixed + (S + R) * stage;
     if (smem <= (size_t)di.max_smem_optin) {
-      if (rms) {
-        if (S == 4) return launch_ws<true, 4>(p, nct, npt, smem, di, stream);
-        if (S == 3) return launch_ws<true, 3>(p, nct, npt, smem, di, stream);
-        return launch_ws<true, 2>(p, nct, npt, smem, di, stream);
-      }
-      if (S == 4) return launch_ws<false, 4>(p, nct, npt, smem, di, stream);
-      if (S == 3) return launch_ws<false, 3>(p, nct, npt, smem, di, stream);
-      return launch_ws<false, 2>(p, nct, npt, smem, di, stream);
+#define ARCQ_WS_CASE(RMS_, S_, R_) \
+  if (rms == RMS_ && S == S_ && R == R_) return launch_ws<RMS_, S_, R_>(p, nct, npt, nteams, npteams, smem, di, stream);
+#define ARCQ_WS_ROW(RMS_, S_) \
+  ARCQ_WS_CASE(RMS_, S_, 2) ARCQ_WS_CASE(RMS_, S_, 4) ARCQ_WS_CASE(RMS_, S_, 6) ARCQ_WS_CASE(RMS_, S_, 8)
+      ARCQ_WS_ROW(true, 2) ARCQ_WS_ROW(true, 4) ARCQ_WS_ROW(false, 2) ARCQ_WS_ROW(false, 4)
+#undef ARCQ_WS_ROW
+#undef ARCQ_WS_CASE
     }
   }
   const size_t table = 160 + (((size_t)KQ * (rawidx ? 2 : 4) + 15) & ~(size_t)15);
