@@ -35,9 +35,10 @@ KE = 128
 TOKENS = 32768
 EPS = 1e-5
 BYTES_PER_TOKEN = 2 * HIDDEN + (HIDDEN + KE) // 2 + (HIDDEN + KE) // 16      # 10568
-# dram__bytes_read + dram__bytes_write per token of the ncu capture under profiles/ (the output mostly
-# stays dirty in L2 while the kernel runs, so the write part is small): (134.27 + 7.53) MB / 16384 tokens
-TRAFFIC_PER_TOKEN_NCU = 8655
+# dram__bytes_read + dram__bytes_write per token of the ncu capture under profiles/ (part of the output
+# stays dirty in L2 while the kernel runs, so the write part is below the algorithmic 2376 B/token):
+# (134.27 + 18.37) MB / 16384 tokens
+TRAFFIC_PER_TOKEN_NCU = 9316
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
@@ -365,16 +366,10 @@ def run_ours(args):
     ms_step = ms_total / args.steps
     value = world * tokens * BYTES_PER_TOKEN / (ms_step * 1e-3) / 1e9
 
-    # per-launch duration of the dominant kernel, measured live on its stream
-    lat = []
-    for _ in range(min(args.steps, 20)):
-        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a0.record()
-        step()
-        a1.record()
-        torch.cuda.synchronize()
-        lat.append(a0.elapsed_time(a1))
-    launch_ms = sum(lat) / len(lat)
+    # Average launch duration of the dominant kernel: every step of the timed region is exactly one
+    # launch of it, issued back to back on the current stream, so the region's CUDA-event time divided
+    # by the launches is the per-launch duration (any gap between launches only makes it larger).
+    launch_ms = ms_step
     algo_bytes = tokens * BYTES_PER_TOKEN + (2 if plain else 4) * HIDDEN
     achieved = algo_bytes / (launch_ms * 1e-3) / 1e9
 
@@ -455,7 +450,7 @@ def run_ours(args):
                    "l2": "step touches 346 MB > 126 MB L2, no flush needed", "parallelism": f"tokens sharded x{world}"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "traffic": TRAFFIC_PER_TOKEN_NCU * tokens, "traffic_source": "ncu capture of a 16384-token launch "
-                     "(profiles/), scaled by tokens", "peak_kind": peak_kind, "kernel": "arcq_quantize_kernel<2,2,RMS>",
+                     "(profiles/), scaled by tokens", "peak_kind": peak_kind, "kernel": "arcq_quantize_ws_kernel<RMS>" if not plain else "arcq_quantize_ws_kernel<plain>",
                      "launch_ms": launch_ms, "algorithmic_bytes_per_launch": algo_bytes},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": int(hx.numel() * 2),
