@@ -709,10 +709,10 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   const int KQ = p.KQ, G = p.G;
   const uint32_t rows = (uint32_t)p.rows, npairs = (uint32_t)p.npairs;
 
-  // shared layout: [barriers full[S] empty[S] raw[R], abort flag: 256 B][offsets][partial sums, rstd][gather ring][raw ring]
+  // shared layout: [barriers, abort flag: 384 B][offsets][partial sums, rstd][gather ring][raw ring]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 192);
-  size_t cursor = 256;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 376);
+  size_t cursor = 384;
   uint32_t* offs32 = reinterpret_cast<uint32_t*>(smem + cursor);
   cursor += (size_t)KQ * 4;
   float* psum = nullptr;
@@ -728,6 +728,9 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   uint8_t* raw = stages + (size_t)S * stage_bytes;
   const uint32_t row_in_bytes = (uint32_t)KQ * 2;
   const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + S), raw0 = smem_addr(bars + 2 * S);
+  // RMSNorm only: raw stage handed back to the loader; per producer team, partial sums ready (x2
+  // buffers) and reciprocal roots ready (x2)
+  const uint32_t rawe0 = raw0 + 8 * R, psr0 = rawe0 + 8 * R, rsr0 = psr0 + 8 * 4;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -735,6 +738,13 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       mbar_init(empty0 + 8 * s, (uint32_t)(nct >> 5));   // one arrival per warp of the consuming team
     }
     for (int r = 0; r < R; ++r) mbar_init(raw0 + 8 * r, 1);   // the thread that issues the copies
+    if (RMS) {
+      for (int r = 0; r < R; ++r) mbar_init(rawe0 + 8 * r, (uint32_t)(npt >> 5));   // one arrival per producer warp
+      for (int k = 0; k < 4; ++k) {
+        mbar_init(psr0 + 8 * k, (uint32_t)(npt >> 5));
+        mbar_init(rsr0 + 8 * k, 2);                                                 // the two reducer warps
+      }
+    }
     abort_flag[0] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -749,11 +759,18 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   const int ncons = nteams * nct;
   if (tid >= ncons) {
     // ------------------------------------------------------------------ producers
-    const int pteam = (tid - ncons) / npt, ptid = (tid - ncons) - pteam * npt;
-    const int lane = tid & 31, pwarp = ptid >> 5, bar_id = 1 + pteam;
+    // A producer team is npt producers and, with RMSNorm, three helper warps behind them: two reducers
+    // (one per row of the pair: they finish the sum of squares of pair m while the producers normalise
+    // pair m-1) and a loader (one thread that starts the bulk copies).
+    const int team_threads = npt + (RMS ? 96 : 0);
+    const int pteam = (tid - ncons) / team_threads, ptid = (tid - ncons) - pteam * team_threads;
+    const int lane = tid & 31, bar_id = 1 + pteam;
     const uint32_t NP = (uint32_t)npteams;
     const int c0 = ptid, c1 = ptid + npt;   // this thread's 16-byte chunks
     if (RMS) { psum += (size_t)pteam * 4 * npt; rstd_s += 4 * pteam; }
+    const uint32_t n = (npairs - blockIdx.x + stride - 1) / stride;   // row pairs of this CTA
+    const uint32_t nt = n > (uint32_t)pteam ? (n - pteam + NP - 1) / NP : 0;   // pairs of this team
+    const uint32_t psr = psr0 + 16 * pteam, rsr = rsr0 + 16 * pteam;           // this team's barrier pairs
     // Bulk copies of the rows of `unit` into raw stage `rs` (one thread).
     auto issue = [&](uint32_t unit, uint32_t rs) {
       if (unit >= npairs) return;
@@ -766,14 +783,71 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       bulk_load(dst, src, row_in_bytes, bar);
       if (has1) bulk_load(dst + row_in_bytes, src + KQ, row_in_bytes, bar);
     };
+    if (RMS && ptid >= npt) {
+      const int helper = (ptid - npt) >> 5;
+      if (helper < 2) {
+        // -------------------------------------------------------------- reducers (row = helper)
+        for (uint32_t m = 0; m < nt; ++m) {
+          if (!mbar_wait(psr + 8 * (m & 1u), (m >> 1) & 1u, abort_flag)) break;
+          const float t = rms_tree(psum + (size_t)(m & 1u) * 2 * npt + helper * npt, npt, lane);
+          if (lane == 0) {
+            rstd_s[(m & 1u) * 2 + helper] = __frsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)KQ), p.eps));
+            mbar_arrive(rsr + 8 * (m & 1u));
+          }
+        }
+      } else if (lane == 0) {
+        // -------------------------------------------------------------- loader
+        uint32_t next = (uint32_t)pteam;    // first pair of this team whose copies are not started yet
+        for (; next < n && next < (uint32_t)R; next += NP) issue(blockIdx.x + next * stride, next % R);
+        // Stay until the producers have taken the team's last pair (or the CTA aborts): every stage that
+        // comes back is refilled with the pair R further on, while there is one.
+        uint32_t freed = (uint32_t)pteam;   // first pair of this team whose stage is not handed back yet
+        bool ok = true;
+        for (; freed < n; freed += NP) {
+          const uint32_t bar = rawe0 + 8 * (freed % R), par = (freed / R) & 1u;
+          if (!mbar_try_wait(bar, par)) {
+            unsigned long long t0, t1;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+            for (uint32_t spin = 1; !mbar_try_wait(bar, par); ++spin) {
+              if ((spin & 255u) == 0) {
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+                if (*abort_flag) { ok = false; break; }
+                if (t1 - t0 > QUANT_WAIT_LIMIT_NS) {
+                  *abort_flag = 1;
+                  atomicExch(&g_quant_error, ARCQ_ERR_TIMEOUT);
+                  ok = false;
+                  break;
+                }
+              }
+            }
+            if (!ok) break;
+          }
+          if (next < n) { issue(blockIdx.x + next * stride, freed % R); next += NP; }
+        }
+        if (!ok) {
+          // Giving up with bulk copies possibly in flight: wait (bounded) for those started here, so
+          // that none lands in shared memory after the CTA has gone.
+          for (uint32_t j = freed; j < next && j < n; j += NP) {
+            unsigned long long t0, t1;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+            while (!mbar_try_wait(raw0 + 8 * (j % R), (j / R) & 1u)) {
+              __nanosleep(256);
+              asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+              if (t1 - t0 > QUANT_WAIT_LIMIT_NS) break;
+            }
+          }
+        }
+      }
+      return;
+    }
     // RMSNorm gains of this thread's sixteen channels, kept packed (two bf16 per register)
     uint4 gn0 = make_uint4(0, 0, 0, 0), gn1 = gn0;
     if (RMS) {
       gn0 = reinterpret_cast<const uint4*>(p.gamma)[c0];
       gn1 = reinterpret_cast<const uint4*>(p.gamma)[c1];
     }
-    if (ptid == 0)   // this team's pairs among the first R (R is a multiple of the number of teams)
-      for (uint32_t r = (uint32_t)pteam; r < (uint32_t)R; r += NP) issue(blockIdx.x + r * stride, r);
+    if (!RMS && ptid == 0)   // (with RMSNorm the loader warp starts the copies)
+      for (uint32_t r = 0; r < (uint32_t)R; ++r) issue(blockIdx.x + r * stride, r);
 
     const uint4 zero = make_uint4(0, 0, 0, 0);
     auto read_raw = [&](uint32_t j, bool has1, uint4& a0, uint4& a1, uint4& b0, uint4& b1) {
@@ -819,7 +893,6 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       if (lane == 0) mbar_arrive(full0 + 8 * s);
     };
 
-    const uint32_t n = (npairs - blockIdx.x + stride - 1) / stride;   // row pairs of this CTA
     // Copies in flight are tracked by pair number (this team's pairs: pteam, pteam + NP, ...):
     uint32_t issued = (uint32_t)pteam;   // first pair of this team whose copies were NOT started yet
     while (issued < n && issued < (uint32_t)R) issued += NP;
@@ -835,24 +908,30 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
         read_raw(it, has1, a0, a1, b0, b1);
         // Producers meet once per pair: every one of them has taken its chunks out of the raw stage,
         // so it is refilled; and all leave together if any wait gave up.
-        if (named_barrier_or(bar_id, npt, failed)) break;
+        if (named_barrier_or(bar_id, team_threads, failed)) break;
         if (ptid == 0 && it + R < n) { issue(unit + R * stride, it % R); issued = it + R + 1; }
         if (!mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag)) { failed = true; continue; }
         fill_stage(it, a0, a1, b0, b1, make_float2(0.f, 0.f));
       }
     } else {
-      // Software pipeline with one meeting per iteration: sum of squares of this team's m-th pair
-      // (pass 1), then - while two warps finish that reduction - normalisation of its (m-1)-th pair
-      // (pass 2), whose chunks are read from the raw stage a second time rather than held in registers.
-      const uint32_t nt = n > (uint32_t)pteam ? (n - pteam + NP - 1) / NP : 0;   // pairs of this team
+      // Software pipeline, synchronised by mbarriers only: normalise and hand over this team's pair
+      // m-1 (pass 2, its chunks still in registers; the reducers had a whole iteration for its sum),
+      // then take pair m out of its raw stage, give the stage back to the loader, and accumulate its
+      // sum of squares (pass 1).
+      uint4 a0 = zero, a1 = zero, b0 = zero, b1 = zero;
       for (uint32_t m = 0; m <= nt; ++m) {
         const uint32_t it = pteam + m * NP;               // pair number within the CTA
-        const uint32_t unit = blockIdx.x + it * stride;   // (only used when it exists)
+        if (m >= 1) {
+          const uint32_t j = it - NP, q = m - 1;
+          if (!mbar_wait(rsr + 8 * (q & 1u), (q >> 1) & 1u, abort_flag)) break;
+          const float2 rstd = make_float2(rstd_s[(q & 1u) * 2], rstd_s[(q & 1u) * 2 + 1]);
+          if (!mbar_wait(empty0 + 8 * (j % S), ((j / S) & 1u) ^ 1u, abort_flag)) break;
+          fill_stage(j, a0, a1, b0, b1, rstd);
+        }
         if (m < nt) {
+          const uint32_t unit = blockIdx.x + it * stride;
           const bool has1 = (2 * unit + 1) < rows;
-          if (!failed && !mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) failed = true;
-          if (!failed) landed = it + NP;
-          uint4 a0, a1, b0, b1;
+          if (!mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) break;
           read_raw(it, has1, a0, a1, b0, b1);
           // reference thread t adds chunk t, then chunk t + KQ/16, eight elements each, in order
           float ss0 = 0.f, ss1 = 0.f;   // x*x is exact in fp32, so each step rounds once, like the fp32 FMA
@@ -868,32 +947,17 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
           float* ps = psum + (size_t)(m & 1u) * 2 * npt;
           ps[ptid] = ss0;
           ps[npt + ptid] = ss1;
-        }
-        if (named_barrier_or(bar_id, npt, failed)) break;
-        // the raw stage of this team's pair m-2 was read for the second time in the previous
-        // iteration: refill it (with the pair R further on, which is this team's as well)
-        if (ptid == 0 && m >= 2) {
-          const uint32_t old = it - 2 * NP;
-          if (old + R < n) { issue(blockIdx.x + (old + R) * stride, old % R); issued = old + R + NP; }
-        }
-        if (m < nt && pwarp < 2) {
-          const float t = rms_tree(psum + (size_t)(m & 1u) * 2 * npt + pwarp * npt, npt, lane);
-          if (lane == 0) rstd_s[(m & 1u) * 2 + pwarp] = __frsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)KQ), p.eps));
-        }
-        if (m >= 1) {
-          const uint32_t j = it - NP;
-          const bool has1 = (2 * (blockIdx.x + j * stride) + 1) < rows;
-          const float2 rstd = make_float2(rstd_s[((m - 1) & 1u) * 2], rstd_s[((m - 1) & 1u) * 2 + 1]);
-          if (!mbar_wait(empty0 + 8 * (j % S), ((j / S) & 1u) ^ 1u, abort_flag)) { failed = true; continue; }
-          uint4 a0, a1, b0, b1;
-          read_raw(j, has1, a0, a1, b0, b1);
-          fill_stage(j, a0, a1, b0, b1, rstd);
+          __syncwarp();   // every lane has its chunks in registers and its partial sums in place
+          if (lane == 0) {
+            mbar_arrive(rawe0 + 8 * (it % R));
+            mbar_arrive(psr + 8 * (m & 1u));
+          }
         }
       }
     }
     // Giving up with bulk copies possibly in flight: wait (bounded) for those this CTA started, so that
     // none lands in shared memory after the CTA has gone.
-    if (failed && ptid == 0) {
+    if (!RMS && failed && ptid == 0) {
       for (uint32_t j = landed; j < issued; j += NP) {
         unsigned long long t0, t1;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
@@ -968,7 +1032,7 @@ int launch_ws(const QuantParams& p, int nct, int npt, int nteams, int npteams, s
   auto kern = arcq_quantize_ws_kernel<RMS, S, R>;
   ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int occ = 0;
-  const int threads = nteams * nct + npteams * npt;
+  const int threads = nteams * nct + npteams * (npt + (RMS ? 96 : 0));
   ARCQ_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, smem));
   if (occ < 1) return ARCQ_ERR_UNSUPPORTED_K;
   long long grid = (long long)di.num_sms * occ;
@@ -1050,23 +1114,23 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
     static const int teams_env = [] { const char* e = getenv("ARCQ_QUANT_TEAMS"); return e ? atoi(e) : 0; }();
     static const int pteams_env = [] { const char* e = getenv("ARCQ_QUANT_PTEAMS"); return e ? atoi(e) : 0; }();
     // Measured best on B200 for hidden 4096: RMSNorm 2 producer + 1 consumer team, plain 1 + 3.
-    int npteams = (rms && 2 * npt + nct <= 1024) ? 2 : 1;
-    if (rms && (pteams_env == 1 || pteams_env == 2) && pteams_env * npt + nct <= 1024) npteams = pteams_env;
-    int nteams = rms ? 1 : (1024 - npteams * npt) / nct;
+    const int ptt = npt + (rms ? 96 : 0);   // threads of a producer team (RMSNorm adds three helper warps)
+    int npteams = (rms && 2 * ptt + nct <= 1024) ? 2 : 1;
+    if (rms && (pteams_env == 1 || pteams_env == 2) && pteams_env * ptt + nct <= 1024) npteams = pteams_env;
+    int nteams = rms ? 1 : (1024 - npteams * ptt) / nct;
     if (nteams > 3) nteams = 3;
-    if (teams_env >= 1 && teams_env <= 3 && teams_env * nct + npteams * npt <= 1024) nteams = teams_env;
+    if (teams_env >= 1 && teams_env <= 3 && teams_env * nct + npteams * ptt <= 1024) nteams = teams_env;
     // gather stages: 2 for a single consumer team, else 4.  Raw stages: a multiple of the number of
-    // producer teams; the RMSNorm pipeline keeps two pairs per team resident and refills a stage two
-    // iterations after its first use, so it needs at least three stages per team to make progress.
+    // producer teams (a stage always serves pairs of the same team), at least two per team.
     int S = nteams > 1 ? 4 : 2;
     if (stages_env == 2 || stages_env == 4) S = stages_env;
-    const int r_min = rms ? (npteams == 2 ? 6 : 4) : 2;
-    size_t fixed = 256 + (size_t)KQ * 4 + (rms ? ((size_t)4 * npt * sizeof(float) + 16) * npteams : 0);
+    const int r_min = rms ? 2 * npteams : 2;
+    size_t fixed = 384 + (size_t)KQ * 4 + (rms ? ((size_t)4 * npt * sizeof(float) + 16) * npteams : 0);
     if (rms && npteams == 2 && fixed + (S + r_min) * stage > (size_t)di.max_smem_optin) {
       npteams = 1;   // not enough shared memory for two pipelines
-      fixed = 256 + (size_t)KQ * 4 + (size_t)4 * npt * sizeof(float) + 16;
+      fixed = 384 + (size_t)KQ * 4 + (size_t)4 * npt * sizeof(float) + 16;
     }
-    const int r_floor = rms ? (npteams == 2 ? 6 : 4) : 2;
+    const int r_floor = rms ? 2 * npteams : 2;
     int R = 8;
     while (R > r_floor && fixed + (S + R) * stage > (size_t)di.max_smem_optin) R -= 2;
     if ((raw_env == 2 || raw_env == 4 || raw_env == 6 || raw_env == 8) && raw_env >= r_floor) R = raw_env;
