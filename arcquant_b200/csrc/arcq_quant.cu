@@ -1105,7 +1105,11 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   static const int raw_env = [] { const char* e = getenv("ARCQ_QUANT_RAW"); return e ? atoi(e) : 0; }();
   const bool gamma_ok = !rms || (reinterpret_cast<uintptr_t>(gamma) & 15u) == 0;   // read with 128-bit loads
   if (ws_env && p.dbg == 0 && gamma_ok && p.G % 32 == 0 && p.G >= 64 && p.G <= 512 && rows < (1LL << 30)) {
-    const int nct = p.G < 256 ? p.G : 256;
+    // Consumer teams of 128 threads (two groups per thread at hidden 4096) were measured faster than
+    // teams of 256: more row pairs in flight for the same number of warps.
+    static const int nct_env = [] { const char* e = getenv("ARCQ_QUANT_NCT"); return e ? atoi(e) : 0; }();
+    int nct = p.G < 128 ? p.G : 128;
+    if (nct_env >= 32 && nct_env % 32 == 0 && nct_env <= p.G && nct_env <= 256) nct = nct_env;
     const int npt = p.G;   // two 16-byte chunks of each row per producer thread
     const size_t stage = (size_t)KQ * 4;
     // One CTA per SM, up to 1024 threads.  Plain: one producer team (it only moves data) and up to three
@@ -1113,11 +1117,11 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
     static const int stages_env = [] { const char* e = getenv("ARCQ_QUANT_STAGES"); return e ? atoi(e) : 0; }();
     static const int teams_env = [] { const char* e = getenv("ARCQ_QUANT_TEAMS"); return e ? atoi(e) : 0; }();
     static const int pteams_env = [] { const char* e = getenv("ARCQ_QUANT_PTEAMS"); return e ? atoi(e) : 0; }();
-    // Measured best on B200 for hidden 4096: RMSNorm 2 producer + 1 consumer team, plain 1 + 3.
+    // Measured best on B200 for hidden 4096: RMSNorm 2 producer + 2 consumer teams, plain 1 + 3.
     const int ptt = npt + (rms ? 96 : 0);   // threads of a producer team (RMSNorm adds three helper warps)
     int npteams = (rms && 2 * ptt + nct <= 1024) ? 2 : 1;
     if (rms && (pteams_env == 1 || pteams_env == 2) && pteams_env * ptt + nct <= 1024) npteams = pteams_env;
-    int nteams = rms ? 1 : (1024 - npteams * ptt) / nct;
+    int nteams = (1024 - npteams * ptt) / nct;
     if (nteams > 3) nteams = 3;
     if (teams_env >= 1 && teams_env <= 3 && teams_env * nct + npteams * ptt <= 1024) nteams = teams_env;
     // gather stages: 2 for a single consumer team, else 4.  Raw stages: a multiple of the number of
