@@ -594,29 +594,32 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       tc_fence_after();
       const int row = tm * 256 + (int)rank * 128 + quad * 32 + lane;
       __nv_bfloat16* crow = p.c + (size_t)row * p.N;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 256; c0 += 32) {
-        uint32_t r[32];
-        tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
-        tc_wait_ld();
-        const int col = tn * 256 + c0;
-        if (row < p.M && col < p.N && !(p.dbg & 4)) {
+      // Drain the accumulator into registers as packed bf16 (128 registers for this thread's 256
+      // columns) and hand tensor memory back at once: the stores below then overlap the next tile's MMAs.
+      uint32_t o[128];
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            if (col + v * 8 < p.N) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * alpha, __uint_as_float(r[v * 8 + 1]) * alpha);
-              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * alpha, __uint_as_float(r[v * 8 + 3]) * alpha);
-              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * alpha, __uint_as_float(r[v * 8 + 5]) * alpha);
-              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * alpha, __uint_as_float(r[v * 8 + 7]) * alpha);
-              *reinterpret_cast<uint4*>(crow + col + v * 8) = o;
-            }
-          }
+      for (int c0 = 0; c0 < 256; c0 += 64) {
+        uint32_t r0[32], r1[32];
+        tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r0);
+        tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c0 + 32), r1);
+        tc_wait_ld();
+#pragma unroll
+        for (int v = 0; v < 16; ++v) {
+          o[c0 / 2 + v] = pack_bf16x2(__uint_as_float(r0[2 * v]) * alpha, __uint_as_float(r0[2 * v + 1]) * alpha);
+          o[c0 / 2 + 16 + v] = pack_bf16x2(__uint_as_float(r1[2 * v]) * alpha, __uint_as_float(r1[2 * v + 1]) * alpha);
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(tmem_empty_bar);
+      if (row < p.M && !(p.dbg & 4)) {
+        const int col0 = tn * 256;
+#pragma unroll
+        for (int v = 0; v < 32; ++v) {          // 32 x 16 bytes = this row's 256 columns
+          if (col0 + v * 8 < p.N)
+            *reinterpret_cast<uint4*>(crow + col0 + v * 8) = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+        }
+      }
     }
   } else {
     // ------------------------------------------------------------------ scale warps (both CTAs)

@@ -637,36 +637,34 @@ __device__ __forceinline__ void scale_of_pair_fma(uint32_t m, uint32_t& codes, f
   codes = c2;
 }
 
-// As quantize_group_pair, with the branch-free scales; row 1's outputs sit `q1off` / `sf1off` bytes
-// after row 0's (0 for the odd last row: row 1 is stored first and row 0 overwrites it).
-__device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g, const QuantParams& p, uint8_t* q0,
-                                                       uint32_t q1off, uint8_t* sf0, uint32_t sf1off) {
+// As quantize_group_pair, with the branch-free scales; q1 / sf1 are row 1's outputs (equal to row 0's
+// for the odd last row: row 1 is stored first and row 0 overwrites it).  In every layout the codes of
+// scale column c start at byte 8 c of the row, and a critical group's residual sits 1 (mode 16) or 2
+// (mode 32) columns after its main part.
+__device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g, int G0, bool mode32, bool is_weight,
+                                                       uint8_t* q0, uint8_t* q1, uint8_t* sf0, uint8_t* sf1) {
   const uint32_t m = amax_pair(w);
   uint32_t codes;
   float2 dec, rcp;
   scale_of_pair_fma(m, codes, dec, rcp);
   uint2 c0, c1;
   encode_pair(w, rcp.x, rcp.y, c0, c1);
-  const bool critical = g >= p.G0;
-  int byte_main = 8 * g, col_main = g;
-  Slot sl;
-  if (critical) {
-    sl = slot_of(g, p.G0, p.mode);
-    byte_main = sl.byte_main;
-    col_main = sl.col_main;
-  }
-  const size_t cm = sf_col(col_main);
-  *reinterpret_cast<uint2*>(q0 + q1off + byte_main) = c1;
-  sf0[sf1off + cm] = (uint8_t)(codes >> 8);
-  *reinterpret_cast<uint2*>(q0 + byte_main) = c0;
+  const int j = g - G0;
+  const bool critical = j >= 0;
+  uint32_t col = (uint32_t)g;
+  if (critical) col = mode32 ? (uint32_t)(G0 + ((j >> 1) << 2) + (j & 1)) : (uint32_t)(g + j);
+  const uint32_t cm = ((col >> 2) << 9) | (col & 3u);
+  *reinterpret_cast<uint2*>(q1 + 8u * col) = c1;
+  sf1[cm] = (uint8_t)(codes >> 8);
+  *reinterpret_cast<uint2*>(q0 + 8u * col) = c0;
   sf0[cm] = (uint8_t)codes;
   if (!critical) return;
 
   uint2 e0 = c0, e1 = c1;
   uint32_t rcodes = codes;
-  if (!p.is_weight) {
+  if (!is_weight) {
     float d0 = dec.x, d1 = dec.y;
-    if (p.mode == 32) {   // against the un-rounded fp32 scale
+    if (mode32) {   // against the un-rounded fp32 scale
       d0 = make_scale_slow(__uint_as_float((m & 0xffffu) << 16)).raw;
       d1 = make_scale_slow(__uint_as_float((m >> 16) << 16)).raw;
     }
@@ -676,10 +674,11 @@ __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g,
     scale_of_pair_fma(rm, rcodes, rdec, rrcp);
     encode_pair(w, rrcp.x, rrcp.y, e0, e1);
   }
-  const size_t cr = sf_col(sl.col_res);
-  *reinterpret_cast<uint2*>(q0 + q1off + sl.byte_res) = e1;
-  sf0[sf1off + cr] = (uint8_t)(rcodes >> 8);
-  *reinterpret_cast<uint2*>(q0 + sl.byte_res) = e0;
+  const uint32_t rcol = col + (mode32 ? 2u : 1u);
+  const uint32_t cr = ((rcol >> 2) << 9) | (rcol & 3u);
+  *reinterpret_cast<uint2*>(q1 + 8u * rcol) = e1;
+  sf1[cr] = (uint8_t)(rcodes >> 8);
+  *reinterpret_cast<uint2*>(q0 + 8u * rcol) = e0;
   sf0[cr] = (uint8_t)rcodes;
 }
 
@@ -972,7 +971,9 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     // ------------------------------------------------------------------ consumers
     const int team = tid / nct, ctid = tid - team * nct;
     const int warp = ctid >> 5, lane = tid & 31, ncw = nct >> 5;
-    const size_t row_bytes = (size_t)(KQ + p.KE) / 2;
+    const size_t row_bytes = (size_t)(KQ + p.KE) / 2, tile_bytes = (size_t)p.natoms * 512;
+    const int G0 = p.G0;
+    const bool mode32 = p.mode == 32, is_weight = p.is_weight != 0;
     int slot = warp;   // which 32 groups this warp takes; rotates so the critical groups move around
     // (npairs < 2^29 and at most a few grid strides beyond it: 32-bit unit numbers do not wrap)
     uint32_t it = (uint32_t)team;
@@ -981,8 +982,11 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       const uint32_t r0 = 2 * unit;
       const bool has1 = (r0 + 1) < rows;
       uint8_t* q0 = p.q + (size_t)r0 * row_bytes;
-      uint8_t* sf0 = p.sf + sf_row_base((long long)r0, p.natoms);
-      const uint32_t q1off = has1 ? (uint32_t)row_bytes : 0u, sf1off = has1 ? 16u : 0u;
+      // 128-row tile, then 16 bytes per row % 32 and 4 per (row / 32) % 4; row 1 of the pair is the
+      // next row of the same 32-row run
+      uint8_t* sf0 = p.sf + (size_t)(r0 >> 7) * tile_bytes + (((r0 & 31u) << 4) | (((r0 >> 5) & 3u) << 2));
+      uint8_t* q1 = has1 ? q0 + row_bytes : q0;
+      uint8_t* sf1 = has1 ? sf0 + 16 : sf0;
       const uint8_t* buf = stages + (size_t)s * stage_bytes;
       if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) break;
       for (int g = slot * 32 + lane; g < G; g += nct) {
@@ -1000,7 +1004,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
           __syncwarp();
           if (lane == 0) mbar_arrive(empty0 + 8 * s);
         }
-        quantize_group_pair_ws(w, g, p, q0, q1off, sf0, sf1off);
+        quantize_group_pair_ws(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1);
       }
       slot = slot + 1 == ncw ? 0 : slot + 1;
     }
