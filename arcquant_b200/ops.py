@@ -32,7 +32,7 @@ def reference_mode(kq: int) -> int:
     return int(_lib.load().arcq_reference_mode(kq))
 
 
-def _quantize(kind: str, x, gamma, eps, reorder_index, ke: int, mode):
+def _quantize(kind: str, x, gamma, eps, reorder_index, ke: int, mode, out=None):
     lib = _lib.load()
     _require(x, torch.bfloat16, "input")
     if x.dim() != 2:
@@ -47,8 +47,16 @@ def _quantize(kind: str, x, gamma, eps, reorder_index, ke: int, mode):
             raise RuntimeError("reorder_index must have KQ entries")
         idx_ptr = reorder_index.data_ptr()
     k_eff = kq + ke
-    q = torch.empty((rows, k_eff // 2), dtype=torch.uint8, device=x.device)
-    sf = torch.empty((sf_bytes(rows, k_eff),), dtype=torch.uint8, device=x.device)
+    if out is None:
+        q = torch.empty((rows, k_eff // 2), dtype=torch.uint8, device=x.device)
+        sf = torch.empty((sf_bytes(rows, k_eff),), dtype=torch.uint8, device=x.device)
+    else:   # caller-provided outputs (e.g. slices of larger buffers)
+        q, sf = out
+        _require(q, torch.uint8, "out codes")
+        _require(sf, torch.uint8, "out scales")
+        span = ((rows + 127) // 128) * ((k_eff // 16 + 3) // 4) * 512
+        if q.numel() < rows * (k_eff // 2) or sf.numel() < span:
+            raise RuntimeError("output buffers too small")
     with torch.cuda.device(x.device):
         if kind == "x":
             rc = lib.arcq_reorder_quantize_x(x.data_ptr(), idx_ptr, rows, kq, ke, mode, q.data_ptr(),
@@ -64,9 +72,9 @@ def _quantize(kind: str, x, gamma, eps, reorder_index, ke: int, mode):
     return q, sf
 
 
-def reorder_quantize_x(x, reorder_index, ke: int, mode=None):
+def reorder_quantize_x(x, reorder_index, ke: int, mode=None, out=None):
     """(QX u8 [M,(KQ+KE)/2], SFX u8 [sf_bytes]) = ARC-NVFP4 of bf16 x [M,KQ]."""
-    return _quantize("x", x, None, 0.0, reorder_index, ke, mode)
+    return _quantize("x", x, None, 0.0, reorder_index, ke, mode, out)
 
 
 def reorder_quantize_w(w, reorder_index, ke: int, mode=None):
@@ -74,9 +82,9 @@ def reorder_quantize_w(w, reorder_index, ke: int, mode=None):
     return _quantize("w", w, None, 0.0, reorder_index, ke, mode)
 
 
-def rmsnorm_quantize_x(x, weight, eps: float, reorder_index, ke: int):
+def rmsnorm_quantize_x(x, weight, eps: float, reorder_index, ke: int, out=None):
     """RMSNorm(x)*weight fused in front of reorder_quantize_x."""
-    return _quantize("rms", x, weight, eps, reorder_index, ke, _lib.MODE_16)
+    return _quantize("rms", x, weight, eps, reorder_index, ke, _lib.MODE_16, out)
 
 
 def _matmul(a, b, sfa, sfb, alpha: float, alpha_a, alpha_b) -> torch.Tensor:

@@ -88,3 +88,30 @@ def test_error_behaviour_mirrors_the_reference():
     keep = x.clone()
     agemm.reorder_quantize_x(x, idx, 128)
     assert torch.equal(x, keep)
+
+
+def test_host_pipeline_matches_single_call():
+    """Chunked upload / kernel / download over three streams gives the bytes of one call on the batch."""
+    from arcquant_b200 import ops
+    from arcquant_b200.host_pipeline import HostQuantizePipeline
+
+    tokens, kq, ke = 1000, 4096, 128          # not a multiple of the chunk: ragged last chunk, odd tile
+    out = synth.outlier_channels(kq, 40, 2)
+    x = synth.activations(tokens, kq, 21, out)
+    gamma = synth.rms_gain(kq, 5)
+    idx = synth.reorder_index_from_stats(synth.activations(64, kq, 3, out).abs().amax(0))
+    hx = x.pin_memory()
+    pipe = HostQuantizePipeline(tokens, kq, ke, "cuda:0", chunk_rows=256)
+    hq = torch.empty((tokens, (kq + ke) // 2), dtype=torch.uint8).pin_memory()
+    hsf = torch.zeros((pipe.sf_bytes(),), dtype=torch.uint8).pin_memory()
+    nvalid = ((tokens + 127) // 128) * (((kq + ke) // 16 + 3) // 4) * 512
+    for g in (None, gamma.cuda()):
+        pipe.run(hx, idx.cuda(), hq, hsf, gamma=g, eps=1e-5)
+        if g is None:
+            q, sf = ops.reorder_quantize_x(x.cuda(), idx.cuda(), ke)
+        else:
+            q, sf = ops.rmsnorm_quantize_x(x.cuda(), g, 1e-5, idx.cuda(), ke)
+        assert torch.equal(hq, q.cpu())
+        # rows beyond `tokens` in the last tile are never written by either path: compare valid bytes
+        from tests.helpers import valid_sf
+        assert (valid_sf(hsf[:nvalid], tokens, kq + ke) == valid_sf(sf[:nvalid], tokens, kq + ke)).all()
