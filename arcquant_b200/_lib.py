@@ -42,6 +42,8 @@ SIGNATURES = {
     "arcq_matmul_nvfp4_static": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp, _vp]),
     "arcq_gemm_poll_error": (_i32, []),
     "arcq_absmax_bf16": (_i32, [_vp, _i64, _vp, _i32, _vp]),
+    "arcq_rope_bf16": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp]),
+    "arcq_silu_mul_bf16": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
 }
 
 _lib = None

@@ -19,7 +19,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 LIB = os.path.join(HERE, "libarcq.so")
-CUDA_SOURCES = ["arcq_api.cu", "arcq_quant.cu", "arcq_gemm.cu"]
+CUDA_SOURCES = ["arcq_api.cu", "arcq_quant.cu", "arcq_gemm.cu", "arcq_layer.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I" + INCLUDE, "-I" + CSRC]
 

@@ -175,6 +175,25 @@ int arcq_gemm_poll_error(void) {
   return g != ARCQ_OK ? g : q;
 }
 
+int arcq_rope_bf16(void* x, const float* cos_table, const float* sin_table, int64_t tokens, int row_elems, int heads,
+                   int head_dim, int seq, void* stream) {
+  if (tokens < 0 || heads < 0 || seq <= 0 || head_dim <= 0 || head_dim % 16 || row_elems % 8 ||
+      (int64_t)heads * head_dim > row_elems)
+    return ARCQ_ERR_BAD_SHAPE;
+  if (tokens == 0 || heads == 0) return ARCQ_OK;
+  if (!x || !cos_table || !sin_table) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(x)) return ARCQ_ERR_ALIGNMENT;
+  return launch_rope(x, cos_table, sin_table, tokens, row_elems, heads, head_dim, seq, (cudaStream_t)stream);
+}
+
+int arcq_silu_mul_bf16(const void* gate_up, void* out, int64_t tokens, int F, float* amax, void* stream) {
+  if (tokens < 0 || F <= 0 || F % 8) return ARCQ_ERR_BAD_SHAPE;
+  if (tokens == 0) return launch_silu_mul(gate_up, out, 0, F, amax, (cudaStream_t)stream);
+  if (!gate_up || !out) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(gate_up) || !aligned16(out)) return ARCQ_ERR_ALIGNMENT;
+  return launch_silu_mul(gate_up, out, tokens, F, amax, (cudaStream_t)stream);
+}
+
 int arcq_absmax_bf16(const void* x, int64_t n, float* out, int accumulate, void* stream) {
   if (n < 0) return ARCQ_ERR_BAD_SHAPE;
   if (!out || (n > 0 && !x)) return ARCQ_ERR_NULL_POINTER;

@@ -38,6 +38,10 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K_eff);
 int launch_gemm_static(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                        int64_t N, int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* C,
                        cudaStream_t stream);
+// Layer glue (arcq_layer.cu).
+int launch_rope(void* x, const float* cos_t, const float* sin_t, int64_t tokens, int row_elems, int heads, int dim,
+                int seq, cudaStream_t stream);
+int launch_silu_mul(const void* gu, void* out, int64_t tokens, int F, float* amax, cudaStream_t stream);
 int gemm_poll_error();
 // Same for the bounded waits of the warp-specialised quantizer.
 int quant_poll_error();

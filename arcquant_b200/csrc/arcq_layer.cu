@@ -1,0 +1,134 @@
+// Element-wise pieces of a decoder layer that sit between the quantized linears: rotary position
+// embedding applied in place to the q and k columns of the fused qkv output, and SiLU(gate) * up with
+// the per-tensor max|.| of the result (which the next activation quantizer needs) taken in the same
+// pass.  The reference's layers call torch for these (model/qLlamaLayer.py of ARCQuant uses the
+// Hugging Face `apply_rotary_pos_emb` and `act_fn(gate) * up`); the arithmetic below reproduces the
+// eager torch results bit for bit: every product and sum is rounded to fp32 separately, the same
+// `expf` and IEEE division, bf16 rounding after SiLU and after the product.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "arcq_internal.h"
+
+namespace arcq {
+namespace {
+
+__device__ __forceinline__ float lo_f(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float hi_f(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// x: [tokens, row_elems] bf16; the first `heads` heads of `dim` elements of each row are rotated:
+// out[d] = x[d] * cos[d] - x[d + dim/2] * sin[d],  out[d + dim/2] = x[d + dim/2] * cos[..] + x[d] * sin[..]
+// (rotate-half convention), cos/sin: [seq, dim] fp32 indexed by token % seq.  One thread = 8 + 8 elements.
+__global__ void arcq_rope_kernel(uint16_t* __restrict__ x, const float* __restrict__ cs, const float* __restrict__ sn,
+                                 long long tokens, int row_elems, int heads, int dim, int seq) {
+  const int half = dim >> 1, per_head = half >> 3;
+  const long long total = tokens * heads * per_head;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int d8 = (int)(i % per_head);
+    const long long th = i / per_head;
+    const int h = (int)(th % heads);
+    const long long t = th / heads;
+    const int pos = (int)(t % seq);
+    uint16_t* base = x + t * row_elems + (long long)h * dim + d8 * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(base), b = *reinterpret_cast<const uint4*>(base + half);
+    const float* c0 = cs + (long long)pos * dim + d8 * 8;
+    const float* s0 = sn + (long long)pos * dim + d8 * 8;
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+    uint32_t oa[4], ob[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float ra[2], rb[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float xa = e ? hi_f(aw[k]) : lo_f(aw[k]), xb = e ? hi_f(bw[k]) : lo_f(bw[k]);
+        const int d = 2 * k + e;
+        // first half: x_a * cos + (-x_b) * sin;  second half: x_b * cos + x_a * sin
+        ra[e] = __fadd_rn(__fmul_rn(xa, c0[d]), __fmul_rn(-xb, s0[d]));
+        rb[e] = __fadd_rn(__fmul_rn(xb, c0[half + d]), __fmul_rn(xa, s0[half + d]));
+      }
+      oa[k] = pack2(ra[0], ra[1]);
+      ob[k] = pack2(rb[0], rb[1]);
+    }
+    *reinterpret_cast<uint4*>(base) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+    *reinterpret_cast<uint4*>(base + half) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+  }
+}
+
+__device__ __forceinline__ float silu_bf16(float g) {
+  const float s = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+  return __uint_as_float(pack2(s, 0.f) << 16);   // rounded to bf16, as torch's bf16 SiLU returns it
+}
+
+// gu: [tokens, 2F] bf16 = [gate | up]; out: [tokens, F] bf16 = bf16(bf16(silu(gate)) * up); amax: max |out|.
+__global__ void arcq_silu_mul_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ out, long long tokens, int F,
+                                     unsigned int* amax) {
+  const int vec_per_row = F >> 3;
+  const long long total = tokens * vec_per_row;
+  uint32_t m = 0;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vec_per_row;
+    const int v = (int)(i - t * vec_per_row);
+    const uint16_t* row = gu + t * 2LL * F;
+    const uint4 g = *reinterpret_cast<const uint4*>(row + v * 8), u = *reinterpret_cast<const uint4*>(row + F + v * 8);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float a = __fmul_rn(silu_bf16(lo_f(gw[k])), lo_f(uw[k]));
+      const float b = __fmul_rn(silu_bf16(hi_f(gw[k])), hi_f(uw[k]));
+      o[k] = pack2(a, b);
+      uint32_t ab;
+      asm("max.u16x2 %0, %1, %2;" : "=r"(ab) : "r"(m), "r"(o[k] & 0x7fff7fffu));
+      m = ab;
+    }
+    *reinterpret_cast<uint4*>(out + t * (long long)F + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  if (amax) {
+    uint32_t r = max(m & 0xffffu, m >> 16);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) r = max(r, __shfl_xor_sync(0xffffffffu, r, d));
+    if ((threadIdx.x & 31) == 0) atomicMax(amax, r << 16);   // non-negative floats order like their bit patterns
+  }
+}
+
+}  // namespace
+
+int launch_rope(void* x, const float* cos_t, const float* sin_t, int64_t tokens, int row_elems, int heads, int dim,
+                int seq, cudaStream_t stream) {
+  if (tokens == 0 || heads == 0) return ARCQ_OK;
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  const long long total = (long long)tokens * heads * (dim / 16);
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)di.num_sms * 16;
+  if (blocks > cap) blocks = cap;
+  arcq_rope_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<uint16_t*>(x), cos_t, sin_t, tokens, row_elems, heads,
+                                                         dim, seq);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
+
+int launch_silu_mul(const void* gu, void* out, int64_t tokens, int F, float* amax, cudaStream_t stream) {
+  if (amax) ARCQ_CUDA_TRY(cudaMemsetAsync(amax, 0, sizeof(float), stream));
+  if (tokens == 0) return ARCQ_OK;
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  const long long total = (long long)tokens * (F / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)di.num_sms * 16;
+  if (blocks > cap) blocks = cap;
+  arcq_silu_mul_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(gu), static_cast<uint16_t*>(out),
+                                                             tokens, F, reinterpret_cast<unsigned int*>(amax));
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
+
+}  // namespace arcq

@@ -132,16 +132,14 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         a, sfa = ops.rmsnorm_quantize_x(x2d, self.ln1, cfg.eps, self.qkv.index, self.qkv.select_num)
         qkv = self.qkv.gemm(a, sfa)
         nq, nk = self.h_local * D, self.kv_local * D
+        # rotary embedding in place on the q and k columns of the fused output (they are adjacent);
+        # attention reads strided views of it, grouped-query heads are not materialised
+        cos, sin = rope_tables(positions, D, cfg.rope_theta)
+        ops.rope_inplace(qkv, cos, sin, self.h_local + self.kv_local, D)
         q = qkv[:, :nq].reshape(bsz, seq, self.h_local, D).transpose(1, 2)
         k = qkv[:, nq:nq + nk].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
         v = qkv[:, nq + nk:].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
-        cos, sin = rope_tables(positions, D, cfg.rope_theta)
-        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-        rep = self.h_local // self.kv_local
-        if rep > 1:
-            k = k.repeat_interleave(rep, dim=1)
-            v = v.repeat_interleave(rep, dim=1)
-        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.h_local != self.kv_local)
         attn = attn.transpose(1, 2).reshape(bsz * seq, nq).contiguous()
         qa, sfo, so = NVFP4_reorder_quantize_x(attn, self.o.index, self.o.select_num, mode=16)
         return self.o.gemm(qa, sfo, so)
@@ -151,8 +149,8 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         cfg = self.cfg
         a, sfa = ops.rmsnorm_quantize_x(h2d, self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
         gu = self.gate_up.gemm(a, sfa)
-        act = (F.silu(gu[:, :self.f_local]) * gu[:, self.f_local:]).contiguous()
-        qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16)
+        act, amax = ops.silu_mul(gu)      # silu(gate) * up and its max|.| in one pass
+        qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16, amax=amax)
         return self.down.gemm(qd, sfd, sd)
 
     @torch.no_grad()

@@ -21,6 +21,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
+from . import ops
 from .qlinear import NVFP4_reorder_quantize_x
 
 
@@ -151,8 +152,8 @@ class QMixtralMoEBlockEP(torch.nn.Module):
             xb = rows[start:start + n].contiguous()
             a, sfa, sx = NVFP4_reorder_quantize_x(xb, gu.index, gu.select_num, mode=16)
             h = gu.gemm(a, sfa, sx)
-            act = (F.silu(h[:, :ffn]) * h[:, ffn:]).contiguous()
-            b, sfb, sa = NVFP4_reorder_quantize_x(act, dn.index, dn.select_num, mode=16)
+            act, amax = ops.silu_mul(h)
+            b, sfb, sa = NVFP4_reorder_quantize_x(act, dn.index, dn.select_num, mode=16, amax=amax)
             out[start:start + n] = dn.gemm(b, sfb, sa)
             start += n
         return out

@@ -133,5 +133,39 @@ def absmax(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def rope_inplace(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, heads: int, head_dim: int) -> torch.Tensor:
+    """Rotate-half rotary embedding in place on the first `heads` heads of every row of x [tokens, row]
+    (bf16); cos / sin fp32 [seq, head_dim], row = token % seq.  Bit-equal to the eager
+    ``(x.float() * cos + rotate_half(x.float()) * sin).to(bf16)``."""
+    lib = _lib.load()
+    _require(x, torch.bfloat16, "x")
+    _require(cos, torch.float32, "cos")
+    _require(sin, torch.float32, "sin")
+    if x.dim() != 2 or cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != head_dim:
+        raise RuntimeError("x must be [tokens, row]; cos / sin [seq, head_dim]")
+    with torch.cuda.device(x.device):
+        rc = lib.arcq_rope_bf16(x.data_ptr(), cos.data_ptr(), sin.data_ptr(), x.shape[0], x.shape[1], heads, head_dim,
+                                cos.shape[0], _stream())
+    _lib.check(rc, "rope")
+    return x
+
+
+def silu_mul(gate_up: torch.Tensor, with_amax: bool = True):
+    """(out bf16 [tokens, F], amax 0-dim fp32 or None) for gate_up [tokens, 2F] = [gate | up]:
+    out = silu(gate) * up as eager bf16 torch computes it, max|out| in the same pass."""
+    lib = _lib.load()
+    _require(gate_up, torch.bfloat16, "gate_up")
+    if gate_up.dim() != 2 or gate_up.shape[1] % 16:
+        raise RuntimeError("gate_up must be [tokens, 2F] with F a multiple of 8")
+    tokens, f2 = gate_up.shape
+    out = torch.empty((tokens, f2 // 2), dtype=torch.bfloat16, device=gate_up.device)
+    amax = torch.empty((), dtype=torch.float32, device=gate_up.device) if with_amax else None
+    with torch.cuda.device(gate_up.device):
+        rc = lib.arcq_silu_mul_bf16(gate_up.data_ptr(), out.data_ptr(), tokens, f2 // 2,
+                                    None if amax is None else amax.data_ptr(), _stream())
+    _lib.check(rc, "silu_mul")
+    return out, amax
+
+
 def gemm_poll_error() -> int:
     return int(_lib.load().arcq_gemm_poll_error())

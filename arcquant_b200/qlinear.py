@@ -14,11 +14,12 @@ FP4_MAX = 6.0
 FP8_MAX = 448.0
 
 
-def NVFP4_reorder_quantize_x(x: torch.Tensor, reorder_index: torch.Tensor, select_num: int, mode=None):
+def NVFP4_reorder_quantize_x(x: torch.Tensor, reorder_index: torch.Tensor, select_num: int, mode=None, amax=None):
     """(qx, scale_x, scale): per-tensor scale = max|x| / (448*6) as a 0-dim fp32 CUDA tensor,
     ``x / scale`` in bf16 as the reference forms it, then the fused reorder + NVFP4 + ARC kernel.
-    One pass for the amax (``arcq_absmax_bf16``) instead of ``torch.max(x.abs())``."""
-    scale = ops.absmax(x) / (FP8_MAX * FP4_MAX)
+    One pass for the amax (``arcq_absmax_bf16``) instead of ``torch.max(x.abs())``; a caller that
+    already has max|x| on the device (``ops.silu_mul``) passes it as ``amax``."""
+    scale = (ops.absmax(x) if amax is None else amax) / (FP8_MAX * FP4_MAX)
     qx, scale_x = ops.reorder_quantize_x(x / scale, reorder_index, select_num, mode=mode)
     return qx, scale_x, scale
 

@@ -161,6 +161,21 @@ int arcq_gemm_poll_error(void);
  * call).  Replaces the torch.max(x.abs()) pass of model/qLlamaLayer.py:74. */
 int arcq_absmax_bf16(const void* x, int64_t n, float* out, int accumulate, void* stream);
 
+/* Layer glue between the quantized linears.  No counterpart in the reference's bindings: its layers
+ * call torch for these (Hugging Face apply_rotary_pos_emb and act_fn(gate) * up in
+ * model/qLlamaLayer.py).  Results equal eager torch bit for bit.
+ *
+ * arcq_rope_bf16: rotate-half rotary embedding, in place, on the first `heads` heads of `head_dim`
+ *   elements of every row of x [tokens, row_elems] (bf16; e.g. the q and k columns of a fused qkv
+ *   output).  cos_table / sin_table: fp32 [seq, head_dim], row = token % seq.
+ *   out = bf16(fp32(x * cos) + fp32(rotate_half(x) * sin)).  head_dim % 16 == 0.
+ * arcq_silu_mul_bf16: out [tokens, F] = bf16(bf16(silu(gate)) * up) for gate_up [tokens, 2F] = [gate | up]
+ *   (bf16); if amax is not NULL it receives max |out| (fp32, device memory) - the per-tensor maximum the
+ *   next activation quantizer's global scale is made of.  F % 8 == 0. */
+int arcq_rope_bf16(void* x, const float* cos_table, const float* sin_table, int64_t tokens, int row_elems, int heads,
+                   int head_dim, int seq, void* stream);
+int arcq_silu_mul_bf16(const void* gate_up, void* out, int64_t tokens, int F, float* amax, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

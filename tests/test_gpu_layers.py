@@ -195,3 +195,34 @@ def test_moe_block_matches_cpu_restatement_and_expert_parallel_emulation():
             total.index_add_(0, tok, out.float().cpu())
     # per-expert batches differ from the unsharded run only in how rows were grouped into calls
     assert _rel(total, exact) < 1.2 * e_ref + 0.01, (_rel(total, exact), e_ref)
+
+
+def test_rope_inplace_equals_eager_torch():
+    from arcquant_b200 import ops
+    from arcquant_b200.llama_layer import apply_rope, rope_tables
+
+    g = torch.Generator().manual_seed(5)
+    bsz, seq, hq, hk, D = 2, 37, 6, 2, 128
+    row = (hq + 2 * hk) * D
+    qkv = (torch.randn(bsz * seq, row, generator=g) * 3).to(torch.bfloat16).cuda()
+    qkv[0, :8] = torch.tensor([0.0, -0.0, 1e-30, -1e-30, 3e38, -3e38, 1.0, -1.0], dtype=torch.bfloat16)
+    pos = torch.arange(seq, device="cuda") + 1000
+    cos, sin = rope_tables(pos, D, 500000.0)
+    ref = qkv.clone()
+    heads = ref[:, :(hq + hk) * D].reshape(bsz, seq, hq + hk, D).transpose(1, 2)
+    ref[:, :(hq + hk) * D] = apply_rope(heads, cos, sin).transpose(1, 2).reshape(bsz * seq, -1)
+    out = ops.rope_inplace(qkv.clone(), cos.contiguous(), sin.contiguous(), hq + hk, D)
+    assert torch.equal(out.view(torch.int16), ref.view(torch.int16))     # v columns untouched, q/k bit-equal
+
+
+def test_silu_mul_equals_eager_torch_and_returns_the_maximum():
+    from arcquant_b200 import ops
+
+    g = torch.Generator().manual_seed(6)
+    tokens, f = 301, 2048
+    gu = (torch.randn(tokens, 2 * f, generator=g) * 4).to(torch.bfloat16).cuda()
+    gu[0, :6] = torch.tensor([0.0, -0.0, 88.0, -88.0, 1e-20, -30.0], dtype=torch.bfloat16)
+    ref = torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]
+    out, amax = ops.silu_mul(gu)
+    assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+    assert float(amax) == float(ref.abs().max())
