@@ -33,6 +33,7 @@ SIGNATURES = {
     "arcq_sf_bytes": (C.c_size_t, [_i64, _i64]),
     "arcq_reference_mode": (_i32, [_i32]),
     "arcq_reorder_quantize_x": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "arcq_reorder_quantize_x_scaled": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
     "arcq_rmsnorm_quantize_x": (_i32, [_vp, _vp, _f32, _vp, _i64, _i32, _i32, _vp, _vp, _vp]),
     "arcq_reorder_quantize_w": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
     "arcq_matmul_nvfp4": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp]),

@@ -95,6 +95,16 @@ int arcq_reorder_quantize_x(const void* x, const int16_t* reorder_index, int64_t
   return launch_quantize(x, nullptr, 0.f, reorder_index, M, KQ, KE, mode, 0, qx, sfx, (cudaStream_t)stream);
 }
 
+int arcq_reorder_quantize_x_scaled(const void* x, const float* scale, const int16_t* reorder_index, int64_t M, int KQ,
+                                   int KE, int mode, uint8_t* qx, uint8_t* sfx, void* stream) {
+  int rc = check_quant_shape(M, KQ, KE, mode);
+  if (rc != ARCQ_OK) return rc;
+  if (M == 0) return ARCQ_OK;
+  if (!x || !scale || !qx || !sfx) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(qx)) return ARCQ_ERR_ALIGNMENT;
+  return launch_quantize(x, nullptr, 0.f, reorder_index, M, KQ, KE, mode, 0, qx, sfx, (cudaStream_t)stream, scale);
+}
+
 int arcq_rmsnorm_quantize_x(const void* x, const void* gamma, float eps, const int16_t* reorder_index,
                             int64_t M, int KQ, int KE, uint8_t* qx, uint8_t* sfx, void* stream) {
   int rc = check_quant_shape(M, KQ, KE, ARCQ_MODE_16);

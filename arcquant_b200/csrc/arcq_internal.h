@@ -27,7 +27,8 @@ int get_device_info(DeviceInfo* out);
 // Launchers (defined in arcq_quant.cu / arcq_gemm.cu); arguments are validated by the callers
 // in arcq_api.cu.
 int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* idx, int64_t rows, int KQ,
-                    int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream);
+                    int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream,
+                    const float* scale = nullptr);   // scale (device): x is divided by it first; plain x only
 int launch_absmax(const void* x, int64_t n, float* out, int accumulate, cudaStream_t stream);
 // workspace (may be null): scratch for split-K partial sums, see gemm_workspace_bytes().
 int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,

@@ -51,6 +51,7 @@ struct QuantParams {
   int is_weight;  // residual slot = copy of the main codes
   float eps;
   int dbg;        // timing experiments only (ARCQ_QUANT_DBG): 1 = no global loads, 2 = no quantize, 4 = no fill
+  const float* scale;   // warp-specialised plain kernel only: x is divided by *scale (device) first, or nullptr
 };
 
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
@@ -692,15 +693,29 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "memory");
 }
 
+// x / s rounded to nearest, for a divisor shared by the whole tensor: r = fp32(1/s) correctly rounded,
+// q = x*r, one FMA for the exact residual x - s*q and one to correct q (Markstein's sequence: exact
+// when nothing under- or overflows).  Results outside a comfortable range - zeros among them, whose
+// sign the sequence loses - take the IEEE routine.
+__device__ __forceinline__ float div_shared(float x, float s, float r) {
+  const float q = __fmul_rn(x, r);
+  const float e = __fmaf_rn(-s, q, x);
+  float q2 = __fmaf_rn(e, r, q);
+  const float mag = fabsf(q2);
+  if (!(mag >= 8.6736174e-19f && mag <= 1.1529215e18f)) q2 = __fdiv_rn(x, s);   // outside [2^-60, 2^60]
+  return q2;
+}
+
 // S: stages of the gather ring (interleaved row pairs).  R: stages of the raw ring (row pairs as they
 // lie in global memory, filled by bulk copies - this is what keeps enough bytes in flight to cover
-// the HBM latency).  RMS: fused RMSNorm.
+// the HBM latency).  RMS: fused RMSNorm.  WIDE (plain only): rows of more than 8192 channels - the offset
+// table holds 16-bit entries so that table, two gather stages and one raw stage fit in shared memory.
 // Threads [0, nteams*nct) are consumers in teams of nct threads - team k takes the row pairs
 // k, k + nteams, ... of this CTA, so several pairs are being quantized at once.  After them come
 // npteams producer teams of npt = KQ/16 threads (more than one only with RMSNorm, whose producers carry
 // real arithmetic), sharing the pairs the same way; producer t of a team owns the 16-byte chunks t and
 // t + KQ/16 of each row, the reference's assignment and summation order for RMSNorm.
-template <bool RMS, int S, int R>
+template <bool RMS, bool WIDE, bool SCALED, int S, int R>
 __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantParams p, const int nct, const int npt, const int nteams,
                                                                         const int npteams) {
   extern __shared__ __align__(16) uint8_t smem[];
@@ -713,7 +728,8 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 376);
   size_t cursor = 384;
   uint32_t* offs32 = reinterpret_cast<uint32_t*>(smem + cursor);
-  cursor += (size_t)KQ * 4;
+  uint16_t* offs16 = reinterpret_cast<uint16_t*>(smem + cursor);
+  cursor += (size_t)KQ * (WIDE ? 2 : 4);
   float* psum = nullptr;
   float* rstd_s = nullptr;
   if (RMS) {
@@ -747,10 +763,13 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     abort_flag[0] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // Offsets are laid out [vector v][group g][entries of one 128-bit load]: consecutive lanes (groups)
+  // read consecutive 16 bytes, so every table load is conflict free.
   for (int j = tid; j < KQ; j += blockDim.x) {
     const int c = p.idx ? (int)p.idx[j] : j;
     const int g = j >> 4, i = j & 15;
-    offs32[(((i >> 2) * G + g) << 2) | (i & 3)] = word_offset((uint32_t)c);
+    if (WIDE) offs16[(((i >> 3) * G + g) << 3) | (i & 7)] = (uint16_t)word_offset((uint32_t)c);
+    else offs32[(((i >> 2) * G + g) << 2) | (i & 3)] = word_offset((uint32_t)c);
   }
   __syncthreads();
 
@@ -898,19 +917,57 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     uint32_t landed = (uint32_t)pteam;   // first pair of this team whose copies were not waited for yet
     bool failed = false;
     if (!RMS) {
+      const int nchunks = KQ >> 3;
+      float sc = 1.0f, rsc = 1.0f;
+      if (SCALED) {
+        // torch's CUDA kernel for (bf16 tensor) / (fp32 scalar tensor) loads the divisor as bf16
+        sc = __uint_as_float(pack_bf16x2_rn(__ldg(p.scale), 0.f) << 16);
+        rsc = __frcp_rn(sc);
+      }
       for (uint32_t it = 0; it < n; ++it) {
         const uint32_t unit = blockIdx.x + it * stride;
         const bool has1 = (2 * unit + 1) < rows;
         if (!failed && !mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) failed = true;
         if (!failed) landed = it + 1;
-        uint4 a0, a1, b0, b1;
-        read_raw(it, has1, a0, a1, b0, b1);
-        // Producers meet once per pair: every one of them has taken its chunks out of the raw stage,
-        // so it is refilled; and all leave together if any wait gave up.
+        if (!failed && !mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag)) failed = true;
+        if (!failed) {
+          // this thread's chunks c = ptid, ptid + npt, ...: interleave the two rows (dividing by the
+          // tensor's scale first, if asked) straight from the raw stage into the gather stage
+          const uint4* rw = reinterpret_cast<const uint4*>(raw + (size_t)(it % R) * stage_bytes);
+          uint4* b4 = reinterpret_cast<uint4*>(stages + (size_t)(it % S) * stage_bytes);
+          auto do_chunk = [&](int c) {
+            const uint4 a = rw[c], b = has1 ? rw[nchunks + c] : zero;
+            uint4 lo, hi;  // words of channels 8c..8c+3 and 8c+4..8c+7: (row0[ch], row1[ch]) per word
+            if (SCALED) {
+              auto dv = [&](uint32_t wa, uint32_t wb, uint32_t& o0, uint32_t& o1) {
+                o0 = pack_bf16x2_rn(div_shared(bf16lo(wa), sc, rsc), div_shared(bf16lo(wb), sc, rsc));
+                o1 = pack_bf16x2_rn(div_shared(bf16hi(wa), sc, rsc), div_shared(bf16hi(wb), sc, rsc));
+              };
+              dv(a.x, b.x, lo.x, lo.y); dv(a.y, b.y, lo.z, lo.w);
+              dv(a.z, b.z, hi.x, hi.y); dv(a.w, b.w, hi.z, hi.w);
+            } else {
+              lo.x = __byte_perm(a.x, b.x, 0x5410); lo.y = __byte_perm(a.x, b.x, 0x7632);
+              lo.z = __byte_perm(a.y, b.y, 0x5410); lo.w = __byte_perm(a.y, b.y, 0x7632);
+              hi.x = __byte_perm(a.z, b.z, 0x5410); hi.y = __byte_perm(a.z, b.z, 0x7632);
+              hi.z = __byte_perm(a.w, b.w, 0x5410); hi.w = __byte_perm(a.w, b.w, 0x7632);
+            }
+            // XOR-swizzled 16-byte units: the eight lanes of a 128-bit store wavefront hit distinct banks
+            b4[swz16(2u * c)] = lo;
+            b4[swz16(2u * c + 1u)] = hi;
+          };
+          if (nchunks == 2 * npt) {   // the decoder-layer widths: exactly two chunks per thread
+            do_chunk(ptid);
+            do_chunk(ptid + npt);
+          } else {
+            for (int c = ptid; c < nchunks; c += npt) do_chunk(c);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full0 + 8 * (it % S));
+        }
+        // Producers meet once per pair: every one of them is done with the raw stage, so it is
+        // refilled; and all leave together if any wait gave up.
         if (named_barrier_or(bar_id, team_threads, failed)) break;
         if (ptid == 0 && it + R < n) { issue(unit + R * stride, it % R); issued = it + R + 1; }
-        if (!mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag)) { failed = true; continue; }
-        fill_stage(it, a0, a1, b0, b1, make_float2(0.f, 0.f));
       }
     } else {
       // Software pipeline, synchronised by mbarriers only: normalise and hand over this team's pair
@@ -991,14 +1048,28 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) break;
       for (int g = slot * 32 + lane; g < G; g += nct) {
         uint32_t w[16];
-        const uint4* op = reinterpret_cast<const uint4*>(offs32) + g;
+        if (WIDE) {
+          const uint4* op = reinterpret_cast<const uint4*>(offs16) + g;
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          const uint4 o = op[v * G];
-          w[4 * v + 0] = *reinterpret_cast<const uint32_t*>(buf + o.x);
-          w[4 * v + 1] = *reinterpret_cast<const uint32_t*>(buf + o.y);
-          w[4 * v + 2] = *reinterpret_cast<const uint32_t*>(buf + o.z);
-          w[4 * v + 3] = *reinterpret_cast<const uint32_t*>(buf + o.w);
+          for (int v = 0; v < 2; ++v) {
+            const uint4 o = op[v * G];
+            const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              w[8 * v + 2 * k] = *reinterpret_cast<const uint32_t*>(buf + (ow[k] & 0xffffu));
+              w[8 * v + 2 * k + 1] = *reinterpret_cast<const uint32_t*>(buf + (ow[k] >> 16));
+            }
+          }
+        } else {
+          const uint4* op = reinterpret_cast<const uint4*>(offs32) + g;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint4 o = op[v * G];
+            w[4 * v + 0] = *reinterpret_cast<const uint32_t*>(buf + o.x);
+            w[4 * v + 1] = *reinterpret_cast<const uint32_t*>(buf + o.y);
+            w[4 * v + 2] = *reinterpret_cast<const uint32_t*>(buf + o.z);
+            w[4 * v + 3] = *reinterpret_cast<const uint32_t*>(buf + o.w);
+          }
         }
         if (g + nct >= G) {   // last group of this thread: the stage can be refilled (warp-uniform)
           __syncwarp();
@@ -1030,10 +1101,10 @@ __global__ void arcq_absmax_kernel(const uint4* __restrict__ x, long long nvec, 
   if ((threadIdx.x & 31) == 0) atomicMax(out, r << 16);
 }
 
-template <bool RMS, int S, int R>
+template <bool RMS, bool WIDE, bool SCALED, int S, int R>
 int launch_ws(const QuantParams& p, int nct, int npt, int nteams, int npteams, size_t smem, const DeviceInfo& di,
               cudaStream_t stream) {
-  auto kern = arcq_quantize_ws_kernel<RMS, S, R>;
+  auto kern = arcq_quantize_ws_kernel<RMS, WIDE, SCALED, S, R>;
   ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int occ = 0;
   const int threads = nteams * nct + npteams * (npt + (RMS ? 96 : 0));
@@ -1064,7 +1135,7 @@ int launch_variant(const QuantParams& p, int nt, size_t smem, const DeviceInfo& 
 }  // namespace
 
 int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* idx, int64_t rows, int KQ,
-                    int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream) {
+                    int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream, const float* scale) {
   if (rows == 0) return ARCQ_OK;
   DeviceInfo di;
   int rc = get_device_info(&di);
@@ -1088,6 +1159,7 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   p.is_weight = is_weight;
   p.eps = eps;
   p.dbg = 0;
+  p.scale = scale;
   if (const char* e = getenv("ARCQ_QUANT_DBG")) p.dbg = atoi(e);
 
   const bool rms = gamma != nullptr;
@@ -1104,55 +1176,82 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   }
   const bool rawidx = KQ > 16384;
 
-  // Warp-specialised kernel for decoder-layer widths (ARCQ_QUANT_WS=0 falls back to the general one).
+  // Warp-specialised kernel (ARCQ_QUANT_WS=0 falls back to the general one): rows of 1024..8192 channels
+  // in full, rows of up to 16384 channels for the plain operator.
   static const int ws_env = [] { const char* e = getenv("ARCQ_QUANT_WS"); return e ? atoi(e) : 1; }();
   static const int raw_env = [] { const char* e = getenv("ARCQ_QUANT_RAW"); return e ? atoi(e) : 0; }();
+  static const int stages_env = [] { const char* e = getenv("ARCQ_QUANT_STAGES"); return e ? atoi(e) : 0; }();
+  static const int teams_env = [] { const char* e = getenv("ARCQ_QUANT_TEAMS"); return e ? atoi(e) : 0; }();
+  static const int pteams_env = [] { const char* e = getenv("ARCQ_QUANT_PTEAMS"); return e ? atoi(e) : 0; }();
+  static const int nct_env = [] { const char* e = getenv("ARCQ_QUANT_NCT"); return e ? atoi(e) : 0; }();
   const bool gamma_ok = !rms || (reinterpret_cast<uintptr_t>(gamma) & 15u) == 0;   // read with 128-bit loads
-  if (ws_env && p.dbg == 0 && gamma_ok && p.G % 32 == 0 && p.G >= 64 && p.G <= 512 && rows < (1LL << 30)) {
-    // Consumer teams of 128 threads (two groups per thread at hidden 4096) were measured faster than
-    // teams of 256: more row pairs in flight for the same number of warps.
-    static const int nct_env = [] { const char* e = getenv("ARCQ_QUANT_NCT"); return e ? atoi(e) : 0; }();
-    int nct = p.G < 128 ? p.G : 128;
-    if (nct_env >= 32 && nct_env % 32 == 0 && nct_env <= p.G && nct_env <= 256) nct = nct_env;
-    const int npt = p.G;   // two 16-byte chunks of each row per producer thread
+  const bool wide = p.G > 512;
+  if (ws_env && p.dbg == 0 && gamma_ok && p.G % 32 == 0 && p.G >= 64 && rows < (1LL << 30) &&
+      (wide ? (!rms && p.G <= 1024) : true)) {
     const size_t stage = (size_t)KQ * 4;
-    // One CTA per SM, up to 1024 threads.  Plain: one producer team (it only moves data) and up to three
-    // consumer teams.  RMSNorm: two producer teams if two consumer teams still fit beside them.
-    static const int stages_env = [] { const char* e = getenv("ARCQ_QUANT_STAGES"); return e ? atoi(e) : 0; }();
-    static const int teams_env = [] { const char* e = getenv("ARCQ_QUANT_TEAMS"); return e ? atoi(e) : 0; }();
-    static const int pteams_env = [] { const char* e = getenv("ARCQ_QUANT_PTEAMS"); return e ? atoi(e) : 0; }();
-    // Measured best on B200 for hidden 4096: RMSNorm 2 producer + 2 consumer teams, plain 1 + 3.
-    const int ptt = npt + (rms ? 96 : 0);   // threads of a producer team (RMSNorm adds three helper warps)
-    int npteams = (rms && 2 * ptt + nct <= 1024) ? 2 : 1;
-    if (rms && (pteams_env == 1 || pteams_env == 2) && pteams_env * ptt + nct <= 1024) npteams = pteams_env;
-    int nteams = (1024 - npteams * ptt) / nct;
-    if (nteams > 3) nteams = 3;
-    if (teams_env >= 1 && teams_env <= 3 && teams_env * nct + npteams * ptt <= 1024) nteams = teams_env;
-    // gather stages: 2 for a single consumer team, else 4.  Raw stages: a multiple of the number of
-    // producer teams (a stage always serves pairs of the same team), at least two per team.
-    int S = nteams > 1 ? 4 : 2;
-    if (stages_env == 2 || stages_env == 4) S = stages_env;
-    const int r_min = rms ? 2 * npteams : 2;
-    size_t fixed = 384 + (size_t)KQ * 4 + (rms ? ((size_t)4 * npt * sizeof(float) + 16) * npteams : 0);
-    if (rms && npteams == 2 && fixed + (S + r_min) * stage > (size_t)di.max_smem_optin) {
-      npteams = 1;   // not enough shared memory for two pipelines
-      fixed = 384 + (size_t)KQ * 4 + (size_t)4 * npt * sizeof(float) + 16;
-    }
-    const int r_floor = rms ? 2 * npteams : 2;
-    int R = 8;
-    while (R > r_floor && fixed + (S + R) * stage > (size_t)di.max_smem_optin) R -= 2;
-    if ((raw_env == 2 || raw_env == 4 || raw_env == 6 || raw_env == 8) && raw_env >= r_floor) R = raw_env;
-    const size_t smem = fixed + (S + R) * stage;
-    if (smem <= (size_t)di.max_smem_optin) {
-#define ARCQ_WS_CASE(RMS_, S_, R_) \
-  if (rms == RMS_ && S == S_ && R == R_) return launch_ws<RMS_, S_, R_>(p, nct, npt, nteams, npteams, smem, di, stream);
-#define ARCQ_WS_ROW(RMS_, S_) \
-  ARCQ_WS_CASE(RMS_, S_, 2) ARCQ_WS_CASE(RMS_, S_, 4) ARCQ_WS_CASE(RMS_, S_, 6) ARCQ_WS_CASE(RMS_, S_, 8)
-      ARCQ_WS_ROW(true, 2) ARCQ_WS_ROW(true, 4) ARCQ_WS_ROW(false, 2) ARCQ_WS_ROW(false, 4)
+    if (wide) {
+      // 256 producers, two consumer teams of 256, two gather stages, 16-bit offset table; one raw
+      // stage (two if they fit)
+      const int nct = 256, npt = 256, nteams = 2;
+      const size_t fixed = 384 + (size_t)KQ * 2;
+      int R = fixed + 4 * stage <= (size_t)di.max_smem_optin ? 2 : 1;
+      if (raw_env == 1 || raw_env == 2) R = raw_env;
+      const size_t smem = fixed + (2 + R) * stage;
+      if (smem <= (size_t)di.max_smem_optin) {
+        if (p.scale) {
+          if (R == 2) return launch_ws<false, true, true, 2, 2>(p, nct, npt, nteams, 1, smem, di, stream);
+          return launch_ws<false, true, true, 2, 1>(p, nct, npt, nteams, 1, smem, di, stream);
+        }
+        if (R == 2) return launch_ws<false, true, false, 2, 2>(p, nct, npt, nteams, 1, smem, di, stream);
+        return launch_ws<false, true, false, 2, 1>(p, nct, npt, nteams, 1, smem, di, stream);
+      }
+    } else {
+      // Consumer teams of 128 threads (two groups per thread at hidden 4096) were measured faster than
+      // teams of 256: more row pairs in flight for the same number of warps.
+      int nct = p.G < 128 ? p.G : 128;
+      if (nct_env >= 32 && nct_env % 32 == 0 && nct_env <= p.G && nct_env <= 256) nct = nct_env;
+      const int npt = p.G;   // two 16-byte chunks of each row per producer thread
+      // One CTA per SM, up to 1024 threads.  Plain: one producer team (it only moves data).  RMSNorm: two
+      // producer teams, each with three helper warps.  The rest, up to three teams, are consumers.
+      const int ptt = npt + (rms ? 96 : 0);   // threads of a producer team
+      int npteams = (rms && 2 * ptt + nct <= 1024) ? 2 : 1;
+      if (rms && (pteams_env == 1 || pteams_env == 2) && pteams_env * ptt + nct <= 1024) npteams = pteams_env;
+      int nteams = (1024 - npteams * ptt) / nct;
+      if (nteams > 3) nteams = 3;
+      if (teams_env >= 1 && teams_env <= 3 && teams_env * nct + npteams * ptt <= 1024) nteams = teams_env;
+      // gather stages: 2 for a single consumer team, else 4.  Raw stages: a multiple of the number of
+      // producer teams (a stage always serves pairs of the same team), at least two per team.
+      int S = nteams > 1 ? 4 : 2;
+      if (stages_env == 2 || stages_env == 4) S = stages_env;
+      size_t fixed = 384 + (size_t)KQ * 4 + (rms ? ((size_t)4 * npt * sizeof(float) + 16) * npteams : 0);
+      if (fixed + (S + 2 * npteams) * stage > (size_t)di.max_smem_optin && S == 4) S = 2;
+      if (rms && npteams == 2 && fixed + (S + 4) * stage > (size_t)di.max_smem_optin) {
+        npteams = 1;   // not enough shared memory for two pipelines
+        fixed = 384 + (size_t)KQ * 4 + (size_t)4 * npt * sizeof(float) + 16;
+      }
+      const int r_floor = 2 * npteams;
+      int R = 8;
+      while (R > r_floor && fixed + (S + R) * stage > (size_t)di.max_smem_optin) R -= 2;
+      if ((raw_env == 2 || raw_env == 4 || raw_env == 6 || raw_env == 8) && raw_env >= r_floor) R = raw_env;
+      const size_t smem = fixed + (S + R) * stage;
+      if (nteams >= 1 && smem <= (size_t)di.max_smem_optin) {
+        const int kind = rms ? 0 : (p.scale ? 2 : 1);   // RMSNorm / plain / plain with the division
+#define ARCQ_WS_CASE(KIND_, RMS_, SCALED_, S_, R_) \
+  if (kind == KIND_ && S == S_ && R == R_) \
+    return launch_ws<RMS_, false, SCALED_, S_, R_>(p, nct, npt, nteams, npteams, smem, di, stream);
+#define ARCQ_WS_ROW(KIND_, RMS_, SCALED_, S_)                                                          \
+  ARCQ_WS_CASE(KIND_, RMS_, SCALED_, S_, 2) ARCQ_WS_CASE(KIND_, RMS_, SCALED_, S_, 4)                  \
+  ARCQ_WS_CASE(KIND_, RMS_, SCALED_, S_, 6) ARCQ_WS_CASE(KIND_, RMS_, SCALED_, S_, 8)
+        ARCQ_WS_ROW(0, true, false, 2) ARCQ_WS_ROW(0, true, false, 4)
+        ARCQ_WS_ROW(1, false, false, 2) ARCQ_WS_ROW(1, false, false, 4)
+        ARCQ_WS_ROW(2, false, true, 2) ARCQ_WS_ROW(2, false, true, 4)
 #undef ARCQ_WS_ROW
 #undef ARCQ_WS_CASE
+      }
     }
   }
+  if (p.scale) return ARCQ_ERR_UNSUPPORTED_K;   // only the warp-specialised kernel divides by the scale
+
   const size_t table = 160 + (((size_t)KQ * (rawidx ? 2 : 4) + 15) & ~(size_t)15);
   auto smem_for = [&](int nbuf, int pairs) {
     return table + (rms ? (size_t)KQ * 4 + (size_t)2 * pairs * nt * sizeof(float) + 16 : 0) +

@@ -32,7 +32,7 @@ def reference_mode(kq: int) -> int:
     return int(_lib.load().arcq_reference_mode(kq))
 
 
-def _quantize(kind: str, x, gamma, eps, reorder_index, ke: int, mode, out=None):
+def _quantize(kind: str, x, gamma, eps, reorder_index, ke: int, mode, out=None, scale=None):
     lib = _lib.load()
     _require(x, torch.bfloat16, "input")
     if x.dim() != 2:
@@ -58,7 +58,15 @@ def _quantize(kind: str, x, gamma, eps, reorder_index, ke: int, mode, out=None):
         if q.numel() < rows * (k_eff // 2) or sf.numel() < span:
             raise RuntimeError("output buffers too small")
     with torch.cuda.device(x.device):
-        if kind == "x":
+        if kind == "x" and scale is not None:
+            _require(scale, torch.float32, "scale")
+            rc = lib.arcq_reorder_quantize_x_scaled(x.data_ptr(), scale.data_ptr(), idx_ptr, rows, kq, ke, mode,
+                                                    q.data_ptr(), sf.data_ptr(), _stream())
+            if rc == _lib.ERR_UNSUPPORTED_K:   # width not covered by the fused path: divide first
+                xs = x / scale
+                rc = lib.arcq_reorder_quantize_x(xs.data_ptr(), idx_ptr, rows, kq, ke, mode, q.data_ptr(),
+                                                 sf.data_ptr(), _stream())
+        elif kind == "x":
             rc = lib.arcq_reorder_quantize_x(x.data_ptr(), idx_ptr, rows, kq, ke, mode, q.data_ptr(),
                                              sf.data_ptr(), _stream())
         elif kind == "w":
@@ -72,9 +80,10 @@ def _quantize(kind: str, x, gamma, eps, reorder_index, ke: int, mode, out=None):
     return q, sf
 
 
-def reorder_quantize_x(x, reorder_index, ke: int, mode=None, out=None):
-    """(QX u8 [M,(KQ+KE)/2], SFX u8 [sf_bytes]) = ARC-NVFP4 of bf16 x [M,KQ]."""
-    return _quantize("x", x, None, 0.0, reorder_index, ke, mode, out)
+def reorder_quantize_x(x, reorder_index, ke: int, mode=None, out=None, scale=None):
+    """(QX u8 [M,(KQ+KE)/2], SFX u8 [sf_bytes]) = ARC-NVFP4 of bf16 x [M,KQ].
+    scale (0-dim fp32 CUDA tensor): quantize ``x / scale`` instead, the division fused into the kernel."""
+    return _quantize("x", x, None, 0.0, reorder_index, ke, mode, out, scale)
 
 
 def reorder_quantize_w(w, reorder_index, ke: int, mode=None):

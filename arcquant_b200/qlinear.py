@@ -20,7 +20,7 @@ def NVFP4_reorder_quantize_x(x: torch.Tensor, reorder_index: torch.Tensor, selec
     One pass for the amax (``arcq_absmax_bf16``) instead of ``torch.max(x.abs())``; a caller that
     already has max|x| on the device (``ops.silu_mul``) passes it as ``amax``."""
     scale = (ops.absmax(x) if amax is None else amax) / (FP8_MAX * FP4_MAX)
-    qx, scale_x = ops.reorder_quantize_x(x / scale, reorder_index, select_num, mode=mode)
+    qx, scale_x = ops.reorder_quantize_x(x, reorder_index, select_num, mode=mode, scale=scale)   # x / scale, fused
     return qx, scale_x, scale
 
 

@@ -83,6 +83,18 @@ int arcq_reference_mode(int kq);
 int arcq_reorder_quantize_x(const void* x, const int16_t* reorder_index, int64_t M, int KQ, int KE,
                             int mode, uint8_t* qx, uint8_t* sfx, void* stream);
 
+/* arcq_reorder_quantize_x on x / *scale: the division by the per-tensor scale that the reference's
+ * callers do in torch before the operator (`x / scale` in NVFP4_reorder_quantize_x,
+ * model/qLlamaLayer.py:73-77) is done while the rows are staged.  No counterpart in the reference's
+ * bindings.  scale: one fp32 in device memory (so no host round trip is needed to produce it).
+ * Every element becomes bf16(fp32(x) / fp32(bf16(*scale))), round to nearest even - what torch's CUDA
+ * kernel gives for (bf16 tensor) / (fp32 0-dim tensor), which loads the divisor in the tensor's type -
+ * and is then quantized as by arcq_reorder_quantize_x.
+ * Returns ARCQ_ERR_UNSUPPORTED_K for row widths the staging kernel does not cover (KQ/16 must be a
+ * multiple of 32 and KQ at most 16384); the caller then divides first. */
+int arcq_reorder_quantize_x_scaled(const void* x, const float* scale, const int16_t* reorder_index, int64_t M, int KQ,
+                                   int KE, int mode, uint8_t* qx, uint8_t* sfx, void* stream);
+
 /* Replaces agemm.rmsnorm_quantize_x (kernels/src/bindings.cpp:216-254 ->
  * kernels/src/rmsnorm.cu:68-281): RMSNorm with gain `gamma` (bf16 [KQ]) fused
  * in front of the mode-16 quantizer.  The sum of squares is accumulated in the

@@ -100,6 +100,31 @@ def test_every_block_maximum(kq, ke, mode):
     _check("x", x, idx, ke, mode)
 
 
+@pytest.mark.parametrize("kq,ke", [(4096, 128), (14336, 128), (11008, 64)])
+def test_fused_division_by_the_tensor_scale(kq, ke):
+    """reorder_quantize_x(x, scale=s) must give the bytes of reorder_quantize_x(x / s): every bf16 bit
+    pattern (zeros of both signs, subnormals, infinities excluded) against a spread of divisors.
+    (11008 is a width the fused kernel does not cover: the operator divides first.)"""
+    ops = _ops()
+    g = torch.Generator().manual_seed(kq)
+    bits = torch.arange(65536, dtype=torch.int32)
+    bits = bits[(bits & 0x7f80) != 0x7f80]                                   # finite values only
+    n = (bits.numel() // kq + 1) * kq
+    vals = bits[torch.randint(0, bits.numel(), (n,), generator=g)]
+    vals[:bits.numel()] = bits
+    x = vals.to(torch.int16).view(torch.bfloat16).reshape(-1, kq).contiguous().cuda()
+    idx = torch.randperm(kq, generator=g).to(torch.int16).cuda()
+    scales = [1.0, 3.0, 0.3721, 1.9999999, 7.0e-4, 2.688e3, 1.0000001, 5.960464e-8, 1.5e9, 0.99999994]
+    scales += [float(v) for v in torch.rand(12, generator=g) * 4 + 1e-3]
+    for sv in scales:
+        sc = torch.tensor(sv, dtype=torch.float32, device="cuda")
+        q, sf = ops.reorder_quantize_x(x, idx, ke, scale=sc)
+        q2, sf2 = ops.reorder_quantize_x(x / sc, idx, ke)
+        assert torch.equal(q, q2), f"codes differ for divisor {sv}"
+        a, b = valid_sf(sf, x.shape[0], kq + ke), valid_sf(sf2, x.shape[0], kq + ke)
+        assert (a == b).all(), f"scales differ for divisor {sv}"
+
+
 @pytest.mark.parametrize("kq", [2048, 3072, 3584, 4096, 5120, 8192])
 @pytest.mark.parametrize("tokens", [1, 130])
 def test_rmsnorm_quantize_x(kq, tokens):
