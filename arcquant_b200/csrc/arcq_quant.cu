@@ -1192,7 +1192,8 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
     if (wide) {
       // 256 producers, two consumer teams of 256, two gather stages, 16-bit offset table; one raw
       // stage (two if they fit)
-      const int nct = 256, npt = 256, nteams = 2;
+      // (twice the producers when they also divide by the tensor's scale)
+      const int nct = 256, npt = p.scale ? 512 : 256, nteams = 2;
       const size_t fixed = 384 + (size_t)KQ * 2;
       int R = fixed + 4 * stage <= (size_t)di.max_smem_optin ? 2 : 1;
       if (raw_env == 1 || raw_env == 2) R = raw_env;
@@ -1210,7 +1211,9 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
       // teams of 256: more row pairs in flight for the same number of warps.
       int nct = p.G < 128 ? p.G : 128;
       if (nct_env >= 32 && nct_env % 32 == 0 && nct_env <= p.G && nct_env <= 256) nct = nct_env;
-      const int npt = p.G;   // two 16-byte chunks of each row per producer thread
+      // producers: two 16-byte chunks of each row per thread (the RMSNorm summation order needs exactly
+      // that); with the division by the tensor's scale, at least 512 of them share the arithmetic
+      const int npt = (p.scale && p.G < 512) ? 512 : p.G;
       // One CTA per SM, up to 1024 threads.  Plain: one producer team (it only moves data).  RMSNorm: two
       // producer teams, each with three helper warps.  The rest, up to three teams, are consumers.
       const int ptt = npt + (rms ? 96 : 0);   // threads of a producer team
