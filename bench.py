@@ -39,8 +39,8 @@ EPS = 1e-5
 BYTES_PER_TOKEN = 2 * HIDDEN + (HIDDEN + KE) // 2 + (HIDDEN + KE) // 16      # 10568
 # dram__bytes_read + dram__bytes_write per token of the ncu capture under profiles/ (part of the output
 # stays dirty in L2 while the kernel runs, so the write part is below the algorithmic 2376 B/token):
-# (134.27 + 18.37) MB / 16384 tokens
-TRAFFIC_PER_TOKEN_NCU = 9316
+# (134.27 + 17.31) MB / 16384 tokens
+TRAFFIC_PER_TOKEN_NCU = 9252
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
