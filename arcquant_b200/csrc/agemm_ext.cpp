@@ -118,6 +118,75 @@ std::tuple<torch::Tensor, torch::Tensor> rmsnorm_quantize_x(const torch::Tensor&
   return quantize_common(X, &W, eps, reorder_index, KE, false, "run_rmsnorm_x_bf16_nvfp4");
 }
 
+// ---- extras without a counterpart in the reference's bindings (its layers call torch for these) ----
+
+// reorder_quantize_x on X / scale (scale: 0-dim fp32 CUDA tensor), the division fused into the kernel
+// where the row width allows it, done with torch first where it does not.  mode < 0: the reference's
+// choice for this KQ.
+std::tuple<torch::Tensor, torch::Tensor> reorder_quantize_x_scaled(const torch::Tensor& X, const torch::Tensor& scale,
+                                                                   const torch::Tensor& reorder_index, const int KE,
+                                                                   int mode) {
+  require_cuda(X, "input");
+  require_cuda(reorder_index, "reorder_index");
+  TORCH_CHECK(X.dim() == 2, "input must be 2-D");
+  const int64_t rows = X.size(0);
+  const int KQ = static_cast<int>(X.size(1));
+  const int K = KQ + KE;
+  if (mode < 0) mode = arcq_reference_mode(KQ);
+  c10::cuda::CUDAGuard guard(X.device());
+  auto options = torch::dtype(torch::kUInt8).device(X.device());
+  auto Q = torch::empty({rows, K / 2}, options);
+  auto SF = torch::empty({static_cast<int64_t>(arcq_sf_bytes(rows, K))}, options);
+  int status = arcq_reorder_quantize_x_scaled(X.data_ptr<at::BFloat16>(), scale.data_ptr<float>(),
+                                              reorder_index.data_ptr<int16_t>(), rows, KQ, KE, mode,
+                                              Q.data_ptr<uint8_t>(), SF.data_ptr<uint8_t>(), current_stream(X));
+  if (status == ARCQ_ERR_UNSUPPORTED_K) {
+    auto Xs = X / scale;
+    status = arcq_reorder_quantize_x(Xs.data_ptr<at::BFloat16>(), reorder_index.data_ptr<int16_t>(), rows, KQ, KE, mode,
+                                     Q.data_ptr<uint8_t>(), SF.data_ptr<uint8_t>(), current_stream(X));
+  }
+  check_status(status, "run_reorder_x_bf16_nvfp4");
+  return std::make_tuple(Q, SF);
+}
+
+std::tuple<torch::Tensor, torch::Tensor> silu_mul(const torch::Tensor& GU) {
+  require_cuda(GU, "gate_up");
+  TORCH_CHECK(GU.dim() == 2 && GU.size(1) % 16 == 0, "gate_up must be [tokens, 2F] with F a multiple of 8");
+  c10::cuda::CUDAGuard guard(GU.device());
+  const int64_t tokens = GU.size(0);
+  const int F = static_cast<int>(GU.size(1) / 2);
+  auto out = torch::empty({tokens, F}, torch::dtype(torch::kBFloat16).device(GU.device()));
+  auto amax = torch::empty({}, torch::dtype(torch::kFloat32).device(GU.device()));
+  check_status(arcq_silu_mul_bf16(GU.data_ptr<at::BFloat16>(), out.data_ptr<at::BFloat16>(), tokens, F,
+                                  amax.data_ptr<float>(), current_stream(GU)),
+               "silu_mul");
+  return std::make_tuple(out, amax);
+}
+
+torch::Tensor rope_inplace(torch::Tensor X, const torch::Tensor& cos_t, const torch::Tensor& sin_t, int heads,
+                           int head_dim) {
+  require_cuda(X, "x");
+  require_cuda(cos_t, "cos");
+  require_cuda(sin_t, "sin");
+  TORCH_CHECK(X.dim() == 2 && cos_t.dim() == 2 && cos_t.size(1) == head_dim && cos_t.sizes() == sin_t.sizes(),
+              "x must be [tokens, row]; cos / sin [seq, head_dim]");
+  c10::cuda::CUDAGuard guard(X.device());
+  check_status(arcq_rope_bf16(X.data_ptr<at::BFloat16>(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), X.size(0),
+                              static_cast<int>(X.size(1)), heads, head_dim, static_cast<int>(cos_t.size(0)),
+                              current_stream(X)),
+               "rope");
+  return X;
+}
+
+torch::Tensor absmax(const torch::Tensor& X) {
+  require_cuda(X, "input");
+  c10::cuda::CUDAGuard guard(X.device());
+  auto out = torch::empty({}, torch::dtype(torch::kFloat32).device(X.device()));
+  check_status(arcq_absmax_bf16(X.data_ptr<at::BFloat16>(), X.numel(), out.data_ptr<float>(), 0, current_stream(X)),
+               "absmax");
+  return out;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -131,6 +200,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("W"), py::arg("eps"), py::arg("reorder_index"), py::arg("KE"));
   m.def("matmul_dev_alpha", &matmul_dev_alpha, "gemm with device-resident global scales", py::arg("A"),
         py::arg("B"), py::arg("SFA"), py::arg("SFB"), py::arg("alpha_a"), py::arg("alpha_b") = py::none());
+  m.def("reorder_quantize_x_scaled", &reorder_quantize_x_scaled, "reorder_quantize_x of X / scale (device scalar)",
+        py::arg("X"), py::arg("scale"), py::arg("reorder_index"), py::arg("KE"), py::arg("mode") = -1);
+  m.def("silu_mul", &silu_mul, "(silu(gate) * up, max|.|) of [gate | up]", py::arg("gate_up"));
+  m.def("rope_inplace", &rope_inplace, "rotate-half rotary embedding in place on the first heads of each row",
+        py::arg("X"), py::arg("cos"), py::arg("sin"), py::arg("heads"), py::arg("head_dim"));
+  m.def("absmax", &absmax, "max|x| of a bf16 tensor as a 0-dim fp32 tensor", py::arg("X"));
   m.def("sf_bytes", [](int64_t rows, int64_t k_eff) { return static_cast<int64_t>(arcq_sf_bytes(rows, k_eff)); },
         "bytes of a scale-factor buffer");
 }

@@ -159,6 +159,70 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         if positions is None:
             positions = torch.arange(seq, device=x.device)
         x2d = x.reshape(bsz * seq, hidden).contiguous()
+        if self.tp > 1 and x2d.shape[0] >= 2 * self.overlap_rows and self._dist_ready():
+            return self._forward_overlapped(x2d, bsz, seq, positions).reshape(bsz, seq, hidden)
         h = x2d + tp.all_reduce_sum(self.attn_partial(x2d, bsz, seq, positions), self.group)
         out = h + tp.all_reduce_sum(self.mlp_partial(h), self.group)
         return out.reshape(bsz, seq, hidden)
+
+    overlap_rows = 4096   # rows per chunk of the overlapped schedule (a multiple of 128)
+
+    def _dist_ready(self) -> bool:
+        import torch.distributed as dist
+        return dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
+
+    @torch.no_grad()
+    def _attn_core(self, x2d, bsz, seq, positions):
+        """Everything of the attention half before the row-parallel o projection."""
+        cfg, D = self.cfg, self.cfg.head_dim
+        a, sfa = ops.rmsnorm_quantize_x(x2d, self.ln1, cfg.eps, self.qkv.index, self.qkv.select_num)
+        qkv = self.qkv.gemm(a, sfa)
+        nq, nk = self.h_local * D, self.kv_local * D
+        cos, sin = rope_tables(positions, D, cfg.rope_theta)
+        ops.rope_inplace(qkv, cos, sin, self.h_local + self.kv_local, D)
+        q = qkv[:, :nq].reshape(bsz, seq, self.h_local, D).transpose(1, 2)
+        k = qkv[:, nq:nq + nk].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
+        v = qkv[:, nq + nk:].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
+        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.h_local != self.kv_local)
+        return attn.transpose(1, 2).reshape(bsz * seq, nq).contiguous()
+
+    @torch.no_grad()
+    def _forward_overlapped(self, x2d, bsz, seq, positions):
+        """Same arithmetic as `forward`'s plain path - per-tensor scales are taken over the whole
+        tensor first, everything after them is independent per row - but the two row-parallel
+        projections run in chunks of rows whose all-reduces (NCCL, asynchronous) overlap the GEMMs
+        and element-wise work of the other chunks."""
+        import torch.distributed as dist
+
+        cfg = self.cfg
+        T = x2d.shape[0]
+        bounds = [(r, min(r + self.overlap_rows, T)) for r in range(0, T, self.overlap_rows)]
+        attn = self._attn_core(x2d, bsz, seq, positions)
+        scale_o = ops.absmax(attn) / (448.0 * 6.0)
+        o_parts, works = [], []
+        for r0, r1 in bounds:
+            qa, sfo = ops.reorder_quantize_x(attn[r0:r1], self.o.index, self.o.select_num, mode=16, scale=scale_o)
+            y = self.o.gemm(qa, sfo, scale_o)
+            works.append(dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            o_parts.append(y)
+        h = torch.empty_like(x2d)
+        acts, amaxes = [], []
+        for (r0, r1), y, w in zip(bounds, o_parts, works):
+            w.wait()
+            torch.add(x2d[r0:r1], y, out=h[r0:r1])
+            a, sfa = ops.rmsnorm_quantize_x(h[r0:r1], self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
+            act, amax = ops.silu_mul(self.gate_up.gemm(a, sfa))
+            acts.append(act)
+            amaxes.append(amax)
+        scale_d = torch.stack(amaxes).max() / (448.0 * 6.0)
+        d_parts, works = [], []
+        for act in acts:
+            qd, sfd = ops.reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16, scale=scale_d)
+            y = self.down.gemm(qd, sfd, scale_d)
+            works.append(dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            d_parts.append(y)
+        out = torch.empty_like(x2d)
+        for (r0, r1), y, w in zip(bounds, d_parts, works):
+            w.wait()
+            torch.add(h[r0:r1], y, out=out[r0:r1])
+        return out

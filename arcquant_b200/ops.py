@@ -11,6 +11,36 @@ import torch
 from . import _lib
 
 
+_EXT = None
+
+
+def _ext():
+    """The `agemm` extension module if it has been built (its calls cost about a third of a ctypes
+    call on the host), else False.  Both reach the same C ABI."""
+    global _EXT
+    if _EXT is None:
+        import importlib.util
+        import os
+        import sysconfig
+
+        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "agemm" + sysconfig.get_config_var("EXT_SUFFIX"))
+        try:
+            import sys
+
+            mod = sys.modules.get("agemm")
+            if mod is None or os.path.abspath(getattr(mod, "__file__", "")) != path:
+                if not os.path.exists(path):
+                    raise ImportError(path)
+                spec = importlib.util.spec_from_file_location("agemm", path)
+                mod = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(mod)
+                sys.modules.setdefault("agemm", mod)
+            _EXT = mod if hasattr(mod, "silu_mul") else False
+        except Exception:
+            _EXT = False
+    return _EXT
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -83,6 +113,9 @@ def _quantize(kind: str, x, gamma, eps, reorder_index, ke: int, mode, out=None, 
 def reorder_quantize_x(x, reorder_index, ke: int, mode=None, out=None, scale=None):
     """(QX u8 [M,(KQ+KE)/2], SFX u8 [sf_bytes]) = ARC-NVFP4 of bf16 x [M,KQ].
     scale (0-dim fp32 CUDA tensor): quantize ``x / scale`` instead, the division fused into the kernel."""
+    ext = _ext()
+    if ext and out is None and scale is not None and reorder_index is not None:
+        return ext.reorder_quantize_x_scaled(x, scale, reorder_index, ke, -1 if mode is None else mode)
     return _quantize("x", x, None, 0.0, reorder_index, ke, mode, out, scale)
 
 
@@ -93,6 +126,9 @@ def reorder_quantize_w(w, reorder_index, ke: int, mode=None):
 
 def rmsnorm_quantize_x(x, weight, eps: float, reorder_index, ke: int, out=None):
     """RMSNorm(x)*weight fused in front of reorder_quantize_x."""
+    ext = _ext()
+    if ext and out is None and reorder_index is not None:
+        return ext.rmsnorm_quantize_x(x, weight, float(eps), reorder_index, ke)
     return _quantize("rms", x, weight, eps, reorder_index, ke, _lib.MODE_16, out)
 
 
@@ -128,11 +164,17 @@ def matmul(a, b, sfa, sfb, scale) -> torch.Tensor:
 
 def matmul_dev_alpha(a, b, sfa, sfb, alpha_a: torch.Tensor, alpha_b: torch.Tensor | None = None) -> torch.Tensor:
     """matmul with alpha = alpha_a * alpha_b, both fp32 scalars in device memory."""
+    ext = _ext()
+    if ext and a.shape[0] > 128:      # (small problems go through the split-K entry point below)
+        return ext.matmul_dev_alpha(a, b, sfa, sfb, alpha_a, alpha_b)
     return _matmul(a, b, sfa, sfb, 1.0, alpha_a, alpha_b)
 
 
 def absmax(x: torch.Tensor) -> torch.Tensor:
     """0-dim fp32 CUDA tensor max|x| of a bf16 tensor, one pass."""
+    ext = _ext()
+    if ext and x.is_contiguous():
+        return ext.absmax(x)
     lib = _lib.load()
     _require(x, torch.bfloat16, "input")
     out = torch.empty((), dtype=torch.float32, device=x.device)
@@ -146,6 +188,9 @@ def rope_inplace(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, heads: i
     """Rotate-half rotary embedding in place on the first `heads` heads of every row of x [tokens, row]
     (bf16); cos / sin fp32 [seq, head_dim], row = token % seq.  Bit-equal to the eager
     ``(x.float() * cos + rotate_half(x.float()) * sin).to(bf16)``."""
+    ext = _ext()
+    if ext:
+        return ext.rope_inplace(x, cos, sin, heads, head_dim)
     lib = _lib.load()
     _require(x, torch.bfloat16, "x")
     _require(cos, torch.float32, "cos")
@@ -162,6 +207,9 @@ def rope_inplace(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, heads: i
 def silu_mul(gate_up: torch.Tensor, with_amax: bool = True):
     """(out bf16 [tokens, F], amax 0-dim fp32 or None) for gate_up [tokens, 2F] = [gate | up]:
     out = silu(gate) * up as eager bf16 torch computes it, max|out| in the same pass."""
+    ext = _ext()
+    if ext and with_amax:
+        return ext.silu_mul(gate_up)
     lib = _lib.load()
     _require(gate_up, torch.bfloat16, "gate_up")
     if gate_up.dim() != 2 or gate_up.shape[1] % 16:

@@ -43,6 +43,15 @@ def _worker(rank, world, port, q):
         h = x2 + sum(r.attn_partial(x2, 1, 64, pos).float() for r in ranks).to(torch.bfloat16)
         ref = (h + sum(r.mlp_partial(h).float() for r in ranks).to(torch.bfloat16)).reshape(1, 64, -1)
         err_tp = float((y.float() - ref.float()).norm() / ref.float().norm())
+        # the overlapped schedule (row chunks, asynchronous all-reduces) must give the same bytes
+        x8 = synth.activations(512, cfg.hidden, 6, synth.outlier_channels(cfg.hidden, 10, 3)).reshape(1, 512, -1).to(dev)
+        pos8 = torch.arange(512, device=dev)
+        layer = QLlamaDecoderLayerTP(cfg, W, I, tp_rank=rank, tp_size=world, device=dev)
+        y_plain = layer(x8, pos8)
+        layer.overlap_rows = 128
+        y_over = layer(x8, pos8)
+        if not torch.equal(y_plain, y_over):
+            err_tp = max(err_tp, 1.0)
         # --- expert-parallel MoE block: same per-expert batches as one rank owning every expert
         mcfg = MoEConfig(hidden=1024, ffn=2048, n_experts=4, top_k=2, select_num=64)
         MW = random_moe_weights(mcfg, 0)
