@@ -245,6 +245,41 @@ def layer_tokens_per_s(dev, world, rank, group, steps, batch=8, seq=2048):
     return batch * seq / (ms * 1e-3), ms
 
 
+def moe_tokens_per_s(dev, world, rank, steps, tokens=4096):
+    """Mixtral-8x7B-shape sparse MoE block (hidden 4096, FFN 14336, 8 experts, top-2, ARC-NVFP4 expert
+    linears, select_num 128), expert-parallel over `world` ranks; `tokens` in total, sharded over ranks."""
+    import torch
+
+    from arcquant_b200 import synth
+    from arcquant_b200.moe_block import MoEConfig, QMixtralMoEBlockEP, random_moe_weights
+
+    cfg = MoEConfig()
+    block = QMixtralMoEBlockEP(cfg, random_moe_weights(cfg, 0), ep_rank=rank, ep_size=world, device=dev)
+    out = synth.outlier_channels(cfg.hidden, 41, 1)
+    x = synth.activations(tokens, cfg.hidden, 11, out, device=dev)
+    lo, hi = rank * tokens // world, (rank + 1) * tokens // world
+    xs = x[lo:hi].contiguous()
+    for _ in range(3):
+        y = block(xs)
+    torch.cuda.synchronize()
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        y = block(xs)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return tokens / (ms * 1e-3), ms
+
+
 def run_side_workload(args):
     """--workload gemm / layer: one JSON line for that workload alone (profiling and tuning runs)."""
     import torch
@@ -271,6 +306,17 @@ def run_side_workload(args):
                               "n_gpus": world, "steps": args.steps, "ms_per_step": ms, "scaling": "strong",
                               "config": {"workload": "llama-3-8b-shape decoder layer, batch 8 x seq 2048, ARC-NVFP4 "
                                                      "linears, select_num 128", "parallelism": f"tp{world}"}}), flush=True)
+        return
+    if args.workload == "moe":
+        tps, ms = moe_tokens_per_s(dev, world, rank, args.steps)
+        if world > 1:
+            dist.destroy_process_group()
+        if rank == 0:
+            print(json.dumps({"metric": "mixtral_shape_moe_block_throughput", "value": tps, "unit": "tokens/s",
+                              "n_gpus": world, "steps": args.steps, "ms_per_step": ms, "scaling": "strong",
+                              "config": {"workload": "mixtral-8x7b-shape MoE block, 4096 tokens, 8 experts, top-2, "
+                                                     "ARC-NVFP4 expert linears, select_num 128",
+                                         "parallelism": f"ep{world}"}}), flush=True)
         return
     m, n, kq = (int(v) for v in args.shape.split(","))
     k_eff = kq + KE
@@ -433,6 +479,12 @@ def run_ours(args):
                                 "scaling": "strong"}
     except Exception as exc:  # the headline must survive a failure of the side measurements
         extra["llama_layer_error"] = repr(exc)[:200]
+    try:
+        tps, mms = moe_tokens_per_s(dev, world, rank, steps=5)
+        extra["moe_block"] = {"tokens_per_s": tps, "ms": mms, "parallelism": f"ep{world}", "tokens": 4096,
+                              "scaling": "strong"}
+    except Exception as exc:
+        extra["moe_block_error"] = repr(exc)[:200]
     if rank == 0:
         try:
             extra["gemm"] = gemm_extra(dev, hbm_peak, tf_peak)
@@ -478,7 +530,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="quantize", choices=["quantize", "quantize_plain", "gemm", "layer"],
+    ap.add_argument("--workload", default="quantize", choices=["quantize", "quantize_plain", "gemm", "layer", "moe"],
                     help="quantize (default, the headline): fused RMSNorm+reorder+NVFP4+ARC; quantize_plain: "
                          "without RMSNorm; gemm: one block-scaled GEMM shape; layer: Llama-3-8B-shape decoder layer")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per GPU for the quantize workloads")
@@ -489,7 +541,7 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload in ("gemm", "layer"):
+    elif args.workload in ("gemm", "layer", "moe"):
         run_side_workload(args)
     else:
         run_ours(args)
