@@ -167,6 +167,62 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
 
     overlap_rows = 4096   # rows per chunk of the overlapped schedule (a multiple of 128)
 
+    # ---- sequence-parallel form: the residual stream is sharded by tokens over the group
+    def _gather_quantized(self, q_s: torch.Tensor, sf_s: torch.Tensor, rows_s: int, k_eff: int):
+        """All-gather of packed codes and block scales of every rank's token shard (whole 128-row scale
+        tiles, so the shards' scale bytes concatenate): 0.56 bytes per element on the wire instead of
+        the 2 of a bf16 activation."""
+        import torch.distributed as dist
+
+        tile = ((k_eff // 16 + 3) // 4) * 512
+        span_s = (rows_s // 128) * tile
+        q = torch.empty((rows_s * self.tp, k_eff // 2), dtype=torch.uint8, device=q_s.device)
+        sf = torch.empty((ops.sf_bytes(rows_s * self.tp, k_eff),), dtype=torch.uint8, device=q_s.device)
+        dist.all_gather_into_tensor(q, q_s, group=self.group)
+        dist.all_gather_into_tensor(sf[:span_s * self.tp], sf_s[:span_s], group=self.group)
+        return q, sf
+
+    @torch.no_grad()
+    def forward_sequence_parallel(self, x_shard: torch.Tensor, bsz: int, seq: int,
+                                  positions: torch.Tensor | None = None) -> torch.Tensor:
+        """x_shard: this rank's contiguous run of bsz*seq/tp tokens [tokens/tp, hidden] (a multiple of
+        128 rows); returns the same rows of the layer's output.  RMSNorm + quantize run on the shard
+        only (not replicated), the packed result is all-gathered for the column-parallel GEMMs, and the
+        row-parallel GEMMs end in a reduce-scatter instead of an all-reduce.  Same arithmetic as
+        `forward` row for row."""
+        import torch.distributed as dist
+
+        cfg, D = self.cfg, self.cfg.head_dim
+        T, rows_s = bsz * seq, x_shard.shape[0]
+        if rows_s * self.tp != T or rows_s % 128:
+            raise ValueError("token shards must be equal and multiples of 128 rows")
+        if positions is None:
+            positions = torch.arange(seq, device=x_shard.device)
+        k_eff = cfg.hidden + self.qkv.select_num
+        a_s, sfa_s = ops.rmsnorm_quantize_x(x_shard, self.ln1, cfg.eps, self.qkv.index, self.qkv.select_num)
+        a, sfa = self._gather_quantized(a_s, sfa_s, rows_s, k_eff)
+        qkv = self.qkv.gemm(a, sfa)
+        nq, nk = self.h_local * D, self.kv_local * D
+        cos, sin = rope_tables(positions, D, cfg.rope_theta)
+        ops.rope_inplace(qkv, cos, sin, self.h_local + self.kv_local, D)
+        q = qkv[:, :nq].reshape(bsz, seq, self.h_local, D).transpose(1, 2)
+        k = qkv[:, nq:nq + nk].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
+        v = qkv[:, nq + nk:].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
+        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.h_local != self.kv_local)
+        attn = attn.transpose(1, 2).reshape(T, nq).contiguous()
+        qa, sfo, so = NVFP4_reorder_quantize_x(attn, self.o.index, self.o.select_num, mode=16)
+        y = self.o.gemm(qa, sfo, so)
+        y_s = torch.empty_like(x_shard)
+        dist.reduce_scatter_tensor(y_s, y, op=dist.ReduceOp.SUM, group=self.group)
+        h_s = x_shard + y_s
+        a_s, sfa_s = ops.rmsnorm_quantize_x(h_s, self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
+        a, sfa = self._gather_quantized(a_s, sfa_s, rows_s, k_eff)
+        act, amax = ops.silu_mul(self.gate_up.gemm(a, sfa))
+        qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16, amax=amax)
+        y = self.down.gemm(qd, sfd, sd)
+        dist.reduce_scatter_tensor(y_s, y, op=dist.ReduceOp.SUM, group=self.group)
+        return h_s + y_s
+
     def _dist_ready(self) -> bool:
         import torch.distributed as dist
         return dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1

@@ -209,7 +209,7 @@ def gemm_extra(dev, hbm_peak, tf_peak):
     return res
 
 
-def layer_tokens_per_s(dev, world, rank, group, steps, batch=8, seq=2048):
+def layer_tokens_per_s(dev, world, rank, group, steps, batch=8, seq=2048, sequence_parallel=False):
     """Llama-3-8B-shape decoder layer (hidden 4096, 32/8 heads, FFN 14336, all seven linears
     ARC-NVFP4 with select_num 128), tensor-parallel over `world` ranks, prefill of batch x seq tokens."""
     import torch
@@ -224,8 +224,14 @@ def layer_tokens_per_s(dev, world, rank, group, steps, batch=8, seq=2048):
     out = synth.outlier_channels(cfg.hidden, 41, 1)
     x = synth.activations(batch * seq, cfg.hidden, 7, out, device=dev).reshape(batch, seq, cfg.hidden)
     pos = torch.arange(seq, device=dev)
+    if sequence_parallel:     # residual stream sharded by tokens: this rank's contiguous run of rows
+        rows = batch * seq // world
+        xs = x.reshape(batch * seq, cfg.hidden)[rank * rows:(rank + 1) * rows].contiguous()
+        step = lambda: layer.forward_sequence_parallel(xs, batch, seq, pos)
+    else:
+        step = lambda: layer(x, pos)
     for _ in range(3):
-        y = layer(x, pos)
+        y = step()
     torch.cuda.synchronize()
     if group is not None or world > 1:
         import torch.distributed as dist
@@ -233,7 +239,7 @@ def layer_tokens_per_s(dev, world, rank, group, steps, batch=8, seq=2048):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        y = layer(x, pos)
+        y = step()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
@@ -479,6 +485,13 @@ def run_ours(args):
                                 "scaling": "strong"}
     except Exception as exc:  # the headline must survive a failure of the side measurements
         extra["llama_layer_error"] = repr(exc)[:200]
+    if world > 1:
+        try:
+            tps, lms = layer_tokens_per_s(dev, world, rank, None, steps=5, sequence_parallel=True)
+            extra["llama_layer_sequence_parallel"] = {"tokens_per_s": tps, "ms": lms, "parallelism": f"tp{world}+sp",
+                                                      "tokens": 8 * 2048, "scaling": "strong"}
+        except Exception as exc:
+            extra["llama_layer_sequence_parallel_error"] = repr(exc)[:200]
     try:
         tps, mms = moe_tokens_per_s(dev, world, rank, steps=5)
         extra["moe_block"] = {"tokens_per_s": tps, "ms": mms, "parallelism": f"ep{world}", "tokens": 4096,

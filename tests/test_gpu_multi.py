@@ -52,6 +52,13 @@ def _worker(rank, world, port, q):
         y_over = layer(x8, pos8)
         if not torch.equal(y_plain, y_over):
             err_tp = max(err_tp, 1.0)
+        # sequence-parallel form: this rank's token shard in, the same rows of the output back
+        rows_s = 512 // world
+        y_sp = layer.forward_sequence_parallel(x8.reshape(512, -1)[rank * rows_s:(rank + 1) * rows_s].contiguous(), 1, 512, pos8)
+        ref_sp = y_plain.reshape(512, -1)[rank * rows_s:(rank + 1) * rows_s]
+        err_sp = float((y_sp.float() - ref_sp.float()).norm() / ref_sp.float().norm())
+        if err_sp > 2e-3:      # (bit-equal with two ranks; a sum of more partials may be ordered differently)
+            err_tp = max(err_tp, 1.0 + err_sp)
         # --- expert-parallel MoE block: same per-expert batches as one rank owning every expert
         mcfg = MoEConfig(hidden=1024, ffn=2048, n_experts=4, top_k=2, select_num=64)
         MW = random_moe_weights(mcfg, 0)
