@@ -803,14 +803,49 @@ int launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int nu
 }  // namespace
 
 // Narrowest tile width and K split the launcher would use for a skinny problem.
-static void plan_splitk(int64_t M, int64_t N, int64_t K_eff, int num_sms, int* bn_out, int* splits_out) {
+static void plan_splitk(int64_t M, int64_t N, int64_t K_eff, int num_sms, int* bn_out, int* splits_out,
+                        bool allow_split = true) {
   const int tiles_m = (int)((M + BM - 1) / BM);
   int bn = 256;
   while (bn > 64 && (long long)tiles_m * ((N + bn - 1) / bn) < num_sms) bn >>= 1;
   const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn);
   const int kstages = (int)((K_eff / 64 + KSTEPS - 1) / KSTEPS);
   int splits = 1;
-  if (tiles * 2 <= num_sms) {
+  static const int bn_env = [] { const char* e = getenv("ARCQ_GEMM_SK_BN"); return e ? atoi(e) : 0; }();
+  static const int sp_env = [] { const char* e = getenv("ARCQ_GEMM_SK_SPLITS"); return e ? atoi(e) : 0; }();
+  if (bn_env && sp_env) {   // tuning knob: force a tile width and a split count
+    splits = sp_env;
+    while (splits > 1 && (splits - 1) * ((kstages + splits - 1) / splits) >= kstages) --splits;
+    *bn_out = bn_env;
+    *splits_out = splits;
+    return;
+  }
+  if (tiles_m == 1) {
+    // One row of tiles (M <= 128: weight streaming).  The K loop is a serial chain of stages whose
+    // latency, not bandwidth, sets the time; splitting K shortens the chain at the price of a second
+    // kernel that adds the fp32 partial sums.  Pick tile width and split count by a small cost model
+    // fitted to measurements on B200 (microseconds: ~5 fixed, 0.35 + 0.65 * bn/256 per stage of the
+    // chain, 2 + 0.35 per MB of partial sums when split), among the choices that fit one wave of CTAs
+    // and 8 MB of scratch.  Measured: N 6144, M 16: 15.4 -> 9.6 us; N 4096 / K 14464, M 16: 24.7 -> 13.4 us.
+    double best = 1e30;
+    int best_bn = 64, best_splits = 1;
+    for (int cand = 64; cand <= 256; cand <<= 1) {
+      const long long t = (N + cand - 1) / cand;
+      for (int sp = 1; sp <= (allow_split ? 8 : 1); ++sp) {
+        if (t * sp > num_sms && sp > 1) break;
+        if (sp > 1 && sp > kstages / 2) break;
+        if (sp > 1 && (sp - 1) * ((kstages + sp - 1) / sp) >= kstages) continue;   // an empty range
+        const double ws_mb = sp > 1 ? (double)sp * (double)M * (double)N * 4.0 / (1 << 20) : 0.0;
+        if (ws_mb > 8.0) break;
+        const double waves = (double)((t * sp + num_sms - 1) / num_sms);
+        const double cost = 5.0 + waves * ((kstages + sp - 1) / sp) * (0.35 + 0.65 * cand / 256.0) +
+                            (sp > 1 ? 2.0 + 0.35 * ws_mb : 0.0);
+        if (cost < best) { best = cost; best_bn = cand; best_splits = sp; }
+      }
+    }
+    bn = best_bn;
+    splits = best_splits;
+  } else if (tiles * 2 <= num_sms) {
     splits = (int)(num_sms / tiles);
     if (splits > 8) splits = 8;
     if (splits > kstages / 2) splits = kstages / 2;   // at least two stages per range
@@ -874,13 +909,17 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
 
   // Skinny problems (few output tiles, long K): split K over otherwise idle SMs when the caller
   // provided scratch for the fp32 partial sums.
-  if (workspace != nullptr && !getenv("ARCQ_GEMM_BN")) {
+  if (!getenv("ARCQ_GEMM_BN")) {
     int bn2, splits;
-    plan_splitk(M, N, K_eff, di.num_sms, &bn2, &splits);
-    if (splits > 1 && workspace_bytes >= (size_t)splits * (size_t)M * (size_t)N * sizeof(float)) {
+    plan_splitk(M, N, K_eff, di.num_sms, &bn2, &splits, workspace != nullptr);
+    if (splits > 1 && workspace_bytes < (size_t)splits * (size_t)M * (size_t)N * sizeof(float))
+      plan_splitk(M, N, K_eff, di.num_sms, &bn2, &splits, false);   // scratch too small: do not split
+    if (splits > 1) {
       bn = bn2;
       p.ws = static_cast<float*>(workspace);
       p.splits = splits;
+    } else if (p.tiles_m == 1) {
+      bn = bn2;   // single row of tiles: the cost model also picks the width of an unsplit launch
     }
   }
 

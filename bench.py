@@ -105,6 +105,10 @@ class ClockSampler:
                 out["sm_max_mhz"] = float(rows[0][1])
             except Exception:
                 pass
+            try:
+                out["power_w_max"] = max(float(r[2]) for r in rows)
+            except Exception:
+                pass
             names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
             for i, n in enumerate(names):
                 if any(r[3 + i].lower().startswith("active") for r in rows):
@@ -334,18 +338,23 @@ def run_side_workload(args):
     for _ in range(max(args.warmup, 3)):
         c = ops.matmul(a, b, sfa, sfb, 1.0)
     torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if args.steps >= 50:      # long enough for nvidia-smi to sample the clocks under this load
+        sampler.start()
+        time.sleep(0.25)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
         c = ops.matmul(a, b, sfa, sfb, 1.0)
     e1.record()
     torch.cuda.synchronize()
+    clocks = sampler.stop() if args.steps >= 50 else None
     ms = e0.elapsed_time(e1) / args.steps
     tf = 2.0 * m * n * k_eff / (ms * 1e-3) / 1e12
     err = ops.gemm_poll_error()
     if rank == 0:
         print(json.dumps({"metric": "arc_nvfp4_gemm_throughput", "value": tf, "unit": "TFLOP/s", "n_gpus": 1,
-                          "steps": args.steps, "ms_per_step": ms, "device_wait_error": err,
+                          "steps": args.steps, "ms_per_step": ms, "device_wait_error": err, "clocks": clocks,
                           "config": {"workload": f"block-scaled NVFP4 GEMM M {m} N {n} K_eff {k_eff}"},
                           "roofline": {"bound": "tensor", "achieved": tf, "peak": 4 * tf_peak, "unit": "TFLOP/s",
                                        "frac": tf / (4 * tf_peak), "peak_kind": f"4 x {peak_kind} bf16 cuBLAS peak",

@@ -172,7 +172,12 @@ def test_large_shapes_by_row_independence_and_samples(m, n, kq):
         dst = (cols // 4) * 512 + (j % 32) * 16 + ((j // 32) % 4) * 4 + cols % 4
         sfsub[dst] = sfh[src]
     csub = ops.matmul(asub, b, torch.from_numpy(sfsub).to(dev), sfb, alpha)
-    assert torch.equal(csub, c[rows.to(dev)])
+    # (a skinny problem may be split over K: same products, fp32 partial sums added in another order,
+    # so a few outputs can land on the neighbouring bf16 value)
+    ref_rows = c[rows.to(dev)]
+    same = (csub == ref_rows).float().mean().item()
+    rel = ((csub.float() - ref_rows.float()).norm() / ref_rows.float().norm()).item()
+    assert same > 0.995 and rel < 1e-3, (same, rel)
     ref = O.gemm_fast(asub.cpu().numpy(), sfsub, b.cpu().numpy(), sfb.cpu().numpy(), alpha)
     _assert_close(csub.float().cpu().numpy(), ref)
     # and against the unquantised product the ARC error stays in the expected band

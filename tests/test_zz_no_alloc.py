@@ -31,7 +31,7 @@ def _packed(m, n, kq, ke, seed):
     return a, sfa, b, sfb, float(sx * sw)
 
 
-@pytest.mark.parametrize("m,n,kq", [(16, 4096, 4096), (64, 4096, 14336), (1, 1024, 4096)])
+@pytest.mark.parametrize("m,n,kq", [(16, 4096, 4096), (16, 4096, 14336), (1, 1024, 4096)])
 def test_static_scratch_matches_caller_scratch_twice_in_a_row(m, n, kq):
     from arcquant_b200 import _lib, ops
 
