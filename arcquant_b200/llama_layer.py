@@ -80,15 +80,50 @@ def apply_rope(t: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return (tf * cos + rot * sin).to(t.dtype)
 
 
-class PackedLinear:
-    """Packed NVFP4 weight + the channel order / KE its activation must be quantized with."""
+class PackedLinear(torch.nn.Module):
+    """Packed NVFP4 weight + the channel order / KE its activation must be quantized with.
 
-    def __init__(self, weight: torch.Tensor, index: torch.Tensor, select_num: int):
+    Codes, block scales, the per-tensor scale, the int16 channel order and KE are registered buffers:
+    a layer's ``state_dict`` carries everything needed to run it, and ``from_packed`` rebuilds the
+    linear from those buffers without touching the bf16 weight again (the reference re-derives them
+    from the bf16 checkpoint at every load, model/qLinearLayer.py:25-28,55)."""
+
+    BUFFERS = ("W", "SFW", "scale", "index", "select_num_t")
+
+    def __init__(self, weight: torch.Tensor | None, index: torch.Tensor | None, select_num: int = 0):
+        super().__init__()
+        if weight is None:      # filled by from_packed
+            return
         dev = weight.device
-        self.index = index.to(torch.int16).to(dev).contiguous()
-        self.select_num = select_num
-        self.W, self.SFW, self.scale = NVFP4_reorder_quantize_w(weight.contiguous(), self.index, select_num, mode=16)
-        self.scale = self.scale.reshape(())
+        idx = index.to(torch.int16).to(dev).contiguous()
+        W, SFW, scale = NVFP4_reorder_quantize_w(weight.contiguous(), idx, select_num, mode=16)
+        self._set(W, SFW, scale.reshape(()), idx, select_num)
+
+    def _set(self, W, SFW, scale, index, select_num: int):
+        self.register_buffer("W", W)
+        self.register_buffer("SFW", SFW)
+        self.register_buffer("scale", scale.to(torch.float32).reshape(()))
+        self.register_buffer("index", index.to(torch.int16))
+        self.register_buffer("select_num_t", torch.tensor(int(select_num), dtype=torch.int32))
+        self.select_num = int(select_num)
+
+    @classmethod
+    def from_packed(cls, state: dict, prefix: str = "", device=None) -> "PackedLinear":
+        """Rebuild from the buffers of a saved ``state_dict`` (keys ``prefix + name``)."""
+        missing = [n for n in cls.BUFFERS if prefix + n not in state]
+        if missing:
+            raise KeyError(f"packed linear '{prefix}': missing {missing}")
+        get = lambda n: state[prefix + n] if device is None else state[prefix + n].to(device)
+        W, SFW, index = get("W"), get("SFW"), get("index")
+        select_num = int(state[prefix + "select_num_t"])
+        kq = index.numel()
+        if W.dtype != torch.uint8 or SFW.dtype != torch.uint8 or index.dtype != torch.int16:
+            raise ValueError(f"packed linear '{prefix}': wrong buffer dtypes")
+        if W.dim() != 2 or W.shape[1] * 2 != kq + select_num:
+            raise ValueError(f"packed linear '{prefix}': codes [{tuple(W.shape)}] do not match KQ {kq} + KE {select_num}")
+        self = cls(None, None)
+        self._set(W.contiguous(), SFW.contiguous(), get("scale"), index.contiguous(), select_num)
+        return self
 
     def gemm(self, qx, sfx, scale_x=None):
         if scale_x is None:
@@ -122,8 +157,34 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         self.down = PackedLinear(to(weights["w_down"][:, f0:f1]).contiguous(),
                                  tp.local_reorder_index(indices["down"], f0, f1),
                                  tp.shard_select_num(cfg.select_num, tp_size, f1 - f0))
-        self.ln1, self.ln2 = to(weights["ln1"]).contiguous(), to(weights["ln2"]).contiguous()
+        self.register_buffer("ln1", to(weights["ln1"]).contiguous())
+        self.register_buffer("ln2", to(weights["ln2"]).contiguous())
         self.f_local = f1 - f0
+
+    @classmethod
+    def from_packed(cls, cfg: LlamaLayerConfig, state: dict, tp_rank: int = 0, tp_size: int = 1, group=None,
+                    device="cuda") -> "QLlamaDecoderLayerTP":
+        """Rebuild one rank's layer from the ``state_dict`` of a layer built for the same
+        (tp_rank, tp_size): packed codes, scales, channel orders and norm gains, no bf16 weights."""
+        self = cls.__new__(cls)
+        torch.nn.Module.__init__(self)
+        self.cfg, self.rank, self.tp, self.group = cfg, tp_rank, tp_size, group
+        if cfg.n_heads % tp_size or cfg.n_kv_heads % tp_size or cfg.ffn % tp_size:
+            raise ValueError("heads / kv heads / ffn must split over the tensor-parallel group")
+        dev = torch.device(device)
+        self.h_local = cfg.n_heads // tp_size
+        self.kv_local = cfg.n_kv_heads // tp_size
+        self.f_local = cfg.ffn // tp_size
+        for name in ("qkv", "gate_up", "o", "down"):
+            setattr(self, name, PackedLinear.from_packed(state, name + ".", dev))
+        want = {"qkv": (self.h_local + 2 * self.kv_local) * cfg.head_dim, "gate_up": 2 * self.f_local,
+                "o": cfg.hidden, "down": cfg.hidden}
+        for name, rows in want.items():
+            if getattr(self, name).W.shape[0] != rows:
+                raise ValueError(f"{name}: {getattr(self, name).W.shape[0]} output rows, expected {rows} for tp_size {tp_size}")
+        self.register_buffer("ln1", state["ln1"].to(dev).contiguous())
+        self.register_buffer("ln2", state["ln2"].to(dev).contiguous())
+        return self
 
     # ---- halves of the layer up to (and excluding) the all-reduce: usable for in-process emulation
     @torch.no_grad()

@@ -226,3 +226,18 @@ def test_silu_mul_equals_eager_torch_and_returns_the_maximum():
     out, amax = ops.silu_mul(gu)
     assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
     assert float(amax) == float(ref.abs().max())
+
+
+def test_packed_layer_checkpoint_round_trip(tmp_path):
+    """A layer rebuilt from its saved packed buffers (no bf16 weights) gives the same bytes."""
+    from arcquant_b200 import checkpoint
+    from arcquant_b200.llama_layer import LlamaLayerConfig, QLlamaDecoderLayerTP, random_layer_weights, random_reorder_indices
+
+    cfg = LlamaLayerConfig(hidden=1024, n_heads=8, n_kv_heads=4, head_dim=128, ffn=2048, select_num=64)
+    layer = QLlamaDecoderLayerTP(cfg, random_layer_weights(cfg, 0), random_reorder_indices(cfg, 1))
+    x = synth.activations(256, cfg.hidden, 4, synth.outlier_channels(cfg.hidden, 10, 3)).reshape(2, 128, -1).cuda()
+    y = layer(x)
+    path = str(tmp_path / "layer.pt")
+    checkpoint.save_packed_layer(layer, path)
+    again = checkpoint.load_packed_layer(cfg, path)
+    assert torch.equal(again(x), y)
