@@ -814,7 +814,7 @@ static void plan_splitk(int64_t M, int64_t N, int64_t K_eff, int num_sms, int* b
   static const int bn_env = [] { const char* e = getenv("ARCQ_GEMM_SK_BN"); return e ? atoi(e) : 0; }();
   static const int sp_env = [] { const char* e = getenv("ARCQ_GEMM_SK_SPLITS"); return e ? atoi(e) : 0; }();
   if (bn_env && sp_env) {   // tuning knob: force a tile width and a split count
-    splits = sp_env;
+    splits = allow_split ? sp_env : 1;
     while (splits > 1 && (splits - 1) * ((kstages + splits - 1) / splits) >= kstages) --splits;
     *bn_out = bn_env;
     *splits_out = splits;
@@ -845,7 +845,7 @@ static void plan_splitk(int64_t M, int64_t N, int64_t K_eff, int num_sms, int* b
     }
     bn = best_bn;
     splits = best_splits;
-  } else if (tiles * 2 <= num_sms) {
+  } else if (allow_split && tiles * 2 <= num_sms) {
     splits = (int)(num_sms / tiles);
     if (splits > 8) splits = 8;
     if (splits > kstages / 2) splits = kstages / 2;   // at least two stages per range
@@ -914,6 +914,7 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
     plan_splitk(M, N, K_eff, di.num_sms, &bn2, &splits, workspace != nullptr);
     if (splits > 1 && workspace_bytes < (size_t)splits * (size_t)M * (size_t)N * sizeof(float))
       plan_splitk(M, N, K_eff, di.num_sms, &bn2, &splits, false);   // scratch too small: do not split
+    if (splits > 1 && workspace == nullptr) splits = 1;             // (never split without scratch)
     if (splits > 1) {
       bn = bn2;
       p.ws = static_cast<float*>(workspace);

@@ -747,6 +747,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   // buffers) and reciprocal roots ready (x2)
   const uint32_t rawe0 = raw0 + 8 * R, psr0 = rawe0 + 8 * R, rsr0 = psr0 + 8 * 4;
 
+  asm volatile("griddepcontrol.launch_dependents;");   // the next kernel of the stream may be set up now
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, (uint32_t)(npt >> 5));    // one arrival per producer warp
@@ -763,6 +764,9 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     abort_flag[0] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // Everything before this line touched shared memory only; global memory may still be written by
+  // the previous kernel of the stream (no-op unless launched as a programmatic dependent).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // Offsets are laid out [vector v][group g][entries of one 128-bit load]: consecutive lanes (groups)
   // read consecutive 16 bytes, so every table load is conflict free.
   for (int j = tid; j < KQ; j += blockDim.x) {
@@ -1105,14 +1109,35 @@ template <bool RMS, bool WIDE, bool SCALED, int S, int R>
 int launch_ws(const QuantParams& p, int nct, int npt, int nteams, int npteams, size_t smem, const DeviceInfo& di,
               cudaStream_t stream) {
   auto kern = arcq_quantize_ws_kernel<RMS, WIDE, SCALED, S, R>;
-  ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  int occ = 0;
   const int threads = nteams * nct + npteams * (npt + (RMS ? 96 : 0));
-  ARCQ_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, smem));
+  // the attribute and the occupancy query cost host time: once per (device, block size, shared memory)
+  static thread_local int c_dev = -1, c_threads = 0, c_occ = 0;
+  static thread_local size_t c_smem = 0;
+  int occ = 0;
+  if (c_dev == di.device && c_threads == threads && c_smem == smem) {
+    occ = c_occ;
+  } else {
+    ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    ARCQ_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, smem));
+    c_dev = di.device; c_threads = threads; c_smem = smem; c_occ = occ;
+  }
   if (occ < 1) return ARCQ_ERR_UNSUPPORTED_K;
   long long grid = (long long)di.num_sms * occ;
   if (grid > p.npairs) grid = p.npairs;
-  kern<<<(unsigned)grid, threads, smem, stream>>>(p, nct, npt, nteams, npteams);
+  // Programmatic dependent launch: the grid may be set up while the previous kernel of the stream is
+  // still draining; the kernel itself waits (griddepcontrol.wait) before it touches global memory.
+  static const int pdl_env = [] { const char* e = getenv("ARCQ_QUANT_PDL"); return e ? atoi(e) : 1; }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_env ? 1 : 0;
+  ARCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p, nct, npt, nteams, npteams));
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
 }
