@@ -94,10 +94,15 @@ torch::Tensor matmul_dev_alpha(const torch::Tensor& A, const torch::Tensor& B, c
   const int64_t M = A.size(0), N = B.size(0), K = A.size(1) * 2;
   c10::cuda::CUDAGuard guard(A.device());
   auto C = torch::empty({M, N}, torch::dtype(torch::kBFloat16).device(A.device()));
-  int status = arcq_matmul_nvfp4_dev_alpha(
-      A.data_ptr<uint8_t>(), B.data_ptr<uint8_t>(), SFA.data_ptr<uint8_t>(), SFB.data_ptr<uint8_t>(), M, N, K,
+  // skinny problems split K over idle SMs; the fp32 partial sums need scratch
+  const int64_t ws_bytes = static_cast<int64_t>(arcq_matmul_workspace_bytes(M, N, K));
+  torch::Tensor ws;
+  if (ws_bytes > 0) ws = torch::empty({ws_bytes}, torch::dtype(torch::kUInt8).device(A.device()));
+  int status = arcq_matmul_nvfp4_ws(
+      A.data_ptr<uint8_t>(), B.data_ptr<uint8_t>(), SFA.data_ptr<uint8_t>(), SFB.data_ptr<uint8_t>(), M, N, K, 1.0f,
       alpha_a.data_ptr<float>(), alpha_b.has_value() ? alpha_b->data_ptr<float>() : nullptr,
-      C.data_ptr<at::BFloat16>(), current_stream(A));
+      C.data_ptr<at::BFloat16>(), ws_bytes > 0 ? ws.data_ptr() : nullptr, static_cast<size_t>(ws_bytes),
+      current_stream(A));
   check_status(status, "matmul_host_nvfp4_bf16");
   return C;
 }

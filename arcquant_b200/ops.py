@@ -165,7 +165,7 @@ def matmul(a, b, sfa, sfb, scale) -> torch.Tensor:
 def matmul_dev_alpha(a, b, sfa, sfb, alpha_a: torch.Tensor, alpha_b: torch.Tensor | None = None) -> torch.Tensor:
     """matmul with alpha = alpha_a * alpha_b, both fp32 scalars in device memory."""
     ext = _ext()
-    if ext and a.shape[0] > 128:      # (small problems go through the split-K entry point below)
+    if ext:
         return ext.matmul_dev_alpha(a, b, sfa, sfb, alpha_a, alpha_b)
     return _matmul(a, b, sfa, sfb, 1.0, alpha_a, alpha_b)
 

@@ -53,6 +53,14 @@ def test_argument_validation_precedes_any_cuda_call():
     assert L.arcq_matmul_nvfp4(p, p, p, p, 4, 60, 128, 1.0, p, None) == _lib.ERR_BAD_SHAPE     # N % 8
     assert L.arcq_matmul_nvfp4(p, p, p, p, 0, 64, 128, 1.0, p, None) == _lib.OK                # empty M
     assert L.arcq_reorder_quantize_x(p, None, 0, 64, 0, 16, p, p, None) == _lib.OK             # empty input
+    assert L.arcq_reorder_quantize_x_scaled(p, None, None, 4, 64, 0, 16, p, p, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_reorder_quantize_x_scaled(p, p, None, 4, 72, 0, 16, p, p, None) == _lib.ERR_BAD_SHAPE
+    assert L.arcq_rope_bf16(p, p, p, 4, 512, 2, 120, 8, None) == _lib.ERR_BAD_SHAPE            # head_dim % 16
+    assert L.arcq_rope_bf16(p, p, p, 4, 512, 5, 128, 8, None) == _lib.ERR_BAD_SHAPE            # heads beyond the row
+    assert L.arcq_rope_bf16(p, None, p, 4, 512, 2, 128, 8, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_rope_bf16(p, p, p, 0, 512, 2, 128, 8, None) == _lib.OK                       # no tokens
+    assert L.arcq_silu_mul_bf16(p, p, 4, 100, None, None) == _lib.ERR_BAD_SHAPE                # F % 8
+    assert L.arcq_silu_mul_bf16(None, p, 4, 128, None, None) == _lib.ERR_NULL_POINTER
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-device behaviour")
