@@ -748,6 +748,19 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   const uint32_t rawe0 = raw0 + 8 * R, psr0 = rawe0 + 8 * R, rsr0 = psr0 + 8 * 4;
 
   asm volatile("griddepcontrol.launch_dependents;");   // the next kernel of the stream may be set up now
+  const uint32_t stride = gridDim.x;
+  // Bulk copies of the rows of `unit` into raw stage `rs` (one thread).
+  auto issue = [&](uint32_t unit, uint32_t rs) {
+    if (unit >= npairs) return;
+    const uint32_t r0 = 2 * unit;
+    const bool has1 = (r0 + 1) < rows;
+    const uint32_t bar = raw0 + 8 * rs;
+    const uint32_t dst = smem_addr(raw + (size_t)rs * stage_bytes);
+    const uint16_t* src = p.x + (size_t)r0 * (size_t)KQ;
+    mbar_expect_tx(bar, has1 ? 2 * row_in_bytes : row_in_bytes);
+    bulk_load(dst, src, row_in_bytes, bar);
+    if (has1) bulk_load(dst + row_in_bytes, src + KQ, row_in_bytes, bar);
+  };
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, (uint32_t)(npt >> 5));    // one arrival per producer warp
@@ -763,6 +776,11 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     }
     abort_flag[0] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the bulk copies see the barriers
+    // The first R row pairs start streaming in while the CTA builds its tables (global memory may
+    // still be written by the previous kernel of the stream until this wait returns).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (uint32_t r = 0; r < (uint32_t)R; ++r) issue(blockIdx.x + r * stride, r);
   }
   // Everything before this line touched shared memory only; global memory may still be written by
   // the previous kernel of the stream (no-op unless launched as a programmatic dependent).
@@ -777,7 +795,6 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   }
   __syncthreads();
 
-  const uint32_t stride = gridDim.x;
   const int ncons = nteams * nct;
   if (tid >= ncons) {
     // ------------------------------------------------------------------ producers
@@ -793,18 +810,6 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     const uint32_t n = (npairs - blockIdx.x + stride - 1) / stride;   // row pairs of this CTA
     const uint32_t nt = n > (uint32_t)pteam ? (n - pteam + NP - 1) / NP : 0;   // pairs of this team
     const uint32_t psr = psr0 + 16 * pteam, rsr = rsr0 + 16 * pteam;           // this team's barrier pairs
-    // Bulk copies of the rows of `unit` into raw stage `rs` (one thread).
-    auto issue = [&](uint32_t unit, uint32_t rs) {
-      if (unit >= npairs) return;
-      const uint32_t r0 = 2 * unit;
-      const bool has1 = (r0 + 1) < rows;
-      const uint32_t bar = raw0 + 8 * rs;
-      const uint32_t dst = smem_addr(raw + (size_t)rs * stage_bytes);
-      const uint16_t* src = p.x + (size_t)r0 * (size_t)KQ;
-      mbar_expect_tx(bar, has1 ? 2 * row_in_bytes : row_in_bytes);
-      bulk_load(dst, src, row_in_bytes, bar);
-      if (has1) bulk_load(dst + row_in_bytes, src + KQ, row_in_bytes, bar);
-    };
     if (RMS && ptid >= npt) {
       const int helper = (ptid - npt) >> 5;
       if (helper < 2) {
@@ -820,7 +825,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       } else if (lane == 0) {
         // -------------------------------------------------------------- loader
         uint32_t next = (uint32_t)pteam;    // first pair of this team whose copies are not started yet
-        for (; next < n && next < (uint32_t)R; next += NP) issue(blockIdx.x + next * stride, next % R);
+        while (next < n && next < (uint32_t)R) next += NP;   // (the first R pairs were started in the prologue)
         // Stay until the producers have taken the team's last pair (or the CTA aborts): every stage that
         // comes back is refilled with the pair R further on, while there is one.
         uint32_t freed = (uint32_t)pteam;   // first pair of this team whose stage is not handed back yet
@@ -868,8 +873,6 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       gn0 = reinterpret_cast<const uint4*>(p.gamma)[c0];
       gn1 = reinterpret_cast<const uint4*>(p.gamma)[c1];
     }
-    if (!RMS && ptid == 0)   // (with RMSNorm the loader warp starts the copies)
-      for (uint32_t r = 0; r < (uint32_t)R; ++r) issue(blockIdx.x + r * stride, r);
 
     const uint4 zero = make_uint4(0, 0, 0, 0);
     auto read_raw = [&](uint32_t j, bool has1, uint4& a0, uint4& a1, uint4& b0, uint4& b1) {
