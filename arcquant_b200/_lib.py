@@ -45,6 +45,7 @@ SIGNATURES = {
     "arcq_absmax_bf16": (_i32, [_vp, _i64, _vp, _i32, _vp]),
     "arcq_rope_bf16": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp]),
     "arcq_silu_mul_bf16": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
+    "arcq_moe_combine_bf16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
 }
 
 _lib = None

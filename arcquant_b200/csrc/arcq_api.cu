@@ -204,6 +204,15 @@ int arcq_silu_mul_bf16(const void* gate_up, void* out, int64_t tokens, int F, fl
   return launch_silu_mul(gate_up, out, tokens, F, amax, (cudaStream_t)stream);
 }
 
+int arcq_moe_combine_bf16(const void* y, const int32_t* pos, const void* weights, void* out, int64_t tokens, int hidden,
+                          int top_k, void* stream) {
+  if (tokens < 0 || hidden <= 0 || hidden % 8 || top_k < 1) return ARCQ_ERR_BAD_SHAPE;
+  if (tokens == 0) return ARCQ_OK;
+  if (!y || !pos || !weights || !out) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(y) || !aligned16(out)) return ARCQ_ERR_ALIGNMENT;
+  return launch_moe_combine(y, pos, weights, out, tokens, hidden, top_k, (cudaStream_t)stream);
+}
+
 int arcq_absmax_bf16(const void* x, int64_t n, float* out, int accumulate, void* stream) {
   if (n < 0) return ARCQ_ERR_BAD_SHAPE;
   if (!out || (n > 0 && !x)) return ARCQ_ERR_NULL_POINTER;

@@ -43,6 +43,8 @@ int launch_gemm_static(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, c
 int launch_rope(void* x, const float* cos_t, const float* sin_t, int64_t tokens, int row_elems, int heads, int dim,
                 int seq, cudaStream_t stream);
 int launch_silu_mul(const void* gu, void* out, int64_t tokens, int F, float* amax, cudaStream_t stream);
+int launch_moe_combine(const void* y, const int* pos, const void* w, void* out, int64_t tokens, int hidden, int k,
+                       cudaStream_t stream);
 int gemm_poll_error();
 // Same for the bounded waits of the warp-specialised quantizer.
 int quant_poll_error();

@@ -97,7 +97,56 @@ __global__ void arcq_silu_mul_kernel(const uint16_t* __restrict__ gu, uint16_t* 
   }
 }
 
+// out[t] = sum over the k routed copies of token t of bf16(y[pos[t][j]] * w[t][j]), accumulated in the
+// output type in the order j = 0..k-1 (a bf16 index_add over the copies adds them in bf16 as well; with
+// k = 2 the order does not matter).  One thread = 8 channels of one token.
+__global__ void arcq_moe_combine_kernel(const uint16_t* __restrict__ y, const int* __restrict__ pos,
+                                        const uint16_t* __restrict__ w, uint16_t* __restrict__ out, long long tokens,
+                                        int hidden, int k) {
+  const int vec_per_row = hidden >> 3;
+  const long long total = tokens * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vec_per_row;
+    const int v = (int)(i - t * vec_per_row);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; ++j) {
+      const long long r = pos[t * k + j];
+      const float wj = __uint_as_float((uint32_t)w[t * k + j] << 16);
+      const uint4 a = *reinterpret_cast<const uint4*>(y + r * hidden + v * 8);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        // product rounded to bf16, then a bf16 addition: what `out.index_add_(0, idx, y * w)` computes
+        const uint32_t pr = pack2(__fmul_rn(lo_f(aw[q]), wj), __fmul_rn(hi_f(aw[q]), wj));
+        const uint32_t sm = pack2(__fadd_rn(acc[2 * q], lo_f(pr)), __fadd_rn(acc[2 * q + 1], hi_f(pr)));
+        acc[2 * q] = lo_f(sm);
+        acc[2 * q + 1] = hi_f(sm);
+      }
+    }
+    uint4 o;
+    o.x = pack2(acc[0], acc[1]); o.y = pack2(acc[2], acc[3]); o.z = pack2(acc[4], acc[5]); o.w = pack2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + t * (long long)hidden + v * 8) = o;
+  }
+}
+
 }  // namespace
+
+int launch_moe_combine(const void* y, const int* pos, const void* w, void* out, int64_t tokens, int hidden, int k,
+                       cudaStream_t stream) {
+  if (tokens == 0) return ARCQ_OK;
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  const long long total = (long long)tokens * (hidden / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)di.num_sms * 16;
+  if (blocks > cap) blocks = cap;
+  arcq_moe_combine_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(y), pos,
+                                                                static_cast<const uint16_t*>(w),
+                                                                static_cast<uint16_t*>(out), tokens, hidden, k);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
 
 int launch_rope(void* x, const float* cos_t, const float* sin_t, int64_t tokens, int row_elems, int heads, int dim,
                 int seq, cudaStream_t stream) {

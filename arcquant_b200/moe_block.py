@@ -16,6 +16,7 @@ with gloo; the expert arithmetic needs the CUDA library.
 """
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass
 
 import torch
@@ -101,6 +102,13 @@ class ExpertParallelDispatcher:
         else:
             ret = y_rows
         T, k, order = state["T"], state["k"], state["order"]
+        if ret.is_cuda and ret.dtype == torch.bfloat16:
+            # one gather per token instead of a scatter-add per copy: row of `ret` holding copy j of token t
+            pos = torch.empty_like(order)
+            pos[order] = torch.arange(order.numel(), device=order.device)
+            from . import ops
+            return ops.moe_combine(ret.contiguous(), pos.reshape(T, k).to(torch.int32).contiguous(),
+                                   weights.to(torch.bfloat16).contiguous())
         token_of = torch.div(order, k, rounding_mode="floor")
         w = weights.reshape(-1).index_select(0, order).unsqueeze(1)
         out = torch.zeros((T, ret.shape[1]), dtype=ret.dtype, device=ret.device)
@@ -141,21 +149,34 @@ class QMixtralMoEBlockEP(torch.nn.Module):
             dn = PackedLinear(ew["w2"].to(dev).contiguous(), ew["w2_index"], cfg.select_num)
             self.experts.append((gu, dn))
 
+    n_streams = 4   # experts are independent: a few streams hide the launch gaps of their small kernels
+
     @torch.no_grad()
     def expert_forward(self, rows: torch.Tensor, per_expert) -> torch.Tensor:
         out = torch.empty_like(rows)
         start = 0
-        ffn = self.cfg.ffn
-        for (gu, dn), n in zip(self.experts, per_expert):
+        use_streams = rows.is_cuda and self.n_streams > 1 and len(self.experts) > 1
+        if use_streams:
+            if not hasattr(self, "_streams"):
+                self._streams = [torch.cuda.Stream(rows.device) for _ in range(self.n_streams)]
+            cur = torch.cuda.current_stream(rows.device)
+            for s in self._streams:
+                s.wait_stream(cur)
+        for i, ((gu, dn), n) in enumerate(zip(self.experts, per_expert)):
             if n == 0:
                 continue
-            xb = rows[start:start + n].contiguous()
-            a, sfa, sx = NVFP4_reorder_quantize_x(xb, gu.index, gu.select_num, mode=16)
-            h = gu.gemm(a, sfa, sx)
-            act, amax = ops.silu_mul(h)
-            b, sfb, sa = NVFP4_reorder_quantize_x(act, dn.index, dn.select_num, mode=16, amax=amax)
-            out[start:start + n] = dn.gemm(b, sfb, sa)
+            ctx = torch.cuda.stream(self._streams[i % self.n_streams]) if use_streams else contextlib.nullcontext()
+            with ctx:
+                xb = rows[start:start + n]
+                a, sfa, sx = NVFP4_reorder_quantize_x(xb, gu.index, gu.select_num, mode=16)
+                h = gu.gemm(a, sfa, sx)
+                act, amax = ops.silu_mul(h)
+                b, sfb, sa = NVFP4_reorder_quantize_x(act, dn.index, dn.select_num, mode=16, amax=amax)
+                out[start:start + n] = dn.gemm(b, sfb, sa)
             start += n
+        if use_streams:
+            for s in self._streams:
+                cur.wait_stream(s)
         return out
 
     @torch.no_grad()

@@ -224,5 +224,21 @@ def silu_mul(gate_up: torch.Tensor, with_amax: bool = True):
     return out, amax
 
 
+def moe_combine(y: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """out [T, H] = sum_j bf16(y[pos[t, j]] * weights[t, j]) in bf16: the routed copies of every token,
+    weighted and added (pos int32 [T, k], weights bf16 [T, k])."""
+    lib = _lib.load()
+    _require(y, torch.bfloat16, "y")
+    _require(pos, torch.int32, "pos")
+    _require(weights, torch.bfloat16, "weights")
+    tokens, k = pos.shape
+    out = torch.empty((tokens, y.shape[1]), dtype=torch.bfloat16, device=y.device)
+    with torch.cuda.device(y.device):
+        rc = lib.arcq_moe_combine_bf16(y.data_ptr(), pos.data_ptr(), weights.data_ptr(), out.data_ptr(), tokens,
+                                       y.shape[1], k, _stream())
+    _lib.check(rc, "moe_combine")
+    return out
+
+
 def gemm_poll_error() -> int:
     return int(_lib.load().arcq_gemm_poll_error())

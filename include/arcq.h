@@ -188,6 +188,15 @@ int arcq_rope_bf16(void* x, const float* cos_table, const float* sin_table, int6
                    int head_dim, int seq, void* stream);
 int arcq_silu_mul_bf16(const void* gate_up, void* out, int64_t tokens, int F, float* amax, void* stream);
 
+/* Weighted sum of the routed copies of each token after the experts of a sparse MoE block (the
+ * `final_hidden_states.index_add_(0, top_x, expert_out * routing_weight)` of the reference's
+ * model/qMixtralLayer.py:466-471, as one gather instead of one scatter-add per expert; no counterpart
+ * in the reference's bindings).  y [rows, hidden] bf16: expert outputs; pos [tokens, top_k] int32: the
+ * row of y holding copy j of token t; weights [tokens, top_k] bf16; out [tokens, hidden] bf16 =
+ * sum_j bf16(y[pos[t][j]] * weights[t][j]), products and running sum rounded to bf16.  hidden % 8 == 0. */
+int arcq_moe_combine_bf16(const void* y, const int32_t* pos, const void* weights, void* out, int64_t tokens, int hidden,
+                          int top_k, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
