@@ -405,7 +405,8 @@ constexpr int C2_SFB_BYTES = 2 * KSTEPS * ATOM;     // 4 KB: both 128-row scale 
 constexpr int C2_STAGE_BYTES = C2_A_BYTES + C2_B_BYTES + C2_SFA_BYTES + C2_SFB_BYTES;   // 38 KB
 constexpr int C2_SF_COLS = KSTEPS * 4 + KSTEPS * 8;  // 48 TMEM columns of scales per stage
 constexpr int C2_TMEM_COLS = 512;                    // 256 accumulator + 5 x 48 scale columns
-constexpr int C2_SMEM_BYTES = 1024 + C2_STAGES * C2_STAGE_BYTES + 256;
+constexpr int C2_CSTAGE_BYTES = 4 * 8192;             // output staging: 32 rows x 128 columns of bf16 per epilogue warp
+constexpr int C2_SMEM_BYTES = 1024 + C2_STAGES * C2_STAGE_BYTES + C2_CSTAGE_BYTES + 256;
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;      // clears the pair-rank bit of a shared address
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -463,17 +464,29 @@ struct Gemm2Params {
   int natoms;         // scale atoms per 128-row tile
   int tiles_m, tiles_n;   // 256 x 256 tiles
   int dbg;                // timing experiments only (ARCQ_GEMM_DBG)
+  int tma_store;          // output leaves through shared memory and bulk tensor stores (else: per-thread stores)
 };
+
+#ifdef ARCQ_GEMM_TRACE
+// Timing experiments only (never compiled into the library): cycle stamps of the first pair's
+// leader CTA, one row per pipeline event, one column per K stage.
+__device__ long long g_trace[8][2048];
+#define ARCQ_TRACE(k, it) do { if (cluster_id == 0 && rank == 0 && (it) < 2048u) g_trace[k][it] = clock64(); } while (0)
+#else
+#define ARCQ_TRACE(k, it) do { } while (0)
+#endif
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C2_THREADS, 1)
 arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                  const Gemm2Params p) {
+                  const __grid_constant__ CUtensorMap map_c, const Gemm2Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t bar_base = base + C2_STAGES * C2_STAGE_BYTES;
-  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(base_ptr + C2_STAGES * C2_STAGE_BYTES + 192);
+  const uint32_t cstage_base = base + C2_STAGES * C2_STAGE_BYTES;   // 1024-byte aligned (swizzled boxes)
+  const uint32_t bar_base = cstage_base + C2_CSTAGE_BYTES;
+  volatile uint32_t* misc =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + C2_STAGES * C2_STAGE_BYTES + C2_CSTAGE_BYTES + 192);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 1);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };                       // A/B landed (leader's is used)
   auto empty_bar = [&](int s) { return bar_base + 8u * (C2_STAGES + s); };        // stage reusable
@@ -530,7 +543,9 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int ks = 0; ks < kstages; ++ks, ++it) {
           const int s = it % C2_STAGES;
           const uint32_t ph = (it / C2_STAGES) & 1u;
+          ARCQ_TRACE(6, it);
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+          ARCQ_TRACE(0, it);
           const uint32_t st = base + s * C2_STAGE_BYTES;
           const uint32_t lbar = full_bar(s) & PEER_BIT_MASK;
           if (rank == 0) mbar_expect_tx(full_bar(s), AB_TX);
@@ -560,7 +575,9 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const int s = it % C2_STAGES;
           const uint32_t ph = (it / C2_STAGES) & 1u;
           if (!mbar_wait(sf_ready_bar(s), ph, abort_flag)) { ok = false; break; }
+          ARCQ_TRACE(3, it);
           if (!mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+          ARCQ_TRACE(4, it);
           tc_fence_after();
           const int nk = min(KSTEPS, p.ksteps_total - ks * KSTEPS);
           const uint32_t st = base + s * C2_STAGE_BYTES;
@@ -574,6 +591,7 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             tc_mma_nvf4_pair(tmem_base, adesc, bdesc, idesc, t_sfa + k * 4, t_sfb + k * 8, (ks | k) ? 1u : 0u);
           }
           tc_commit_pair(empty_bar(s));
+          ARCQ_TRACE(5, it);
         }
         if (ok) tc_commit_pair(tmem_full_bar);
       }
@@ -612,8 +630,47 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(tmem_empty_bar);
-      if (row < p.M && !(p.dbg & 4)) {
-        const int col0 = tn * 256;
+      const int col0 = tn * 256;
+      if (p.tma_store) {
+        // Through shared memory: the warp's 32 rows x 256 columns leave as four boxes of 64 columns
+        // (32 rows x 128 bytes, 128-byte swizzle: lane = row, 16-byte chunk c of row r sits at chunk
+        // c ^ (r & 7), so a warp's 128-bit stores are conflict free), two boxes per round in the
+        // warp's 8 KB of staging.  The bulk stores write whole 128-byte lines, clip rows >= M and
+        // columns >= N themselves, and keep the load/store pipe free for the scale warps.
+        const int row0 = tm * 256 + (int)rank * 128 + quad * 32;
+        const uint32_t cst = cstage_base + (uint32_t)quad * 8192u;
+        if (row0 < p.M && !(p.dbg & 4)) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging is free again
+            __syncwarp();
+#pragma unroll
+            for (int bs = 0; bs < 2; ++bs) {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                const int j = 32 * (2 * h + bs) + 4 * c;
+                const uint32_t addr = cst + (uint32_t)bs * 4096u + (uint32_t)lane * 128u + (uint32_t)((c ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[j]), "r"(o[j + 1]),
+                             "r"(o[j + 2]), "r"(o[j + 3])
+                             : "memory");
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+#pragma unroll
+              for (int bs = 0; bs < 2; ++bs) {
+                const int col = col0 + 64 * (2 * h + bs);
+                if (col < p.N)
+                  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_c),
+                               "r"(cst + (uint32_t)bs * 4096u), "r"(col), "r"(row0)
+                               : "memory");
+              }
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+        }
+      } else if (row < p.M && !(p.dbg & 4)) {
 #pragma unroll
         for (int v = 0; v < 32; ++v) {          // 32 x 16 bytes = this row's 256 columns
           if (col0 + v * 8 < p.N)
@@ -621,6 +678,9 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
       }
     }
+    // the last boxes must have left shared memory (and reached global memory) before the CTA goes
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
   } else {
     // ------------------------------------------------------------------ scale warps (both CTAs)
     // Warp q writes TMEM lanes 32q..32q+31.  An atom is 32 rows x 16 bytes: lane l's 16 bytes are
@@ -636,6 +696,7 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         ok = mbar_wait(sf_full_bar(s), ph, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (quad == 0 && lane == 0) ARCQ_TRACE(1, it);
         const uint4* sf = reinterpret_cast<const uint4*>(base_ptr + s * C2_STAGE_BYTES + C2_A_BYTES + C2_B_BYTES);
         const uint32_t taddr = tmem_sf + s * C2_SF_COLS + ((uint32_t)(quad * 32) << 16);
         // TMEM columns: [SFA k0..k3 (4 each)] [SFB k0: tile0, tile1][k1: ...] ...
@@ -660,6 +721,7 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_leader(sf_ready_bar(s));
+        if (quad == 0 && lane == 0) ARCQ_TRACE(2, it);
       }
     }
   }
@@ -754,6 +816,23 @@ int make_sf_map(CUtensorMap* map, const void* ptr, int64_t total_atoms) {
   return ARCQ_OK;
 }
 
+// bf16 output [M, N] with a box of 64 columns x 32 rows, 128-byte swizzle (what one epilogue warp
+// hands over per bulk store).
+int make_c_map(CUtensorMap* map, const void* ptr, int64_t M, int64_t N) {
+  EncodeTiledFn fn;
+  int rc = get_encode_fn(&fn);
+  if (rc != ARCQ_OK) return rc;
+  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t strides[1] = {(cuuint64_t)N * 2};
+  cuuint32_t box[2] = {64, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  return ARCQ_OK;
+}
+
 int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M, int64_t N,
                 int64_t K_eff, const GemmParams& gp, int num_sms, cudaStream_t stream) {
   Gemm2Params p;
@@ -768,8 +847,12 @@ int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   p.tiles_m = (int)((M + 255) / 256);
   p.tiles_n = (int)((N + 255) / 256);
   p.dbg = gp.dbg;
-  CUtensorMap ma, mb, msa, msb;
-  int rc = make_operand_map(&ma, A, M, K_eff / 2, 128);
+  p.tma_store = 1;
+  if (const char* e = getenv("ARCQ_GEMM_TMA_STORE")) p.tma_store = atoi(e) != 0;   // timing experiments
+  CUtensorMap ma, mb, msa, msb, mc;
+  int rc = make_c_map(&mc, gp.c, M, N);
+  if (rc != ARCQ_OK) return rc;
+  rc = make_operand_map(&ma, A, M, K_eff / 2, 128);
   if (rc != ARCQ_OK) return rc;
   rc = make_operand_map(&mb, B, N, K_eff / 2, 128);
   if (rc != ARCQ_OK) return rc;
@@ -782,7 +865,7 @@ int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   long long clusters = num_sms / 2;
   if (clusters > tiles) clusters = tiles;
-  kern<<<(unsigned)(2 * clusters), C2_THREADS, C2_SMEM_BYTES, stream>>>(ma, mb, msa, msb, p);
+  kern<<<(unsigned)(2 * clusters), C2_THREADS, C2_SMEM_BYTES, stream>>>(ma, mb, msa, msb, mc, p);
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
 }
@@ -993,3 +1076,9 @@ int gemm_poll_error() {
 }
 
 }  // namespace arcq
+
+#ifdef ARCQ_GEMM_TRACE
+extern "C" int arcq_debug_trace_read(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, arcq::g_trace, sizeof(long long) * 8 * 2048);
+}
+#endif
