@@ -465,7 +465,21 @@ struct Gemm2Params {
   int tiles_m, tiles_n;   // 256 x 256 tiles
   int dbg;                // timing experiments only (ARCQ_GEMM_DBG)
   int tma_store;          // output leaves through shared memory and bulk tensor stores (else: per-thread stores)
+  int group_m;            // tile rows per band of the tile order (see pair_tile_coords)
 };
+
+// Tile order of the persistent pairs: bands of group_m tile rows, and inside a band column by column.
+// The ~74 tiles in flight at any time then cover about group_m x (74 / group_m) tiles, so every strip of
+// A and of B that is being streamed is shared by several pairs (one column of tiles would share one
+// strip of B and nothing of A), and a band's A rows plus all of B stay in L2 while the band lasts.
+__device__ __forceinline__ void pair_tile_coords(int tile, const Gemm2Params& p, int& tm, int& tn) {
+  const int per_band = p.group_m * p.tiles_n;
+  const int band = tile / per_band, in_band = tile - band * per_band;
+  const int first = band * p.group_m;
+  const int rows = min(p.group_m, p.tiles_m - first);
+  tn = in_band / rows;
+  tm = first + (in_band - tn * rows);
+}
 
 #ifdef ARCQ_GEMM_TRACE
 // Timing experiments only (never compiled into the library): cycle stamps of the first pair's
@@ -535,7 +549,8 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       uint32_t it = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        int tm, tn;
+        pair_tile_coords(tile, p, tm, tn);
         const int row_a = tm * 256 + (int)rank * 128;        // this CTA's rows of A (and of the output)
         const int row_b = tn * 256 + (int)rank * 128;        // this CTA's rows of B (half of the N tile)
         const int sfa_tile = tm * 2 + (int)rank;             // 128-row scale tiles
@@ -605,7 +620,8 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint32_t tile_it = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tile_it) {
-      const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      int tm, tn;
+      pair_tile_coords(tile, p, tm, tn);
       ok = mbar_wait(tmem_full_bar, tile_it & 1u, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -849,6 +865,12 @@ int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   p.dbg = gp.dbg;
   p.tma_store = 1;
   if (const char* e = getenv("ARCQ_GEMM_TMA_STORE")) p.tma_store = atoi(e) != 0;   // timing experiments
+  // Column by column unless A alone overflows half of L2: then bands of 32 tile rows, whose A rows
+  // (plus all of B) stay resident while the band lasts.  Measured on B200, the order makes no
+  // difference beyond run-to-run noise for operands that fit.
+  p.group_m = (double)M * (double)K_eff / 2.0 > 64e6 ? 32 : p.tiles_m;
+  if (const char* e = getenv("ARCQ_GEMM_GROUP_M")) p.group_m = atoi(e) > 0 ? atoi(e) : p.tiles_m;
+  if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
   CUtensorMap ma, mb, msa, msb, mc;
   int rc = make_c_map(&mc, gp.c, M, N);
   if (rc != ARCQ_OK) return rc;
