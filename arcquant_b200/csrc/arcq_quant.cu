@@ -715,6 +715,14 @@ __device__ __forceinline__ float div_shared(float x, float s, float r) {
 // npteams producer teams of npt = KQ/16 threads (more than one only with RMSNorm, whose producers carry
 // real arithmetic), sharing the pairs the same way; producer t of a team owns the 16-byte chunks t and
 // t + KQ/16 of each row, the reference's assignment and summation order for RMSNorm.
+#ifdef ARCQ_QUANT_TRACE
+// Timing experiments only (never compiled into the library): cycle stamps of CTA 0.
+__device__ long long g_qtrace[8][512];
+#define ARCQ_QT(k, i) do { if (blockIdx.x == 0 && (uint32_t)(i) < 512u) g_qtrace[k][i] = clock64(); } while (0)
+#else
+#define ARCQ_QT(k, i) do { } while (0)
+#endif
+
 template <bool RMS, bool WIDE, bool SCALED, int S, int R>
 __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantParams p, const int nct, const int npt, const int nteams,
                                                                         const int npteams) {
@@ -748,6 +756,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   const uint32_t rawe0 = raw0 + 8 * R, psr0 = rawe0 + 8 * R, rsr0 = psr0 + 8 * 4;
 
   asm volatile("griddepcontrol.launch_dependents;");   // the next kernel of the stream may be set up now
+  if (tid == 0) ARCQ_QT(0, 0);
   const uint32_t stride = gridDim.x;
   // Bulk copies of the rows of `unit` into raw stage `rs` (one thread).
   auto issue = [&](uint32_t unit, uint32_t rs) {
@@ -781,19 +790,35 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     // still be written by the previous kernel of the stream until this wait returns).
     asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t r = 0; r < (uint32_t)R; ++r) issue(blockIdx.x + r * stride, r);
+    ARCQ_QT(0, 1);
   }
   // Everything before this line touched shared memory only; global memory may still be written by
   // the previous kernel of the stream (no-op unless launched as a programmatic dependent).
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // Offsets are laid out [vector v][group g][entries of one 128-bit load]: consecutive lanes (groups)
   // read consecutive 16 bytes, so every table load is conflict free.
-  for (int j = tid; j < KQ; j += blockDim.x) {
-    const int c = p.idx ? (int)p.idx[j] : j;
+  auto put = [&](int j, int c) {
     const int g = j >> 4, i = j & 15;
     if (WIDE) offs16[(((i >> 3) * G + g) << 3) | (i & 7)] = (uint16_t)word_offset((uint32_t)c);
     else offs32[(((i >> 2) * G + g) << 2) | (i & 3)] = word_offset((uint32_t)c);
+  };
+  if (p.idx && (reinterpret_cast<uintptr_t>(p.idx) & 15u) == 0) {
+    // eight indices per 128-bit load: one round trip to global memory for rows of up to 8192 channels
+    const uint4* idx4 = reinterpret_cast<const uint4*>(p.idx);
+    for (int v = tid; v < (KQ >> 3); v += blockDim.x) {
+      const uint4 w = __ldg(idx4 + v);
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        put(8 * v + 2 * k, (int)(int16_t)(ww[k] & 0xffffu));
+        put(8 * v + 2 * k + 1, (int)(int16_t)(ww[k] >> 16));
+      }
+    }
+  } else {
+    for (int j = tid; j < KQ; j += blockDim.x) put(j, p.idx ? (int)p.idx[j] : j);
   }
   __syncthreads();
+  if (tid == 0) ARCQ_QT(0, 2);
 
   const int ncons = nteams * nct;
   if (tid >= ncons) {
@@ -987,14 +1012,18 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
         if (m >= 1) {
           const uint32_t j = it - NP, q = m - 1;
           if (!mbar_wait(rsr + 8 * (q & 1u), (q >> 1) & 1u, abort_flag)) break;
+          if (pteam == 0 && ptid == 0) ARCQ_QT(1, q);
           const float2 rstd = make_float2(rstd_s[(q & 1u) * 2], rstd_s[(q & 1u) * 2 + 1]);
           if (!mbar_wait(empty0 + 8 * (j % S), ((j / S) & 1u) ^ 1u, abort_flag)) break;
+          if (pteam == 0 && ptid == 0) ARCQ_QT(2, q);
           fill_stage(j, a0, a1, b0, b1, rstd);
+          if (pteam == 0 && ptid == 0) ARCQ_QT(3, q);
         }
         if (m < nt) {
           const uint32_t unit = blockIdx.x + it * stride;
           const bool has1 = (2 * unit + 1) < rows;
           if (!mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) break;
+          if (pteam == 0 && ptid == 0) ARCQ_QT(4, m);
           read_raw(it, has1, a0, a1, b0, b1);
           // reference thread t adds chunk t, then chunk t + KQ/16, eight elements each, in order
           float ss0 = 0.f, ss1 = 0.f;   // x*x is exact in fp32, so each step rounds once, like the fp32 FMA
@@ -1015,6 +1044,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
             mbar_arrive(rawe0 + 8 * (it % R));
             mbar_arrive(psr + 8 * (m & 1u));
           }
+          if (pteam == 0 && ptid == 0) ARCQ_QT(5, m);
         }
       }
     }
@@ -1053,6 +1083,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       uint8_t* sf1 = has1 ? sf0 + 16 : sf0;
       const uint8_t* buf = stages + (size_t)s * stage_bytes;
       if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) break;
+      if (tid == 0) ARCQ_QT(6, it / (uint32_t)nteams);
       for (int g = slot * 32 + lane; g < G; g += nct) {
         uint32_t w[16];
         if (WIDE) {
@@ -1085,8 +1116,10 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
         quantize_group_pair_ws(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1);
       }
       slot = slot + 1 == ncw ? 0 : slot + 1;
+      if (tid == 0) ARCQ_QT(7, it / (uint32_t)nteams);
     }
   }
+  if (tid == 0) ARCQ_QT(0, 3);
 }
 
 __global__ void arcq_absmax_kernel(const uint4* __restrict__ x, long long nvec, const uint16_t* tail,
@@ -1343,3 +1376,9 @@ int launch_absmax(const void* x, int64_t n, float* out, int accumulate, cudaStre
 }
 
 }  // namespace arcq
+
+#ifdef ARCQ_QUANT_TRACE
+extern "C" int arcq_debug_qtrace_read(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, arcq::g_qtrace, sizeof(long long) * 8 * 512);
+}
+#endif
