@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "arcq_internal.h"
 
@@ -97,6 +98,67 @@ __global__ void arcq_silu_mul_kernel(const uint16_t* __restrict__ gu, uint16_t* 
   }
 }
 
+// Large calls: bf16 SiLU is a function of 65 536 bit patterns, and its exact evaluation (expf, IEEE
+// division: ~25 instructions per element) makes the pass above instruction bound at ~0.75 of the HBM
+// rate.  g_silu_table holds bf16(silu(g)) for every g, written by arcq_silu_table_kernel with the very
+// function above (so the results cannot differ); each CTA of the main kernel copies the 128 KB into
+// shared memory and looks SiLU up.  The table is rewritten by every call on the call's own stream:
+// calls on other streams can only ever see the same values.
+__device__ uint16_t g_silu_table[65536];
+
+__global__ void arcq_silu_table_kernel() {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  g_silu_table[i] = (uint16_t)(__float_as_uint(silu_bf16(__uint_as_float(i << 16))) >> 16);
+}
+
+__global__ void __launch_bounds__(1024, 1) arcq_silu_mul_table_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ out,
+                                                                      long long tokens, int F, unsigned int* amax) {
+  extern __shared__ __align__(16) uint16_t tab[];
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(g_silu_table);
+    uint4* dst = reinterpret_cast<uint4*>(tab);
+    for (int i = threadIdx.x; i < 65536 / 8; i += blockDim.x) dst[i] = src[i];
+  }
+  __syncthreads();
+  const int vec_per_row = F >> 3;
+  const long long total = tokens * vec_per_row;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  uint32_t m = 0;
+  // two vectors per thread and iteration: four 16-byte loads in flight before any is used
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += 2 * step) {
+    const long long i1 = i + step;
+    const bool two = i1 < total;
+    const long long t0 = i / vec_per_row, t1 = two ? i1 / vec_per_row : t0;
+    const int v0 = (int)(i - t0 * vec_per_row), v1 = two ? (int)(i1 - t1 * vec_per_row) : v0;
+    const uint16_t* r0 = gu + t0 * 2LL * F + v0 * 8;
+    const uint16_t* r1 = gu + t1 * 2LL * F + v1 * 8;
+    const uint4 g0 = *reinterpret_cast<const uint4*>(r0), u0 = *reinterpret_cast<const uint4*>(r0 + F);
+    const uint4 g1 = *reinterpret_cast<const uint4*>(r1), u1 = *reinterpret_cast<const uint4*>(r1 + F);
+    auto one = [&](const uint4& g, const uint4& u, long long t, int v) {
+      const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float sa = __uint_as_float((uint32_t)tab[gw[k] & 0xffffu] << 16);
+        const float sb = __uint_as_float((uint32_t)tab[gw[k] >> 16] << 16);
+        o[k] = pack2(__fmul_rn(sa, lo_f(uw[k])), __fmul_rn(sb, hi_f(uw[k])));
+        uint32_t ab;
+        asm("max.u16x2 %0, %1, %2;" : "=r"(ab) : "r"(m), "r"(o[k] & 0x7fff7fffu));
+        m = ab;
+      }
+      *reinterpret_cast<uint4*>(out + t * (long long)F + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    };
+    one(g0, u0, t0, v0);
+    if (two) one(g1, u1, t1, v1);
+  }
+  if (amax) {
+    uint32_t r = max(m & 0xffffu, m >> 16);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) r = max(r, __shfl_xor_sync(0xffffffffu, r, d));
+    if ((threadIdx.x & 31) == 0) atomicMax(amax, r << 16);   // non-negative floats order like their bit patterns
+  }
+}
+
 // out[t] = sum over the k routed copies of token t of bf16(y[pos[t][j]] * w[t][j]), accumulated in the
 // output type in the order j = 0..k-1 (a bf16 index_add over the copies adds them in bf16 as well; with
 // k = 2 the order does not matter).  One thread = 8 channels of one token.
@@ -171,6 +233,21 @@ int launch_silu_mul(const void* gu, void* out, int64_t tokens, int F, float* ama
   int rc = get_device_info(&di);
   if (rc != ARCQ_OK) return rc;
   const long long total = (long long)tokens * (F / 8);
+  static const int table_env = [] { const char* e = getenv("ARCQ_SILU_TABLE"); return e ? atoi(e) : 1; }();
+  if (table_env && total >= (1LL << 22) && di.max_smem_optin >= 131072) {   // 32 M elements and more: table lookups
+    arcq_silu_table_kernel<<<65536 / 256, 256, 0, stream>>>();
+    ARCQ_CUDA_TRY(cudaGetLastError());
+    auto kern = arcq_silu_mul_table_kernel;
+    static thread_local int attr_dev = -1;
+    if (attr_dev != di.device) {
+      ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
+      attr_dev = di.device;
+    }
+    kern<<<(unsigned)di.num_sms, 1024, 131072, stream>>>(static_cast<const uint16_t*>(gu), static_cast<uint16_t*>(out),
+                                                        tokens, F, reinterpret_cast<unsigned int*>(amax));
+    ARCQ_CUDA_TRY(cudaGetLastError());
+    return ARCQ_OK;
+  }
   long long blocks = (total + 255) / 256;
   const long long cap = (long long)di.num_sms * 16;
   if (blocks > cap) blocks = cap;

@@ -693,17 +693,18 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "memory");
 }
 
-// x / s rounded to nearest, for a divisor shared by the whole tensor: r = fp32(1/s) correctly rounded,
-// q = x*r, one FMA for the exact residual x - s*q and one to correct q (Markstein's sequence: exact
-// when nothing under- or overflows).  Results outside a comfortable range - zeros among them, whose
-// sign the sequence loses - take the IEEE routine.
+// bf16(x / s) for bf16 x and a bf16 divisor s shared by the whole tensor, as one multiplication by
+// r = fp32(1/s): the caller rounds the product to bf16, and that rounding cannot differ from the
+// rounding of the exact quotient.  With 8-bit significands mx, ms the quotient mx/ms is never within
+// 2^-18 (relative) of the midpoint of two bf16 values unless it is a bf16 value itself (a dyadic
+// mx/ms has at most 8 significant bits), while x*r is within 2^-23 of it; the same holds for the
+// fp32 quotient an IEEE division would round first.  Products outside a comfortable range take the
+// IEEE routine (a zero product is exact and keeps its sign, but stays on that path with them).
 __device__ __forceinline__ float div_shared(float x, float s, float r) {
-  const float q = __fmul_rn(x, r);
-  const float e = __fmaf_rn(-s, q, x);
-  float q2 = __fmaf_rn(e, r, q);
-  const float mag = fabsf(q2);
-  if (!(mag >= 8.6736174e-19f && mag <= 1.1529215e18f)) q2 = __fdiv_rn(x, s);   // outside [2^-60, 2^60]
-  return q2;
+  float q = __fmul_rn(x, r);
+  const float mag = fabsf(q);
+  if (!(mag >= 8.6736174e-19f && mag <= 1.1529215e18f)) q = __fdiv_rn(x, s);   // outside [2^-60, 2^60]
+  return q;
 }
 
 // S: stages of the gather ring (interleaved row pairs).  R: stages of the raw ring (row pairs as they

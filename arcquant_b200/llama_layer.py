@@ -65,11 +65,27 @@ def random_reorder_indices(cfg: LlamaLayerConfig, seed: int = 1):
     }
 
 
+_ROPE_CACHE: dict = {}
+
+
 def rope_tables(positions: torch.Tensor, head_dim: int, theta: float):
+    """cos / sin tables [len(positions), head_dim] in fp32.  The tables of the last few position
+    tensors are kept (keyed by storage, length and version counter: a tensor that was written to in
+    place is a new key), so a prefill loop that passes the same positions to every layer and step
+    builds them once instead of with a dozen small kernels per layer."""
+    key = (positions.data_ptr(), positions.numel(), positions._version, str(positions.device), positions.dtype,
+           head_dim, float(theta))
+    hit = _ROPE_CACHE.get(key)
+    if hit is not None and hit[0] is positions:
+        return hit[1], hit[2]
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=positions.device, dtype=torch.float32) / head_dim))
     ang = positions.to(torch.float32)[:, None] * inv[None, :]
     emb = torch.cat([ang, ang], dim=-1)
-    return emb.cos(), emb.sin()
+    cos, sin = emb.cos(), emb.sin()
+    if len(_ROPE_CACHE) >= 8:
+        _ROPE_CACHE.pop(next(iter(_ROPE_CACHE)))
+    _ROPE_CACHE[key] = (positions, cos, sin)   # holding the tensor keeps its storage address unique
+    return cos, sin
 
 
 def apply_rope(t: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:

@@ -228,6 +228,28 @@ def test_silu_mul_equals_eager_torch_and_returns_the_maximum():
     assert float(amax) == float(ref.abs().max())
 
 
+def test_silu_mul_large_calls_look_silu_up_in_a_table():
+    """From 32 M elements on, SiLU comes out of a 65 536-entry table (built on the device by the exact
+    routine): every finite bf16 gate value against eager torch, bit for bit."""
+    from arcquant_b200 import ops
+
+    g = torch.Generator().manual_seed(7)
+    tokens, f = 4200, 8192
+    bits = torch.arange(65536, dtype=torch.int32)
+    bits = bits[(bits & 0x7f80) != 0x7f80]
+    gate = bits[torch.randint(0, bits.numel(), (tokens * f,), generator=g)]
+    gate[:bits.numel()] = bits
+    gate = gate.to(torch.int16).view(torch.bfloat16).reshape(tokens, f)
+    up = (torch.randn(tokens, f, generator=g) * 3).to(torch.bfloat16)
+    gu = torch.cat([gate, up], dim=1).contiguous().cuda()
+    ref = torch.nn.functional.silu(gu[:, :f]) * gu[:, f:]
+    out, amax = ops.silu_mul(gu)
+    fin = torch.isfinite(ref)
+    assert torch.equal(out.view(torch.int16)[fin], ref.view(torch.int16)[fin])
+    assert bool((torch.isfinite(out) == fin).all())
+    assert float(amax) == float(ref[fin].abs().max()) or not bool(fin.all())
+
+
 def test_packed_layer_checkpoint_round_trip(tmp_path):
     """A layer rebuilt from its saved packed buffers (no bf16 weights) gives the same bytes."""
     from arcquant_b200 import checkpoint
