@@ -771,6 +771,21 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     bulk_load(dst, src, row_in_bytes, bar);
     if (has1) bulk_load(dst + row_in_bytes, src + KQ, row_in_bytes, bar);
   };
+  // WIDE: the raw ring holds half pairs (the same half of the channels of both rows), so that the
+  // copies of the next half overlap the work on this one although only ~1.5 pairs of raw rows fit.
+  // Half u of this CTA is half u & 1 of its pair u >> 1.
+  auto issue_half = [&](uint32_t u, uint32_t rs) {
+    const uint32_t unit = blockIdx.x + (u >> 1) * stride;
+    if (unit >= npairs) return;
+    const uint32_t r0 = 2 * unit, hbytes = row_in_bytes >> 1;
+    const bool has1 = (r0 + 1) < rows;
+    const uint32_t bar = raw0 + 8 * rs;
+    const uint32_t dst = smem_addr(raw + (size_t)rs * row_in_bytes);
+    const uint16_t* src = p.x + (size_t)r0 * (size_t)KQ + (size_t)(u & 1u) * (size_t)(KQ >> 1);
+    mbar_expect_tx(bar, has1 ? 2 * hbytes : hbytes);
+    bulk_load(dst, src, hbytes, bar);
+    if (has1) bulk_load(dst + hbytes, src + KQ, hbytes, bar);
+  };
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, (uint32_t)(npt >> 5));    // one arrival per producer warp
@@ -790,7 +805,10 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     // The first R row pairs start streaming in while the CTA builds its tables (global memory may
     // still be written by the previous kernel of the stream until this wait returns).
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (uint32_t r = 0; r < (uint32_t)R; ++r) issue(blockIdx.x + r * stride, r);
+    for (uint32_t r = 0; r < (uint32_t)R; ++r) {
+      if (WIDE) issue_half(r, r);
+      else issue(blockIdx.x + r * stride, r);
+    }
     ARCQ_QT(0, 1);
   }
   // Everything before this line touched shared memory only; global memory may still be written by
@@ -949,7 +967,57 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     while (issued < n && issued < (uint32_t)R) issued += NP;
     uint32_t landed = (uint32_t)pteam;   // first pair of this team whose copies were not waited for yet
     bool failed = false;
-    if (!RMS) {
+    if (!RMS && WIDE) {
+      const int hc = KQ >> 4;   // 16-byte chunks of half a row
+      float sc = 1.0f, rsc = 1.0f;
+      if (SCALED) {
+        sc = __uint_as_float(pack_bf16x2_rn(__ldg(p.scale), 0.f) << 16);   // (the divisor as bf16, see below)
+        rsc = __frcp_rn(sc);
+      }
+      const uint32_t nu = 2 * n;
+      issued = nu < (uint32_t)R ? nu : (uint32_t)R;
+      landed = 0;
+      for (uint32_t u = 0; u < nu; ++u) {
+        const uint32_t it = u >> 1, h = u & 1u;
+        const uint32_t unit = blockIdx.x + it * stride;
+        const bool has1 = (2 * unit + 1) < rows;
+        if (!failed && !mbar_wait(raw0 + 8 * (u % R), (u / R) & 1u, abort_flag)) failed = true;
+        if (!failed) landed = u + 1;
+        if (h == 0 && !failed && !mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag)) failed = true;
+        if (!failed) {
+          const uint4* rw = reinterpret_cast<const uint4*>(raw + (size_t)(u % R) * row_in_bytes);
+          uint4* b4 = reinterpret_cast<uint4*>(stages + (size_t)(it % S) * stage_bytes);
+          const uint32_t cbase = h * (uint32_t)hc;
+          for (int c = ptid; c < hc; c += npt) {
+            const uint4 a = rw[c], b = has1 ? rw[hc + c] : zero;
+            uint4 lo, hi;
+            if (SCALED) {
+              auto dv = [&](uint32_t wa, uint32_t wb, uint32_t& o0, uint32_t& o1) {
+                o0 = pack_bf16x2_rn(div_shared(bf16lo(wa), sc, rsc), div_shared(bf16lo(wb), sc, rsc));
+                o1 = pack_bf16x2_rn(div_shared(bf16hi(wa), sc, rsc), div_shared(bf16hi(wb), sc, rsc));
+              };
+              dv(a.x, b.x, lo.x, lo.y); dv(a.y, b.y, lo.z, lo.w);
+              dv(a.z, b.z, hi.x, hi.y); dv(a.w, b.w, hi.z, hi.w);
+            } else {
+              lo.x = __byte_perm(a.x, b.x, 0x5410); lo.y = __byte_perm(a.x, b.x, 0x7632);
+              lo.z = __byte_perm(a.y, b.y, 0x5410); lo.w = __byte_perm(a.y, b.y, 0x7632);
+              hi.x = __byte_perm(a.z, b.z, 0x5410); hi.y = __byte_perm(a.z, b.z, 0x7632);
+              hi.z = __byte_perm(a.w, b.w, 0x5410); hi.w = __byte_perm(a.w, b.w, 0x7632);
+            }
+            const uint32_t cc = cbase + (uint32_t)c;
+            b4[swz16(2u * cc)] = lo;
+            b4[swz16(2u * cc + 1u)] = hi;
+          }
+          if (h == 1u) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full0 + 8 * (it % S));
+          }
+        }
+        // every producer is done with this half stage: refill it, or leave together
+        if (named_barrier_or(bar_id, team_threads, failed)) break;
+        if (ptid == 0 && u + R < nu) { issue_half(u + R, u % R); issued = u + R + 1; }
+      }
+    } else if (!RMS) {
       const int nchunks = KQ >> 3;
       float sc = 1.0f, rsc = 1.0f;
       if (SCALED) {
@@ -1256,17 +1324,22 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
       // stage (two if they fit)
       // (twice the producers when they also divide by the tensor's scale)
       const int nct = 256, npt = p.scale ? 512 : 256, nteams = 2;
+      // (raw stages here are half pairs, half a gather stage each: two to four of them)
       const size_t fixed = 384 + (size_t)KQ * 2;
-      int R = fixed + 4 * stage <= (size_t)di.max_smem_optin ? 2 : 1;
-      if (raw_env == 1 || raw_env == 2) R = raw_env;
-      const size_t smem = fixed + (2 + R) * stage;
-      if (smem <= (size_t)di.max_smem_optin) {
+      int R = 0;
+      if (fixed + 2 * stage <= (size_t)di.max_smem_optin) R = (int)(((size_t)di.max_smem_optin - fixed - 2 * stage) / (stage / 2));
+      if (R > 4) R = 4;
+      if (raw_env >= 2 && raw_env <= 4 && raw_env <= R) R = raw_env;
+      const size_t smem = fixed + 2 * stage + (size_t)R * (stage / 2);
+      if (R >= 2) {
         if (p.scale) {
-          if (R == 2) return launch_ws<false, true, true, 2, 2>(p, nct, npt, nteams, 1, smem, di, stream);
-          return launch_ws<false, true, true, 2, 1>(p, nct, npt, nteams, 1, smem, di, stream);
+          if (R == 4) return launch_ws<false, true, true, 2, 4>(p, nct, npt, nteams, 1, smem, di, stream);
+          if (R == 3) return launch_ws<false, true, true, 2, 3>(p, nct, npt, nteams, 1, smem, di, stream);
+          return launch_ws<false, true, true, 2, 2>(p, nct, npt, nteams, 1, smem, di, stream);
         }
-        if (R == 2) return launch_ws<false, true, false, 2, 2>(p, nct, npt, nteams, 1, smem, di, stream);
-        return launch_ws<false, true, false, 2, 1>(p, nct, npt, nteams, 1, smem, di, stream);
+        if (R == 4) return launch_ws<false, true, false, 2, 4>(p, nct, npt, nteams, 1, smem, di, stream);
+        if (R == 3) return launch_ws<false, true, false, 2, 3>(p, nct, npt, nteams, 1, smem, di, stream);
+        return launch_ws<false, true, false, 2, 2>(p, nct, npt, nteams, 1, smem, di, stream);
       }
     } else {
       // Consumer teams of 128 threads (two groups per thread at hidden 4096) were measured faster than
