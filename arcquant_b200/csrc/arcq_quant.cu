@@ -699,12 +699,19 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 // 2^-18 (relative) of the midpoint of two bf16 values unless it is a bf16 value itself (a dyadic
 // mx/ms has at most 8 significant bits), while x*r is within 2^-23 of it; the same holds for the
 // fp32 quotient an IEEE division would round first.  Products outside a comfortable range take the
-// IEEE routine (a zero product is exact and keeps its sign, but stays on that path with them).
-__device__ __forceinline__ float div_shared(float x, float s, float r) {
+// IEEE routine: products below 2^-60 in magnitude (a zero product is exact and keeps its sign, but
+// stays on that path with them) and NaNs.  There is no upper guard: a large product is as accurate as
+// any other, and where it overflows the quotient is beyond the largest bf16 number as well.  `qlo` is
+// 2^-60, or NaN (every comparison fails: IEEE routine throughout) when the divisor is so large or
+// small that 1/s is not a well-scaled normal number.
+__device__ __forceinline__ float div_shared(float x, float s, float r, float qlo) {
   float q = __fmul_rn(x, r);
-  const float mag = fabsf(q);
-  if (!(mag >= 8.6736174e-19f && mag <= 1.1529215e18f)) q = __fdiv_rn(x, s);   // outside [2^-60, 2^60]
+  if (!(fabsf(q) >= qlo)) q = __fdiv_rn(x, s);
   return q;
+}
+__device__ __forceinline__ float div_guard(float s) {
+  const float m = fabsf(s);
+  return (m >= 7.8886091e-31f && m <= 1.2676506e30f) ? 8.6736174e-19f : __int_as_float(0x7fc00000);   // 2^-100 .. 2^100
 }
 
 // S: stages of the gather ring (interleaved row pairs).  R: stages of the raw ring (row pairs as they
@@ -969,10 +976,11 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     bool failed = false;
     if (!RMS && WIDE) {
       const int hc = KQ >> 4;   // 16-byte chunks of half a row
-      float sc = 1.0f, rsc = 1.0f;
+      float sc = 1.0f, rsc = 1.0f, qlo = 0.f;
       if (SCALED) {
         sc = __uint_as_float(pack_bf16x2_rn(__ldg(p.scale), 0.f) << 16);   // (the divisor as bf16, see below)
         rsc = __frcp_rn(sc);
+        qlo = div_guard(sc);
       }
       const uint32_t nu = 2 * n;
       issued = nu < (uint32_t)R ? nu : (uint32_t)R;
@@ -993,8 +1001,8 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
             uint4 lo, hi;
             if (SCALED) {
               auto dv = [&](uint32_t wa, uint32_t wb, uint32_t& o0, uint32_t& o1) {
-                o0 = pack_bf16x2_rn(div_shared(bf16lo(wa), sc, rsc), div_shared(bf16lo(wb), sc, rsc));
-                o1 = pack_bf16x2_rn(div_shared(bf16hi(wa), sc, rsc), div_shared(bf16hi(wb), sc, rsc));
+                o0 = pack_bf16x2_rn(div_shared(bf16lo(wa), sc, rsc, qlo), div_shared(bf16lo(wb), sc, rsc, qlo));
+                o1 = pack_bf16x2_rn(div_shared(bf16hi(wa), sc, rsc, qlo), div_shared(bf16hi(wb), sc, rsc, qlo));
               };
               dv(a.x, b.x, lo.x, lo.y); dv(a.y, b.y, lo.z, lo.w);
               dv(a.z, b.z, hi.x, hi.y); dv(a.w, b.w, hi.z, hi.w);
@@ -1019,11 +1027,12 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       }
     } else if (!RMS) {
       const int nchunks = KQ >> 3;
-      float sc = 1.0f, rsc = 1.0f;
+      float sc = 1.0f, rsc = 1.0f, qlo = 0.f;
       if (SCALED) {
         // torch's CUDA kernel for (bf16 tensor) / (fp32 scalar tensor) loads the divisor as bf16
         sc = __uint_as_float(pack_bf16x2_rn(__ldg(p.scale), 0.f) << 16);
         rsc = __frcp_rn(sc);
+        qlo = div_guard(sc);
       }
       for (uint32_t it = 0; it < n; ++it) {
         const uint32_t unit = blockIdx.x + it * stride;
@@ -1041,8 +1050,8 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
             uint4 lo, hi;  // words of channels 8c..8c+3 and 8c+4..8c+7: (row0[ch], row1[ch]) per word
             if (SCALED) {
               auto dv = [&](uint32_t wa, uint32_t wb, uint32_t& o0, uint32_t& o1) {
-                o0 = pack_bf16x2_rn(div_shared(bf16lo(wa), sc, rsc), div_shared(bf16lo(wb), sc, rsc));
-                o1 = pack_bf16x2_rn(div_shared(bf16hi(wa), sc, rsc), div_shared(bf16hi(wb), sc, rsc));
+                o0 = pack_bf16x2_rn(div_shared(bf16lo(wa), sc, rsc, qlo), div_shared(bf16lo(wb), sc, rsc, qlo));
+                o1 = pack_bf16x2_rn(div_shared(bf16hi(wa), sc, rsc, qlo), div_shared(bf16hi(wb), sc, rsc, qlo));
               };
               dv(a.x, b.x, lo.x, lo.y); dv(a.y, b.y, lo.z, lo.w);
               dv(a.z, b.z, hi.x, hi.y); dv(a.w, b.w, hi.z, hi.w);

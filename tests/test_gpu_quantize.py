@@ -117,7 +117,8 @@ def test_fused_division_by_the_tensor_scale(kq, ke):
     vals[:bits.numel()] = bits
     x = vals.to(torch.int16).view(torch.bfloat16).reshape(-1, kq).contiguous().cuda()
     idx = torch.randperm(kq, generator=g).to(torch.int16).cuda()
-    scales = [1.0, 3.0, 0.3721, 1.9999999, 7.0e-4, 2.688e3, 1.0000001, 5.960464e-8, 1.5e9, 0.99999994]
+    scales = [1.0, 3.0, 0.3721, 1.9999999, 7.0e-4, 2.688e3, 1.0000001, 5.960464e-8, 1.5e9, 0.99999994, 1e-25, 1e25,
+              1e-35, 3e35]
     scales += [float(v) for v in torch.rand(12, generator=g) * 4 + 1e-3]
     for sv in scales:
         sc = torch.tensor(sv, dtype=torch.float32, device="cuda")
