@@ -31,16 +31,44 @@ void require_cuda(const torch::Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor (this library has no CPU path)");
   TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
 }
+// Every tensor a kernel will dereference: on the device of `like`, contiguous, of the given type.
+void require_on(const torch::Tensor& t, const torch::Tensor& like, at::ScalarType type, const char* name) {
+  require_cuda(t, name);
+  TORCH_CHECK(t.device() == like.device(), name, " must be on the same device as the first operand");
+  TORCH_CHECK(t.scalar_type() == type, name, ": expected ", type, ", got ", t.scalar_type());
+}
+void require_scalar_f32(const torch::Tensor& t, const torch::Tensor& like, const char* name) {
+  require_on(t, like, at::kFloat, name);
+  TORCH_CHECK(t.numel() == 1, name, " must hold one fp32 value");
+}
+// Shapes of a block-scaled GEMM's operands; returns M, N, K_eff.
+std::tuple<int64_t, int64_t, int64_t> check_gemm_operands(const torch::Tensor& A, const torch::Tensor& B,
+                                                          const torch::Tensor& SFA, const torch::Tensor& SFB) {
+  require_cuda(A, "A");
+  TORCH_CHECK(A.scalar_type() == at::kByte, "A: expected uint8 packed codes");
+  require_on(B, A, at::kByte, "B");
+  require_on(SFA, A, at::kByte, "SFA");
+  require_on(SFB, A, at::kByte, "SFB");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2, "A and B must be 2-D [rows, K_eff/2]");
+  TORCH_CHECK(A.size(1) == B.size(1), "A and B disagree on K");
+  const int64_t M = A.size(0), N = B.size(0), K = A.size(1) * 2;
+  // what the kernels read: whole 512-byte atoms of every 128-row tile
+  const int64_t atoms = (K / 16 + 3) / 4;
+  TORCH_CHECK(SFA.numel() >= ((M + 127) / 128) * atoms * 512, "SFA is smaller than the scale layout of A");
+  TORCH_CHECK(SFB.numel() >= ((N + 127) / 128) * atoms * 512, "SFB is smaller than the scale layout of B");
+  return std::make_tuple(M, N, K);
+}
 
 std::tuple<torch::Tensor, torch::Tensor> quantize_common(const torch::Tensor& X, const torch::Tensor* gamma,
                                                          float eps, const torch::Tensor& reorder_index, int KE,
                                                          bool is_weight, const char* where) {
   require_cuda(X, "input");
-  require_cuda(reorder_index, "reorder_index");
+  require_on(reorder_index, X, at::kShort, "reorder_index");
   TORCH_CHECK(X.dim() == 2, "input must be 2-D");
   const int64_t rows = X.size(0);
   const int KQ = static_cast<int>(X.size(1));
   const int K = KQ + KE;
+  TORCH_CHECK(KE >= 0 && KE <= KQ, "KE must lie in [0, KQ]");
   TORCH_CHECK(reorder_index.numel() == KQ, "reorder_index must have KQ entries");
   c10::cuda::CUDAGuard guard(X.device());
   auto options = torch::dtype(torch::kUInt8).device(X.device());
@@ -50,7 +78,8 @@ std::tuple<torch::Tensor, torch::Tensor> quantize_common(const torch::Tensor& X,
   const int16_t* pidx = reorder_index.data_ptr<int16_t>();
   int status;
   if (gamma) {
-    require_cuda(*gamma, "weight");
+    require_on(*gamma, X, at::kBFloat16, "weight");
+    TORCH_CHECK(gamma->numel() == KQ, "weight must have KQ entries");
     status = arcq_rmsnorm_quantize_x(px, gamma->data_ptr<at::BFloat16>(), eps, pidx, rows, KQ, KE,
                                      Q.data_ptr<uint8_t>(), SF.data_ptr<uint8_t>(), current_stream(X));
   } else if (is_weight) {
@@ -66,11 +95,8 @@ std::tuple<torch::Tensor, torch::Tensor> quantize_common(const torch::Tensor& X,
 
 torch::Tensor matmul(const torch::Tensor& A, const torch::Tensor& B, const torch::Tensor& SFA,
                      const torch::Tensor& SFB, const float scale) {
-  require_cuda(A, "A");
-  require_cuda(B, "B");
-  require_cuda(SFA, "SFA");
-  require_cuda(SFB, "SFB");
-  const int64_t M = A.size(0), N = B.size(0), K = A.size(1) * 2;
+  int64_t M, N, K;
+  std::tie(M, N, K) = check_gemm_operands(A, B, SFA, SFB);
   c10::cuda::CUDAGuard guard(A.device());
   auto C = torch::empty({M, N}, torch::dtype(torch::kBFloat16).device(A.device()));
   // skinny problems split K over idle SMs; the fp32 partial sums need scratch
@@ -89,9 +115,10 @@ torch::Tensor matmul(const torch::Tensor& A, const torch::Tensor& B, const torch
 torch::Tensor matmul_dev_alpha(const torch::Tensor& A, const torch::Tensor& B, const torch::Tensor& SFA,
                                const torch::Tensor& SFB, const torch::Tensor& alpha_a,
                                const c10::optional<torch::Tensor>& alpha_b) {
-  require_cuda(A, "A");
-  require_cuda(B, "B");
-  const int64_t M = A.size(0), N = B.size(0), K = A.size(1) * 2;
+  int64_t M, N, K;
+  std::tie(M, N, K) = check_gemm_operands(A, B, SFA, SFB);
+  require_scalar_f32(alpha_a, A, "alpha_a");
+  if (alpha_b.has_value()) require_scalar_f32(*alpha_b, A, "alpha_b");
   c10::cuda::CUDAGuard guard(A.device());
   auto C = torch::empty({M, N}, torch::dtype(torch::kBFloat16).device(A.device()));
   // skinny problems split K over idle SMs; the fp32 partial sums need scratch
@@ -132,11 +159,14 @@ std::tuple<torch::Tensor, torch::Tensor> reorder_quantize_x_scaled(const torch::
                                                                    const torch::Tensor& reorder_index, const int KE,
                                                                    int mode) {
   require_cuda(X, "input");
-  require_cuda(reorder_index, "reorder_index");
+  require_on(reorder_index, X, at::kShort, "reorder_index");
+  require_scalar_f32(scale, X, "scale");
   TORCH_CHECK(X.dim() == 2, "input must be 2-D");
   const int64_t rows = X.size(0);
   const int KQ = static_cast<int>(X.size(1));
   const int K = KQ + KE;
+  TORCH_CHECK(KE >= 0 && KE <= KQ, "KE must lie in [0, KQ]");
+  TORCH_CHECK(reorder_index.numel() == KQ, "reorder_index must have KQ entries");
   if (mode < 0) mode = arcq_reference_mode(KQ);
   c10::cuda::CUDAGuard guard(X.device());
   auto options = torch::dtype(torch::kUInt8).device(X.device());
@@ -171,8 +201,8 @@ std::tuple<torch::Tensor, torch::Tensor> silu_mul(const torch::Tensor& GU) {
 torch::Tensor rope_inplace(torch::Tensor X, const torch::Tensor& cos_t, const torch::Tensor& sin_t, int heads,
                            int head_dim) {
   require_cuda(X, "x");
-  require_cuda(cos_t, "cos");
-  require_cuda(sin_t, "sin");
+  require_on(cos_t, X, at::kFloat, "cos");
+  require_on(sin_t, X, at::kFloat, "sin");
   TORCH_CHECK(X.dim() == 2 && cos_t.dim() == 2 && cos_t.size(1) == head_dim && cos_t.sizes() == sin_t.sizes(),
               "x must be [tokens, row]; cos / sin [seq, head_dim]");
   c10::cuda::CUDAGuard guard(X.device());

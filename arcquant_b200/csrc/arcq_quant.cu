@@ -52,6 +52,8 @@ struct QuantParams {
   float eps;
   int dbg;        // timing experiments only (ARCQ_QUANT_DBG): 1 = no global loads, 2 = no quantize, 4 = no fill
   const float* scale;   // warp-specialised plain kernel only: x is divided by *scale (device) first, or nullptr
+  uint32_t hint;        // suspend-time hint (ns) of the mbarrier waits
+  int exp;              // experiment switches
 };
 
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
@@ -216,6 +218,19 @@ __device__ __forceinline__ uint32_t amax_pair(const uint32_t (&w)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) m = max_u16x2(m, w[i] & 0x7fff7fffu);
   return m;
+}
+
+// The same with the packed bf16 maximum of magnitudes (one instruction per word).  A NaN input gives
+// the canonical NaN 0x7fff, which the caller clamps like the integer maximum of a NaN pattern.
+__device__ __forceinline__ uint32_t amax_pair_h(const uint32_t (&w)[16]) {
+  uint32_t m[4] = {w[0], w[1], w[2], w[3]};
+#pragma unroll
+  for (int i = 4; i < 16; ++i)
+    asm("max.NaN.xorsign.abs.bf16x2 %0, %0, %1;" : "+r"(m[i & 3]) : "r"(w[i]));
+  asm("max.NaN.xorsign.abs.bf16x2 %0, %0, %1;" : "+r"(m[0]) : "r"(m[1]));
+  asm("max.NaN.xorsign.abs.bf16x2 %0, %0, %1;" : "+r"(m[2]) : "r"(m[3]));
+  asm("max.NaN.xorsign.abs.bf16x2 %0, %0, %1;" : "+r"(m[0]) : "r"(m[2]));
+  return m[0] & 0x7fff7fffu;
 }
 
 // Residuals of a critical group, both rows: w[i] <- bf16(x - q*s) per half.
@@ -539,9 +554,6 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
 // the approximate reciprocal plus one Newton step (exact here: a scale is k*2^e with k <= 15, so its
 // reciprocal lies far from every fp32 rounding boundary).
 
-#ifndef ARCQ_WAIT_HINT_NS
-#define ARCQ_WAIT_HINT_NS 0u
-#endif
 __device__ int g_quant_error = 0;   // sticky until polled
 constexpr unsigned long long QUANT_WAIT_LIMIT_NS = 2000000000ull;
 
@@ -554,15 +566,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-#if ARCQ_WAIT_HINT_NS > 0
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"   // may sleep up to the hint (ns)
-      "selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(ARCQ_WAIT_HINT_NS)
-      : "memory");
-#else
   asm volatile(
       "{\n.reg .pred p;\n"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
@@ -570,21 +573,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
-#endif
   return ok != 0;
 }
-// Bounded wait: false if this wait (or another warp's) gave up; the CTA then winds down.
-// (Polling from one lane with sleeps in between was measured slower: the hand-over latency counts.)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// The same with a suspend-time hint: the warp may sleep in hardware for up to `hint` nanoseconds and
+// wakes when the phase completes, so a long wait costs few issue slots.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if this wait (or another warp's) gave up; the CTA then winds down.  The clock is
+// first read after 64 failed polls, so a wait of ordinary length never touches it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t hint) {
   if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  unsigned long long t0 = 0;
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 255u) == 0) {
+    if (hint & 0x80000000u) {   // experiment: sleep between polls
+      if (mbar_try_wait(bar, parity)) return true;
+      __nanosleep(hint & 0xffffu);
+    } else if (hint ? mbar_try_wait_hint(bar, parity, hint) : mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0) {
       if (*abort_flag) return false;
       unsigned long long t1;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+      if (t0 == 0) t0 = t1;
       if (t1 - t0 > QUANT_WAIT_LIMIT_NS) {
         *abort_flag = 1;
         atomicExch(&g_quant_error, ARCQ_ERR_TIMEOUT);
@@ -643,8 +661,8 @@ __device__ __forceinline__ void scale_of_pair_fma(uint32_t m, uint32_t& codes, f
 // scale column c start at byte 8 c of the row, and a critical group's residual sits 1 (mode 16) or 2
 // (mode 32) columns after its main part.
 __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g, int G0, bool mode32, bool is_weight,
-                                                       uint8_t* q0, uint8_t* q1, uint8_t* sf0, uint8_t* sf1) {
-  const uint32_t m = amax_pair(w);
+                                                       uint8_t* q0, uint8_t* q1, uint8_t* sf0, uint8_t* sf1, int exp) {
+  const uint32_t m = (exp & 1) ? amax_pair_h(w) : amax_pair(w);
   uint32_t codes;
   float2 dec, rcp;
   scale_of_pair_fma(m, codes, dec, rcp);
@@ -670,7 +688,7 @@ __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g,
       d1 = make_scale_slow(__uint_as_float((m >> 16) << 16)).raw;
     }
     residual_pair(w, c0, c1, d0, d1);
-    const uint32_t rm = amax_pair(w);
+    const uint32_t rm = (exp & 1) ? amax_pair_h(w) : amax_pair(w);
     float2 rdec, rrcp;
     scale_of_pair_fma(rm, rcodes, rdec, rrcp);
     encode_pair(w, rrcp.x, rrcp.y, e0, e1);
@@ -738,6 +756,8 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   const int tid = threadIdx.x;
   const int KQ = p.KQ, G = p.G;
   const uint32_t rows = (uint32_t)p.rows, npairs = (uint32_t)p.npairs;
+  const uint32_t hint = p.hint;
+  const int exp = p.exp;
 
   // shared layout: [barriers, abort flag: 384 B][offsets][partial sums, rstd][gather ring][raw ring]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
@@ -866,7 +886,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       if (helper < 2) {
         // -------------------------------------------------------------- reducers (row = helper)
         for (uint32_t m = 0; m < nt; ++m) {
-          if (!mbar_wait(psr + 8 * (m & 1u), (m >> 1) & 1u, abort_flag)) break;
+          if (!mbar_wait(psr + 8 * (m & 1u), (m >> 1) & 1u, abort_flag, hint)) break;
           const float t = rms_tree(psum + (size_t)(m & 1u) * 2 * npt + helper * npt, npt, lane);
           if (lane == 0) {
             rstd_s[(m & 1u) * 2 + helper] = __frsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)KQ), p.eps));
@@ -989,9 +1009,9 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
         const uint32_t it = u >> 1, h = u & 1u;
         const uint32_t unit = blockIdx.x + it * stride;
         const bool has1 = (2 * unit + 1) < rows;
-        if (!failed && !mbar_wait(raw0 + 8 * (u % R), (u / R) & 1u, abort_flag)) failed = true;
+        if (!failed && !mbar_wait(raw0 + 8 * (u % R), (u / R) & 1u, abort_flag, hint)) failed = true;
         if (!failed) landed = u + 1;
-        if (h == 0 && !failed && !mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag)) failed = true;
+        if (h == 0 && !failed && !mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag, hint)) failed = true;
         if (!failed) {
           const uint4* rw = reinterpret_cast<const uint4*>(raw + (size_t)(u % R) * row_in_bytes);
           uint4* b4 = reinterpret_cast<uint4*>(stages + (size_t)(it % S) * stage_bytes);
@@ -1037,9 +1057,9 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       for (uint32_t it = 0; it < n; ++it) {
         const uint32_t unit = blockIdx.x + it * stride;
         const bool has1 = (2 * unit + 1) < rows;
-        if (!failed && !mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) failed = true;
+        if (!failed && !mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag, hint)) failed = true;
         if (!failed) landed = it + 1;
-        if (!failed && !mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag)) failed = true;
+        if (!failed && !mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag, hint)) failed = true;
         if (!failed) {
           // this thread's chunks c = ptid, ptid + npt, ...: interleave the two rows (dividing by the
           // tensor's scale first, if asked) straight from the raw stage into the gather stage
@@ -1089,10 +1109,10 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
         const uint32_t it = pteam + m * NP;               // pair number within the CTA
         if (m >= 1) {
           const uint32_t j = it - NP, q = m - 1;
-          if (!mbar_wait(rsr + 8 * (q & 1u), (q >> 1) & 1u, abort_flag)) break;
+          if (!mbar_wait(rsr + 8 * (q & 1u), (q >> 1) & 1u, abort_flag, hint)) break;
           if (pteam == 0 && ptid == 0) ARCQ_QT(1, q);
           const float2 rstd = make_float2(rstd_s[(q & 1u) * 2], rstd_s[(q & 1u) * 2 + 1]);
-          if (!mbar_wait(empty0 + 8 * (j % S), ((j / S) & 1u) ^ 1u, abort_flag)) break;
+          if (!mbar_wait(empty0 + 8 * (j % S), ((j / S) & 1u) ^ 1u, abort_flag, hint)) break;
           if (pteam == 0 && ptid == 0) ARCQ_QT(2, q);
           fill_stage(j, a0, a1, b0, b1, rstd);
           if (pteam == 0 && ptid == 0) ARCQ_QT(3, q);
@@ -1100,7 +1120,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
         if (m < nt) {
           const uint32_t unit = blockIdx.x + it * stride;
           const bool has1 = (2 * unit + 1) < rows;
-          if (!mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) break;
+          if (!mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag, hint)) break;
           if (pteam == 0 && ptid == 0) ARCQ_QT(4, m);
           read_raw(it, has1, a0, a1, b0, b1);
           // reference thread t adds chunk t, then chunk t + KQ/16, eight elements each, in order
@@ -1160,7 +1180,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       uint8_t* q1 = has1 ? q0 + row_bytes : q0;
       uint8_t* sf1 = has1 ? sf0 + 16 : sf0;
       const uint8_t* buf = stages + (size_t)s * stage_bytes;
-      if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) break;
+      if (!mbar_wait(full0 + 8 * s, ph, abort_flag, hint)) break;
       if (tid == 0) ARCQ_QT(6, it / (uint32_t)nteams);
       for (int g = slot * 32 + lane; g < G; g += nct) {
         uint32_t w[16];
@@ -1191,7 +1211,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
           __syncwarp();
           if (lane == 0) mbar_arrive(empty0 + 8 * s);
         }
-        quantize_group_pair_ws(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1);
+        quantize_group_pair_ws(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1, exp);
       }
       slot = slot + 1 == ncw ? 0 : slot + 1;
       if (tid == 0) ARCQ_QT(7, it / (uint32_t)nteams);
@@ -1300,6 +1320,10 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   p.dbg = 0;
   p.scale = scale;
   if (const char* e = getenv("ARCQ_QUANT_DBG")) p.dbg = atoi(e);
+  static const int hint_env = [] { const char* e = getenv("ARCQ_QUANT_HINT"); return e ? atoi(e) : 0; }();
+  static const int exp_env = [] { const char* e = getenv("ARCQ_QUANT_EXP"); return e ? atoi(e) : 0; }();
+  p.hint = (uint32_t)hint_env | ((exp_env & 2) ? 0x80000000u : 0u);
+  p.exp = exp_env;
 
   const bool rms = gamma != nullptr;
   int nt, cpt;
@@ -1376,6 +1400,9 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
         npteams = 1;   // not enough shared memory for two pipelines
         fixed = 384 + (size_t)KQ * 4 + (size_t)4 * npt * sizeof(float) + 16;
       }
+      // A consumer team that is more than one lap of the gather ring ahead would pass its "full" wait
+      // on the previous lap's phase: never more consumer teams than gather stages.
+      if (nteams > S) nteams = S;
       const int r_floor = 2 * npteams;
       int R = 8;
       while (R > r_floor && fixed + (S + R) * stage > (size_t)di.max_smem_optin) R -= 2;

@@ -48,3 +48,64 @@ def valid_sf(sf, rows: int, k_eff: int):
     off = O.sf_valid_offsets(rows, k_eff)
     a = sf if isinstance(sf, np.ndarray) else sf.cpu().numpy()
     return a[off]
+
+
+def steady_state_rows(tokens: int, ctas: int = 148, ring: int = 8, extra: int = 24, seed: int = 0) -> torch.Tensor:
+    """Rows that exercise the persistent quantizer's steady state: a CTA b of `ctas` takes the row
+    pairs b, b + ctas, b + 2 ctas, ...; its k-th pair occupies ring stage k % ring.  Returned are both
+    rows of the pairs k = 0, ring-1, ring, ring+1, middle, last-1, last of several CTAs (first, second,
+    middle, last), plus the first and last rows of the tensor and `extra` random rows."""
+    npairs = (tokens + 1) // 2
+    per_cta = max(1, npairs // ctas)
+    ks = sorted({0, ring - 1, ring, ring + 1, per_cta // 2, per_cta - 2, per_cta - 1})
+    rows = set(range(min(4, tokens))) | set(range(max(0, tokens - 4), tokens))
+    for b in (0, 1, ctas // 2, ctas - 1):
+        for k in ks:
+            pair = b + k * ctas
+            if 0 <= pair < npairs:
+                rows.update(r for r in (2 * pair, 2 * pair + 1) if r < tokens)
+    g = torch.Generator().manual_seed(seed)
+    rows.update(torch.randint(0, tokens, (extra,), generator=g).tolist())
+    return torch.tensor(sorted(rows), dtype=torch.int64)
+
+
+def sampled_rows_match_oracle(q, sf, rows: torch.Tensor, q_oracle: np.ndarray, sf_oracle: np.ndarray, k_eff: int):
+    """Codes and every valid scale byte of the sampled rows of a large launch (q, sf: device tensors of
+    the whole launch) against the oracle run on those rows alone (row j of the oracle = row rows[j])."""
+    qg = q[rows.to(q.device)].cpu().numpy()
+    bad = np.argwhere(qg != q_oracle)
+    assert bad.size == 0, f"{len(bad)} code bytes differ, first (sample, byte) {bad[:4].tolist()}, rows {rows[bad[:4, 0]].tolist()}"
+    ncols = k_eff // 16
+    natoms = (ncols + 3) // 4
+    c = np.arange(ncols, dtype=np.int64)[None, :]
+
+    def offsets(r):
+        r = np.asarray(r, dtype=np.int64)[:, None]
+        return ((r // 128) * natoms + c // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + (c % 4)
+
+    og = offsets(rows.numpy())
+    oo = offsets(np.arange(len(rows)))
+    sg = sf.cpu().numpy()[og]
+    so = np.asarray(sf_oracle)[oo]
+    bad = np.argwhere(sg != so)
+    assert bad.size == 0, f"{len(bad)} scale bytes differ, first (sample, column) {bad[:4].tolist()}, rows {rows[bad[:4, 0]].tolist()}"
+
+
+def sf_take_rows(sf, rows, k_eff: int) -> np.ndarray:
+    """Scale bytes of the sampled rows of a packed operand, re-laid out as the scale buffer of an operand
+    that consists of those rows only (row j of the result = row rows[j] of the source)."""
+    from oracle import oracle as O
+
+    src = sf if isinstance(sf, np.ndarray) else sf.cpu().numpy()
+    rows = np.asarray(rows, dtype=np.int64)
+    ncols = k_eff // 16
+    natoms = (ncols + 3) // 4
+    c = np.arange(ncols, dtype=np.int64)[None, :]
+
+    def offsets(r):
+        r = np.asarray(r, dtype=np.int64)[:, None]
+        return ((r // 128) * natoms + c // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + (c % 4)
+
+    out = np.zeros(O.sf_alloc_bytes(len(rows), k_eff), np.uint8)
+    out[offsets(np.arange(len(rows)))] = src[offsets(rows)]
+    return out

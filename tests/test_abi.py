@@ -84,3 +84,59 @@ def test_agemm_module_surface():
         assert callable(getattr(agemm, name))
     with pytest.raises(RuntimeError):
         agemm.reorder_quantize_x(torch.zeros(4, 64, dtype=torch.bfloat16), torch.arange(64, dtype=torch.int16), 0)
+
+
+def test_agemm_rejects_host_tensors_and_short_buffers_before_any_launch():
+    """Every tensor a kernel would dereference is checked by the extension itself: a CPU scalar, a
+    short index or a short scale buffer raises here instead of reaching a kernel as a bad pointer."""
+    import importlib
+    import sys
+
+    sys.path.insert(0, os.path.join(ROOT, "arcquant_b200"))
+    agemm = importlib.import_module("agemm")
+    x = torch.zeros(4, 64, dtype=torch.bfloat16)
+    idx = torch.arange(64, dtype=torch.int16)
+    u8 = torch.zeros(4, 32, dtype=torch.uint8)
+    sf = torch.zeros(512, dtype=torch.uint8)
+    s = torch.tensor(1.0)
+    for call in (lambda: agemm.reorder_quantize_x_scaled(x, s, idx, 0),
+                 lambda: agemm.matmul_dev_alpha(u8, u8, sf, sf, s, None),
+                 lambda: agemm.matmul(u8, u8, sf, sf, 1.0),
+                 lambda: agemm.rmsnorm_quantize_x(x, x[0], 1e-5, idx, 0),
+                 lambda: agemm.absmax(x)):
+        with pytest.raises(RuntimeError, match="CUDA tensor"):
+            call()
+
+
+@pytest.mark.gpu
+def test_agemm_argument_checks_on_device_tensors():
+    import importlib
+    import sys
+
+    sys.path.insert(0, os.path.join(ROOT, "arcquant_b200"))
+    agemm = importlib.import_module("agemm")
+    dev = "cuda"
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device=dev)
+    idx = torch.arange(64, dtype=torch.int16, device=dev)
+    s = torch.tensor(1.0, device=dev)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):            # a host amax passed as the scale
+        agemm.reorder_quantize_x_scaled(x, torch.tensor(1.0), idx, 0)
+    with pytest.raises(RuntimeError, match="KQ entries"):             # a short index
+        agemm.reorder_quantize_x_scaled(x, s, idx[:32].contiguous(), 0)
+    with pytest.raises(RuntimeError, match="KQ entries"):
+        agemm.reorder_quantize_x(x, idx[:32].contiguous(), 0)
+    with pytest.raises(RuntimeError, match="expected"):               # index of the wrong type
+        agemm.reorder_quantize_x(x, idx.int(), 0)
+    a = torch.zeros(4, 32, dtype=torch.uint8, device=dev)
+    b = torch.zeros(8, 32, dtype=torch.uint8, device=dev)
+    sf = torch.zeros(512, dtype=torch.uint8, device=dev)
+    with pytest.raises(RuntimeError, match="smaller than the scale layout"):
+        agemm.matmul(a, b, sf[:256].contiguous(), sf, 1.0)
+    with pytest.raises(RuntimeError, match="disagree on K"):
+        agemm.matmul(a, torch.zeros(8, 64, dtype=torch.uint8, device=dev), sf, sf, 1.0)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        agemm.matmul_dev_alpha(a, b, sf, sf, torch.tensor(1.0), None)
+    with pytest.raises(RuntimeError, match="one fp32 value"):
+        agemm.matmul_dev_alpha(a, b, sf, sf, torch.ones(2, device=dev), None)
+    torch.cuda.synchronize()                                          # nothing was launched, nothing faulted
+    assert agemm.matmul(a, b, sf, sf, 1.0).shape == (4, 8)

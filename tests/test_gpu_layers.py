@@ -263,3 +263,147 @@ def test_packed_layer_checkpoint_round_trip(tmp_path):
     checkpoint.save_packed_layer(layer, path)
     again = checkpoint.load_packed_layer(cfg, path)
     assert torch.equal(again(x), y)
+
+
+# ---- stage by stage at the Llama-3-8B widths ---------------------------------------------------------
+# Quantization is chaotic in its inputs, so an end-to-end comparison of a deep chain can only be judged
+# within a noise band.  Here every stage is judged by itself instead: the oracle is fed the GPU's own
+# bf16 input of that stage, so each quantizer is held to bit-exactness and each GEMM to 1e-3.
+
+
+def _check_stage(name, x_in, qa, sfa, lin, y, scale_x=None, gamma=None, eps=0.0, ncols_sample=384):
+    """x_in: the bf16 tensor the stage's quantizer consumed (already divided by its per-tensor scale where
+    the stage has one); qa / sfa: what the GPU quantizer produced; lin: PackedLinear; y: the GEMM output."""
+    from oracle import oracle as O
+    from tests.helpers import sf_take_rows, valid_sf
+
+    rows, kq = x_in.shape
+    ke = lin.select_num
+    qo, sfo = O.quantize_x(x_in.cpu(), lin.index.cpu().numpy(), ke, gamma=None if gamma is None else gamma.cpu(), eps=eps)
+    assert np.array_equal(qa.cpu().numpy(), qo), f"{name}: activation codes differ from the oracle"
+    assert np.array_equal(valid_sf(sfa, rows, kq + ke), valid_sf(sfo, rows, kq + ke)), f"{name}: scales differ"
+    n = lin.W.shape[0]
+    g = torch.Generator().manual_seed(len(name))
+    cols = torch.cat([torch.arange(0, 8), torch.arange(n - 8, n), torch.randint(0, n, (ncols_sample,), generator=g)])
+    b = lin.W[cols.cuda()].cpu().numpy()
+    sfb = sf_take_rows(lin.SFW, cols.numpy(), kq + ke)
+    alpha = float(lin.scale) * (1.0 if scale_x is None else float(scale_x))
+    ref = O.gemm_fast(qo, sfo, b, sfb, alpha)
+    refb = torch.from_numpy(ref).to(torch.bfloat16).float().numpy()
+    got = y[:, cols.cuda()].float().cpu().numpy()
+    err = float(np.linalg.norm(got - refb) / np.linalg.norm(refb))
+    assert err <= 1e-3, f"{name}: GEMM relative Frobenius error {err}"
+    assert (got == refb).mean() >= 0.99, name
+
+
+def test_llama_3_8b_width_layer_stage_by_stage():
+    from arcquant_b200 import ops
+    from arcquant_b200.llama_layer import (LlamaLayerConfig, QLlamaDecoderLayerTP, random_layer_weights,
+                                           random_reorder_indices, rope_tables)
+    from arcquant_b200.qlinear import NVFP4_reorder_quantize_x
+    from oracle import oracle as O
+
+    cfg = LlamaLayerConfig()                      # hidden 4096, 32 / 8 heads, FFN 14336, select_num 128
+    W, I = random_layer_weights(cfg, 0), random_reorder_indices(cfg, 1)
+    layer = QLlamaDecoderLayerTP(cfg, W, I)
+    bsz, seq, D = 2, 160, cfg.head_dim
+    T = bsz * seq
+    x = synth.activations(T, cfg.hidden, 4, synth.outlier_channels(cfg.hidden, 41, 3)).cuda()
+    pos = torch.arange(seq, device="cuda")
+
+    # the offline packer, on a sample of weight rows of the widest and the longest linear
+    for lin, w in ((layer.gate_up, torch.cat([W["w_gate"], W["w_up"]], 0)), (layer.down, W["w_down"])):
+        rows = torch.randint(0, w.shape[0], (48,), generator=torch.Generator().manual_seed(1))
+        sw = torch.max(w.cuda()).float() / 2688.0
+        assert float(sw) == float(lin.scale)
+        ws = (w.cuda() / sw)[rows.cuda()].cpu().contiguous()
+        qo, _ = O.quantize_w(ws, lin.index.cpu().numpy(), lin.select_num)
+        assert np.array_equal(lin.W[rows.cuda()].cpu().numpy(), qo)
+
+    # stage 1: RMSNorm + quantize -> fused q/k/v projection
+    a, sfa = ops.rmsnorm_quantize_x(x, layer.ln1, cfg.eps, layer.qkv.index, layer.qkv.select_num)
+    qkv = layer.qkv.gemm(a, sfa)
+    _check_stage("qkv", x, a, sfa, layer.qkv, qkv, gamma=layer.ln1, eps=cfg.eps)
+    nq, nk = cfg.n_heads * D, cfg.n_kv_heads * D
+    cos, sin = rope_tables(pos, D, cfg.rope_theta)
+    ops.rope_inplace(qkv, cos, sin, cfg.n_heads + cfg.n_kv_heads, D)
+    q = qkv[:, :nq].reshape(bsz, seq, cfg.n_heads, D).transpose(1, 2)
+    k = qkv[:, nq:nq + nk].reshape(bsz, seq, cfg.n_kv_heads, D).transpose(1, 2)
+    v = qkv[:, nq + nk:].reshape(bsz, seq, cfg.n_kv_heads, D).transpose(1, 2)
+    attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+    attn = attn.transpose(1, 2).reshape(T, nq).contiguous()
+    # stage 2: per-tensor scale, division, quantize -> o projection
+    qa, sfo, so = NVFP4_reorder_quantize_x(attn, layer.o.index, layer.o.select_num, mode=16)
+    assert float(so) == float(attn.abs().max().float() / 2688.0)
+    yo = layer.o.gemm(qa, sfo, so)
+    _check_stage("o", attn / so, qa, sfo, layer.o, yo, scale_x=so)
+    h = x + yo
+    # stage 3: RMSNorm + quantize -> fused gate/up projection
+    a, sfa = ops.rmsnorm_quantize_x(h, layer.ln2, cfg.eps, layer.gate_up.index, layer.gate_up.select_num)
+    gu = layer.gate_up.gemm(a, sfa)
+    _check_stage("gate_up", h, a, sfa, layer.gate_up, gu, gamma=layer.ln2, eps=cfg.eps)
+    act, amax = ops.silu_mul(gu)
+    assert torch.equal(act, F.silu(gu[:, :cfg.ffn]) * gu[:, cfg.ffn:])
+    # stage 4: per-tensor scale, division, quantize (14336 channels) -> down projection
+    qd, sfd, sd = NVFP4_reorder_quantize_x(act, layer.down.index, layer.down.select_num, mode=16, amax=amax)
+    yd = layer.down.gemm(qd, sfd, sd)
+    _check_stage("down", act / sd, qd, sfd, layer.down, yd, scale_x=sd)
+    out = (h + yd).reshape(bsz, seq, cfg.hidden)
+    # ... and the chain above is what the layer itself computes
+    assert torch.equal(layer(x.reshape(bsz, seq, cfg.hidden), pos), out)
+    assert ops.gemm_poll_error() == 0
+
+
+def test_qlinear_layer_mirror():
+    """`QLinearLayer` as the reference's layers use it (model/qLinearLayer.py:30-81 of ARCQuant): built from
+    an nn.Linear, called with the tuple (qx, scale_x, scale, bsz, q_len); bias, both reshapes, a host
+    float as well as a device tensor for the activation scale, and the state_dict round trip."""
+    import torch.nn as nn
+
+    from arcquant_b200.qlinear import NVFP4_reorder_quantize_x, QLinearLayer
+
+    kq, n, ke, bsz, q_len = 1024, 768, 64, 2, 24
+    g = torch.Generator().manual_seed(3)
+    lin = nn.Linear(kq, n, bias=True)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(n, kq, generator=g) * 0.02)
+        lin.bias.copy_(torch.randn(n, generator=g) * 0.1)
+    lin = lin.to(torch.bfloat16)
+    x = synth.activations(bsz * q_len, kq, 5, synth.outlier_channels(kq, 10, 6))
+    idx = synth.reorder_index_from_stats(x.abs().amax(0))
+    layer = QLinearLayer(lin, ke, idx)
+    qx, scale_x, scale = NVFP4_reorder_quantize_x(x.cuda(), idx.cuda(), ke)
+    y = layer((qx, scale_x, scale, bsz, q_len))
+    assert y.shape == (bsz, q_len, n) and y.dtype == torch.bfloat16
+    # reference of the same linear: oracle quantizers (signed maximum for the weight, as the reference
+    # takes it), fp64 matmul, bf16 output, bias added in bf16
+    from oracle import oracle as O
+
+    w = lin.weight.data
+    sw, sx = torch.max(w).float() / 2688.0, x.abs().max().float() / 2688.0
+    assert float(sw) == float(layer.scale) and float(sx) == float(scale)
+    # (torch's CUDA kernel for bf16 / fp32-scalar rounds the divisor to bf16 first)
+    div = lambda t, s: (t.float() / s.to(torch.bfloat16).float()).to(torch.bfloat16).contiguous()
+    qb, sfb = O.quantize_w(div(w, sw), idx.numpy(), ke)
+    qa, sfa = O.quantize_x(div(x, sx), idx.numpy(), ke)
+    assert np.array_equal(layer.W.cpu().numpy(), qb) and np.array_equal(qx.cpu().numpy(), qa)
+    ref = torch.from_numpy(O.gemm_fast(qa, sfa, qb, sfb, float(sx) * float(sw))).to(torch.bfloat16) + lin.bias.data
+    assert _rel(y.reshape(-1, n).cpu(), ref) <= 1e-3
+    y2 = layer((qx, scale_x, float(scale), None, bsz * q_len))            # host scale, 2-D result
+    assert y2.shape == (bsz * q_len, n)
+    assert _rel(y2.cpu(), y.reshape(-1, n).cpu()) <= 1e-3
+    # no bias
+    lin_nb = nn.Linear(kq, n, bias=False).to(torch.bfloat16)
+    with torch.no_grad():
+        lin_nb.weight.copy_(w)
+    layer_nb = QLinearLayer(lin_nb, ke, idx)
+    assert layer_nb.bias is None
+    y3 = layer_nb((qx, scale_x, scale, bsz, q_len))
+    assert torch.equal((y3 + lin.bias.data.cuda()), y)
+    # packed weight, block scales and global scale travel through state_dict
+    sd = layer.state_dict()
+    assert {"W", "scale_w", "scale", "bias"} <= set(sd)
+    layer_nb.load_state_dict({k: v for k, v in sd.items() if k != "bias"})
+    assert torch.equal(layer_nb((qx, scale_x, scale, bsz, q_len)), y3)
+    with pytest.raises(NotImplementedError):
+        QLinearLayer(lin, ke, idx, quant_type="MXFP4")

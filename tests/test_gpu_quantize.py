@@ -5,7 +5,8 @@ import pytest
 import torch
 
 from arcquant_b200 import synth
-from tests.helpers import adversarial_rows, scaled_activations, valid_sf
+from tests.helpers import (adversarial_rows, sampled_rows_match_oracle, scaled_activations, steady_state_rows,
+                           valid_sf)
 
 pytestmark = pytest.mark.gpu
 
@@ -186,6 +187,110 @@ def test_full_size_is_row_independent_and_matches_oracle_on_samples():
     for j, r in enumerate(rows.tolist()):
         for c in (0, 1, 131, 247, 248, 249, 263):
             assert sfh[O.sf_offset(r, c, ncols)] == sfo[O.sf_offset(j, c, ncols)]
+
+
+# ---- steady state of the persistent kernels: many row pairs per CTA, rings wrapping ----------------
+# The launches below are too large for the scalar oracle as a whole; rows are independent, so the
+# oracle runs on a sample chosen to hit the first, ring-wrapping, middle and last pairs of several
+# CTAs (see tests.helpers.steady_state_rows).
+
+
+def _big_inputs(tokens, kq, seed):
+    dev = torch.device("cuda:0")
+    out = synth.outlier_channels(kq, max(1, kq // 100), seed)
+    x = synth.activations(tokens, kq, seed + 1, out, device=dev)
+    idx = synth.reorder_index_from_stats(x[:2048].abs().amax(0))
+    return x, idx
+
+
+@pytest.mark.parametrize("tokens", [1024, 8192, 32768])
+@pytest.mark.parametrize("ke", [0, 64, 128, 256])
+def test_rmsnorm_quantize_x_steady_state(tokens, ke):
+    """Fused RMSNorm at the token counts of the kernel-alone benchmark grid (hidden 4096): every CTA
+    takes up to 111 row pairs, both producer teams alternate, raw and gather rings wrap many times."""
+    ops, O = _ops(), _oracle()
+    kq = 4096
+    x, idx = _big_inputs(tokens, kq, 40 + ke)
+    gamma = synth.rms_gain(kq, 3)
+    q, sf = ops.rmsnorm_quantize_x(x, gamma.cuda(), 1e-5, idx.cuda(), ke)
+    torch.cuda.synchronize()
+    assert ops.gemm_poll_error() == 0
+    rows = steady_state_rows(tokens)
+    qo, sfo = O.quantize_x(x[rows.cuda()].cpu(), idx.numpy(), ke, gamma=gamma, eps=1e-5)
+    sampled_rows_match_oracle(q, sf, rows, qo, sfo, kq + ke)
+
+
+@pytest.mark.parametrize("kq", [2048, 8192])
+def test_rmsnorm_quantize_x_steady_state_other_widths(kq):
+    ops, O = _ops(), _oracle()
+    tokens, ke = 16384, 128
+    x, idx = _big_inputs(tokens, kq, kq)
+    gamma = synth.rms_gain(kq, 5)
+    q, sf = ops.rmsnorm_quantize_x(x, gamma.cuda(), 1e-5, idx.cuda(), ke)
+    rows = steady_state_rows(tokens)
+    qo, sfo = O.quantize_x(x[rows.cuda()].cpu(), idx.numpy(), ke, gamma=gamma, eps=1e-5)
+    sampled_rows_match_oracle(q, sf, rows, qo, sfo, kq + ke)
+
+
+@pytest.mark.parametrize("kq,tokens", [(14336, 16384), (8192, 16384), (14336, 16383), (1024, 40000), (7168, 8192),
+                                       (3584, 8192), (1792, 8192), (512, 8192)])
+def test_reorder_quantize_x_steady_state_wide_and_shard_widths(kq, tokens):
+    """Plain operator at the down projection's width (half-pair raw ring), at an odd row count, and at
+    the row-parallel shard widths of 2, 4 and 8 ranks."""
+    ops, O = _ops(), _oracle()
+    ke = 128 if kq >= 4096 else 64
+    x, idx = _big_inputs(tokens, kq, kq + 1)
+    mode = O.reference_mode(kq)
+    q, sf = ops.reorder_quantize_x(x, idx.cuda(), ke, mode=mode)
+    torch.cuda.synchronize()
+    assert ops.gemm_poll_error() == 0
+    rows = steady_state_rows(tokens, ring=3 if kq > 8192 else 8)
+    qo, sfo = O.quantize_x(x[rows.cuda()].cpu(), idx.numpy(), ke, mode=mode)
+    sampled_rows_match_oracle(q, sf, rows, qo, sfo, kq + ke)
+
+
+@pytest.mark.parametrize("kq,tokens", [(4096, 16384), (14336, 16384), (4096, 32767), (7168, 8192), (2048, 8192),
+                                       (3584, 8192), (1024, 8192), (1792, 8192), (512, 8192)])
+def test_fused_division_steady_state(kq, tokens):
+    """`scale=` (division by the per-tensor scale fused into the quantizer) at layer sizes, against the
+    oracle fed torch's own CUDA quotient x / scale - the reference callers' pre-scaling
+    (model/qLlamaLayer.py:73-77 of ARCQuant)."""
+    ops, O = _ops(), _oracle()
+    ke = 128 if kq >= 4096 else 64
+    x, idx = _big_inputs(tokens, kq, kq + 2)
+    mode = O.reference_mode(kq)
+    scale = ops.absmax(x) / 2688.0
+    q, sf = ops.reorder_quantize_x(x, idx.cuda(), ke, mode=mode, scale=scale)
+    torch.cuda.synchronize()
+    assert ops.gemm_poll_error() == 0
+    rows = steady_state_rows(tokens, ring=3 if kq > 8192 else 8)
+    xs = (x[rows.cuda()] / scale).cpu()
+    qo, sfo = O.quantize_x(xs, idx.numpy(), ke, mode=mode)
+    sampled_rows_match_oracle(q, sf, rows, qo, sfo, kq + ke)
+
+
+def test_reference_script_distribution_seed_45510():
+    """The input distribution of the reference's own manual check (kernels/main.py:8-33 of ARCQuant),
+    restated: seed 45510, 128 x 4096 uniform magnitudes in [0, 3) with random signs, the last 384
+    channels in [3, 6), the last 128 in [8, 16), the last 16 in [32, 64); identity channel order;
+    residual widths 0, 256, ..., 4096; activations and weights divided by max|.| / 2688 first.  (The
+    reference draws on the GPU, so the values differ; the distribution and the sweep are the same.)"""
+    ops, O = _ops(), _oracle()
+    g = torch.Generator().manual_seed(45510)
+    m, n, kq = 128, 64, 4096
+    sign = torch.randint(0, 2, (m, kq), generator=g).float() * 2 - 1
+    x = torch.rand(m, kq, generator=g) * 3
+    x[:, -384:] = torch.rand(m, 384, generator=g) * 3 + 3
+    x[:, -128:] = torch.rand(m, 128, generator=g) * 8 + 8
+    x[:, -16:] = torch.rand(m, 16, generator=g) * 32 + 32
+    x = (x * sign).to(torch.bfloat16)
+    w = (torch.rand(n, kq, generator=g) * 3).to(torch.bfloat16)
+    idx = torch.arange(kq, dtype=torch.int16)
+    xs = (x / (x.abs().max().float() / 2688.0)).contiguous()
+    ws = (w / (w.abs().max().float() / 2688.0)).contiguous()
+    for ke in range(0, kq + 1, kq // 16):
+        _check("x", xs, idx, ke, 16)
+        _check("w", ws, idx, ke, 16)
 
 
 def test_absmax():
