@@ -21,6 +21,8 @@ ERR_TIMEOUT = 6
 ERR_SCRATCH_LIMIT = 7
 STATIC_SCRATCH_BYTES = 2 << 20
 
+GEMM_KIND_SINGLE, GEMM_KIND_SPLIT_K, GEMM_KIND_PAIR = 0, 1, 2
+
 MODE_16 = 16
 MODE_32 = 32
 
@@ -39,6 +41,7 @@ SIGNATURES = {
     "arcq_matmul_nvfp4": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp]),
     "arcq_matmul_nvfp4_dev_alpha": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "arcq_matmul_workspace_bytes": (C.c_size_t, [_i64, _i64, _i64]),
+    "arcq_matmul_plan": (_i32, [_i64, _i64, _i64, _vp, _vp, _vp]),
     "arcq_matmul_nvfp4_ws": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
     "arcq_matmul_nvfp4_static": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _vp, _vp]),
     "arcq_gemm_poll_error": (_i32, []),

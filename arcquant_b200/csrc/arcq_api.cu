@@ -161,6 +161,11 @@ size_t arcq_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K_eff) {
   return gemm_workspace_bytes(M, N, K_eff);
 }
 
+int arcq_matmul_plan(int64_t M, int64_t N, int64_t K_eff, int* kind, int* tile_n, int* splits) {
+  if (M <= 0 || N <= 0 || K_eff <= 0 || K_eff % 64 || N % 8) return ARCQ_ERR_BAD_SHAPE;
+  return gemm_plan(M, N, K_eff, kind, tile_n, splits);
+}
+
 int arcq_matmul_nvfp4_ws(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                          int64_t N, int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* C,
                          void* workspace, size_t workspace_bytes, void* stream) {

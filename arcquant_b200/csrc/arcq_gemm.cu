@@ -970,6 +970,29 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K_eff) {
   return splits > 1 ? (size_t)splits * (size_t)M * (size_t)N * sizeof(float) : 0;
 }
 
+// Problems with enough 256 x 256 tiles to occupy at least half of the SM pairs run on CTA pairs
+// (about 1.4x the throughput of the single-CTA kernel).
+static bool use_pair_kernel(int64_t M, int64_t N, int num_sms) {
+  return (long long)((M + 255) / 256) * ((N + 255) / 256) >= num_sms / 4 && M > 128;
+}
+
+int gemm_plan(int64_t M, int64_t N, int64_t K_eff, int* kind, int* tile_n, int* splits) {
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  int k = ARCQ_GEMM_KIND_SINGLE, bn = 256, sp = 1;
+  if (use_pair_kernel(M, N, di.num_sms)) {
+    k = ARCQ_GEMM_KIND_PAIR;
+  } else {
+    plan_splitk(M, N, K_eff, di.num_sms, &bn, &sp);
+    if (sp > 1) k = ARCQ_GEMM_KIND_SPLIT_K;
+  }
+  if (kind) *kind = k;
+  if (tile_n) *tile_n = bn;
+  if (splits) *splits = sp;
+  return ARCQ_OK;
+}
+
 int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M, int64_t N,
                 int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* Cout,
                 void* workspace, size_t workspace_bytes, cudaStream_t stream) {
@@ -1006,11 +1029,7 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
     if (v == 64 || v == 128 || v == 256) bn = v;
   }
 
-  // Problems with enough 256 x 256 tiles to occupy at least half of the SM pairs run on CTA pairs
-  // (about 1.4x the throughput of the single-CTA kernel).  ARCQ_GEMM_PAIR=0/1 overrides the choice.
-  bool pair = (long long)((M + 255) / 256) * ((N + 255) / 256) >= di.num_sms / 4 && M > 128;
-  if (const char* e = getenv("ARCQ_GEMM_PAIR")) pair = atoi(e) != 0;
-  if (pair) return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream);
+  if (use_pair_kernel(M, N, di.num_sms)) return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream);
 
   // Skinny problems (few output tiles, long K): split K over otherwise idle SMs when the caller
   // provided scratch for the fp32 partial sums.

@@ -35,6 +35,8 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
                 int64_t N, int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* C,
                 void* workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K_eff);
+// Kernel choice for a shape (see arcq_matmul_plan).
+int gemm_plan(int64_t M, int64_t N, int64_t K_eff, int* kind, int* tile_n, int* splits);
 // Split-K GEMM whose scratch is the library's own static device array (no allocation anywhere).
 int launch_gemm_static(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                        int64_t N, int64_t K_eff, float alpha, const float* alpha_a, const float* alpha_b, void* C,

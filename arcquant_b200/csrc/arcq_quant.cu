@@ -50,10 +50,7 @@ struct QuantParams {
   int mode;       // 16 or 32 (placement of critical groups, residual flavour)
   int is_weight;  // residual slot = copy of the main codes
   float eps;
-  int dbg;        // timing experiments only (ARCQ_QUANT_DBG): 1 = no global loads, 2 = no quantize, 4 = no fill
   const float* scale;   // warp-specialised plain kernel only: x is divided by *scale (device) first, or nullptr
-  uint32_t hint;        // suspend-time hint (ns) of the mbarrier waits
-  int exp;              // experiment switches
 };
 
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
@@ -377,8 +374,8 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
       for (int j = 0; j < CPT; ++j) {
         int c = tid + j * nt;
         if (c < nchunks) {
-          ra[u][j] = (has0 && !(p.dbg & 1)) ? ldg_stream(x0 + c) : make_uint4(0, 0, 0, 0);
-          rb[u][j] = (has1 && !(p.dbg & 1)) ? ldg_stream(x1 + c) : make_uint4(0, 0, 0, 0);
+          ra[u][j] = has0 ? ldg_stream(x0 + c) : make_uint4(0, 0, 0, 0);
+          rb[u][j] = has1 ? ldg_stream(x1 + c) : make_uint4(0, 0, 0, 0);
         }
       }
     }
@@ -524,11 +521,11 @@ __global__ void __launch_bounds__(MAXT, MINB) arcq_quantize_kernel(const QuantPa
       }
 #pragma unroll
       for (int u = 0; u < PAIRS; ++u)
-        if (live[u] && !(p.dbg & 2)) quantize_group_pair(w[u], g, p, lut, q0[u], q1[u], sf0[u], sf1[u]);
+        if (live[u]) quantize_group_pair(w[u], g, p, lut, q0[u], q1[u], sf0[u], sf1[u]);
     }
 
     if (NBUF == 2) {
-      if (more && !(p.dbg & 4)) store_unit(bufs + (size_t)(cur ^ 1) * buf_words);
+      if (more) store_unit(bufs + (size_t)(cur ^ 1) * buf_words);
       __syncthreads();
       cur ^= 1;
     } else {
@@ -575,29 +572,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// The same with a suspend-time hint: the warp may sleep in hardware for up to `hint` nanoseconds and
-// wakes when the phase completes, so a long wait costs few issue slots.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-      "selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(hint)
-      : "memory");
-  return ok != 0;
-}
 // Bounded wait: false if this wait (or another warp's) gave up; the CTA then winds down.  The clock is
 // first read after 64 failed polls, so a wait of ordinary length never touches it.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t hint) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = 0;
   for (uint32_t it = 1;; ++it) {
-    if (hint & 0x80000000u) {   // experiment: sleep between polls
-      if (mbar_try_wait(bar, parity)) return true;
-      __nanosleep(hint & 0xffffu);
-    } else if (hint ? mbar_try_wait_hint(bar, parity, hint) : mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0) {
       if (*abort_flag) return false;
       unsigned long long t1;
@@ -661,8 +642,8 @@ __device__ __forceinline__ void scale_of_pair_fma(uint32_t m, uint32_t& codes, f
 // scale column c start at byte 8 c of the row, and a critical group's residual sits 1 (mode 16) or 2
 // (mode 32) columns after its main part.
 __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g, int G0, bool mode32, bool is_weight,
-                                                       uint8_t* q0, uint8_t* q1, uint8_t* sf0, uint8_t* sf1, int exp) {
-  const uint32_t m = (exp & 1) ? amax_pair_h(w) : amax_pair(w);
+                                                       uint8_t* q0, uint8_t* q1, uint8_t* sf0, uint8_t* sf1) {
+  const uint32_t m = amax_pair_h(w);
   uint32_t codes;
   float2 dec, rcp;
   scale_of_pair_fma(m, codes, dec, rcp);
@@ -688,7 +669,7 @@ __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g,
       d1 = make_scale_slow(__uint_as_float((m >> 16) << 16)).raw;
     }
     residual_pair(w, c0, c1, d0, d1);
-    const uint32_t rm = (exp & 1) ? amax_pair_h(w) : amax_pair(w);
+    const uint32_t rm = amax_pair_h(w);
     float2 rdec, rrcp;
     scale_of_pair_fma(rm, rcodes, rdec, rrcp);
     encode_pair(w, rrcp.x, rrcp.y, e0, e1);
@@ -741,14 +722,6 @@ __device__ __forceinline__ float div_guard(float s) {
 // npteams producer teams of npt = KQ/16 threads (more than one only with RMSNorm, whose producers carry
 // real arithmetic), sharing the pairs the same way; producer t of a team owns the 16-byte chunks t and
 // t + KQ/16 of each row, the reference's assignment and summation order for RMSNorm.
-#ifdef ARCQ_QUANT_TRACE
-// Timing experiments only (never compiled into the library): cycle stamps of CTA 0.
-__device__ long long g_qtrace[8][512];
-#define ARCQ_QT(k, i) do { if (blockIdx.x == 0 && (uint32_t)(i) < 512u) g_qtrace[k][i] = clock64(); } while (0)
-#else
-#define ARCQ_QT(k, i) do { } while (0)
-#endif
-
 template <bool RMS, bool WIDE, bool SCALED, int S, int R>
 __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantParams p, const int nct, const int npt, const int nteams,
                                                                         const int npteams) {
@@ -756,8 +729,6 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   const int tid = threadIdx.x;
   const int KQ = p.KQ, G = p.G;
   const uint32_t rows = (uint32_t)p.rows, npairs = (uint32_t)p.npairs;
-  const uint32_t hint = p.hint;
-  const int exp = p.exp;
 
   // shared layout: [barriers, abort flag: 384 B][offsets][partial sums, rstd][gather ring][raw ring]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
@@ -784,7 +755,6 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   const uint32_t rawe0 = raw0 + 8 * R, psr0 = rawe0 + 8 * R, rsr0 = psr0 + 8 * 4;
 
   asm volatile("griddepcontrol.launch_dependents;");   // the next kernel of the stream may be set up now
-  if (tid == 0) ARCQ_QT(0, 0);
   const uint32_t stride = gridDim.x;
   // Bulk copies of the rows of `unit` into raw stage `rs` (one thread).
   auto issue = [&](uint32_t unit, uint32_t rs) {
@@ -836,7 +806,6 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       if (WIDE) issue_half(r, r);
       else issue(blockIdx.x + r * stride, r);
     }
-    ARCQ_QT(0, 1);
   }
   // Everything before this line touched shared memory only; global memory may still be written by
   // the previous kernel of the stream (no-op unless launched as a programmatic dependent).
@@ -864,7 +833,6 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     for (int j = tid; j < KQ; j += blockDim.x) put(j, p.idx ? (int)p.idx[j] : j);
   }
   __syncthreads();
-  if (tid == 0) ARCQ_QT(0, 2);
 
   const int ncons = nteams * nct;
   if (tid >= ncons) {
@@ -886,7 +854,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       if (helper < 2) {
         // -------------------------------------------------------------- reducers (row = helper)
         for (uint32_t m = 0; m < nt; ++m) {
-          if (!mbar_wait(psr + 8 * (m & 1u), (m >> 1) & 1u, abort_flag, hint)) break;
+          if (!mbar_wait(psr + 8 * (m & 1u), (m >> 1) & 1u, abort_flag)) break;
           const float t = rms_tree(psum + (size_t)(m & 1u) * 2 * npt + helper * npt, npt, lane);
           if (lane == 0) {
             rstd_s[(m & 1u) * 2 + helper] = __frsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)KQ), p.eps));
@@ -1009,9 +977,9 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
         const uint32_t it = u >> 1, h = u & 1u;
         const uint32_t unit = blockIdx.x + it * stride;
         const bool has1 = (2 * unit + 1) < rows;
-        if (!failed && !mbar_wait(raw0 + 8 * (u % R), (u / R) & 1u, abort_flag, hint)) failed = true;
+        if (!failed && !mbar_wait(raw0 + 8 * (u % R), (u / R) & 1u, abort_flag)) failed = true;
         if (!failed) landed = u + 1;
-        if (h == 0 && !failed && !mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag, hint)) failed = true;
+        if (h == 0 && !failed && !mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag)) failed = true;
         if (!failed) {
           const uint4* rw = reinterpret_cast<const uint4*>(raw + (size_t)(u % R) * row_in_bytes);
           uint4* b4 = reinterpret_cast<uint4*>(stages + (size_t)(it % S) * stage_bytes);
@@ -1057,9 +1025,9 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       for (uint32_t it = 0; it < n; ++it) {
         const uint32_t unit = blockIdx.x + it * stride;
         const bool has1 = (2 * unit + 1) < rows;
-        if (!failed && !mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag, hint)) failed = true;
+        if (!failed && !mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) failed = true;
         if (!failed) landed = it + 1;
-        if (!failed && !mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag, hint)) failed = true;
+        if (!failed && !mbar_wait(empty0 + 8 * (it % S), ((it / S) & 1u) ^ 1u, abort_flag)) failed = true;
         if (!failed) {
           // this thread's chunks c = ptid, ptid + npt, ...: interleave the two rows (dividing by the
           // tensor's scale first, if asked) straight from the raw stage into the gather stage
@@ -1109,19 +1077,15 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
         const uint32_t it = pteam + m * NP;               // pair number within the CTA
         if (m >= 1) {
           const uint32_t j = it - NP, q = m - 1;
-          if (!mbar_wait(rsr + 8 * (q & 1u), (q >> 1) & 1u, abort_flag, hint)) break;
-          if (pteam == 0 && ptid == 0) ARCQ_QT(1, q);
+          if (!mbar_wait(rsr + 8 * (q & 1u), (q >> 1) & 1u, abort_flag)) break;
           const float2 rstd = make_float2(rstd_s[(q & 1u) * 2], rstd_s[(q & 1u) * 2 + 1]);
-          if (!mbar_wait(empty0 + 8 * (j % S), ((j / S) & 1u) ^ 1u, abort_flag, hint)) break;
-          if (pteam == 0 && ptid == 0) ARCQ_QT(2, q);
+          if (!mbar_wait(empty0 + 8 * (j % S), ((j / S) & 1u) ^ 1u, abort_flag)) break;
           fill_stage(j, a0, a1, b0, b1, rstd);
-          if (pteam == 0 && ptid == 0) ARCQ_QT(3, q);
         }
         if (m < nt) {
           const uint32_t unit = blockIdx.x + it * stride;
           const bool has1 = (2 * unit + 1) < rows;
-          if (!mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag, hint)) break;
-          if (pteam == 0 && ptid == 0) ARCQ_QT(4, m);
+          if (!mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) break;
           read_raw(it, has1, a0, a1, b0, b1);
           // reference thread t adds chunk t, then chunk t + KQ/16, eight elements each, in order
           float ss0 = 0.f, ss1 = 0.f;   // x*x is exact in fp32, so each step rounds once, like the fp32 FMA
@@ -1142,7 +1106,6 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
             mbar_arrive(rawe0 + 8 * (it % R));
             mbar_arrive(psr + 8 * (m & 1u));
           }
-          if (pteam == 0 && ptid == 0) ARCQ_QT(5, m);
         }
       }
     }
@@ -1180,8 +1143,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       uint8_t* q1 = has1 ? q0 + row_bytes : q0;
       uint8_t* sf1 = has1 ? sf0 + 16 : sf0;
       const uint8_t* buf = stages + (size_t)s * stage_bytes;
-      if (!mbar_wait(full0 + 8 * s, ph, abort_flag, hint)) break;
-      if (tid == 0) ARCQ_QT(6, it / (uint32_t)nteams);
+      if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) break;
       for (int g = slot * 32 + lane; g < G; g += nct) {
         uint32_t w[16];
         if (WIDE) {
@@ -1211,13 +1173,11 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
           __syncwarp();
           if (lane == 0) mbar_arrive(empty0 + 8 * s);
         }
-        quantize_group_pair_ws(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1, exp);
+        quantize_group_pair_ws(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1);
       }
       slot = slot + 1 == ncw ? 0 : slot + 1;
-      if (tid == 0) ARCQ_QT(7, it / (uint32_t)nteams);
     }
   }
-  if (tid == 0) ARCQ_QT(0, 3);
 }
 
 __global__ void arcq_absmax_kernel(const uint4* __restrict__ x, long long nvec, const uint16_t* tail,
@@ -1317,13 +1277,7 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   p.mode = mode;
   p.is_weight = is_weight;
   p.eps = eps;
-  p.dbg = 0;
   p.scale = scale;
-  if (const char* e = getenv("ARCQ_QUANT_DBG")) p.dbg = atoi(e);
-  static const int hint_env = [] { const char* e = getenv("ARCQ_QUANT_HINT"); return e ? atoi(e) : 0; }();
-  static const int exp_env = [] { const char* e = getenv("ARCQ_QUANT_EXP"); return e ? atoi(e) : 0; }();
-  p.hint = (uint32_t)hint_env | ((exp_env & 2) ? 0x80000000u : 0u);
-  p.exp = exp_env;
 
   const bool rms = gamma != nullptr;
   int nt, cpt;
@@ -1349,7 +1303,7 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   static const int nct_env = [] { const char* e = getenv("ARCQ_QUANT_NCT"); return e ? atoi(e) : 0; }();
   const bool gamma_ok = !rms || (reinterpret_cast<uintptr_t>(gamma) & 15u) == 0;   // read with 128-bit loads
   const bool wide = p.G > 512;
-  if (ws_env && p.dbg == 0 && gamma_ok && p.G % 32 == 0 && p.G >= 64 && rows < (1LL << 30) &&
+  if (gamma_ok && p.G % 32 == 0 && p.G >= 64 && rows < (1LL << 30) &&
       (wide ? (!rms && p.G <= 1024) : true)) {
     const size_t stage = (size_t)KQ * 4;
     if (wide) {
@@ -1486,9 +1440,3 @@ int launch_absmax(const void* x, int64_t n, float* out, int accumulate, cudaStre
 }
 
 }  // namespace arcq
-
-#ifdef ARCQ_QUANT_TRACE
-extern "C" int arcq_debug_qtrace_read(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, arcq::g_qtrace, sizeof(long long) * 8 * 512);
-}
-#endif

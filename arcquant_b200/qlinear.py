@@ -48,13 +48,13 @@ class QLinearLayer(nn.Module):
         self.out_features = originalLayer.out_features
         self.select_num = select_num
         self.quant_type = quant_type
-        if originalLayer.bias is not None:
-            self.register_buffer("bias", originalLayer.bias.detach().clone())
-        else:
-            self.bias = None
         w = originalLayer.weight.data
         if not w.is_cuda:
             w = w.cuda()
+        if originalLayer.bias is not None:
+            self.register_buffer("bias", originalLayer.bias.detach().to(w.device).clone())
+        else:
+            self.bias = None
         idx = reorder_index.to(torch.int16).to(w.device)
         W, scale_w, scale = NVFP4_reorder_quantize_w(w.to(torch.bfloat16).contiguous(), idx, select_num)
         self.register_buffer("W", W)

@@ -139,6 +139,16 @@ int arcq_matmul_nvfp4_ws(const uint8_t* A, const uint8_t* B, const uint8_t* SFA,
                          int64_t M, int64_t N, int64_t K_eff, float alpha, const float* alpha_a,
                          const float* alpha_b, void* C, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Which kernel arcq_matmul_nvfp4* would run for this shape on the current device (no counterpart in the
+ * reference, whose CUTLASS template picks nothing at run time): *kind = ARCQ_GEMM_KIND_PAIR (persistent
+ * CTA pairs, 256 x 256 tiles), ARCQ_GEMM_KIND_SINGLE (one CTA per 128 x tile_n tile) or
+ * ARCQ_GEMM_KIND_SPLIT_K (single-CTA tiles over *splits ranges of K; needs scratch).  *tile_n: tile
+ * width; *splits: 1 unless split.  Any output pointer may be NULL. */
+#define ARCQ_GEMM_KIND_SINGLE 0
+#define ARCQ_GEMM_KIND_SPLIT_K 1
+#define ARCQ_GEMM_KIND_PAIR 2
+int arcq_matmul_plan(int64_t M, int64_t N, int64_t K_eff, int* kind, int* tile_n, int* splits);
+
 /* No counterpart in the reference.  The split-K GEMM for callers that must not allocate device
  * memory: code that runs where an allocation would fail or stall - an inference-server plugin
  * whose enqueue hook is forbidden to call the allocator, a process whose whole device memory has

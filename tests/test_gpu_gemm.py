@@ -222,3 +222,57 @@ def test_split_k_for_skinny_problems(m, n, kq, ke):
                                   alpha, None, None, c.data_ptr(), ws.data_ptr(), 16, None) == 0
     torch.cuda.synchronize()
     assert np.array_equal(c.float().cpu().numpy(), outs[2])
+
+
+@pytest.mark.parametrize("m,n", [(1000, 4104), (4100, 4104), (1000, 28672), (16383, 4104), (300, 9992), (4100, 28672)])
+def test_cta_pair_kernel_on_ragged_tiles(m, n):
+    """Shapes that select the CTA-pair kernel (256 x 256 tiles) with M and/or N that are not multiples of
+    the tile: the last tile row has a half-empty A box and scale tile, the last tile column clips its
+    bulk stores.  Sampled rows x sampled columns (first, last, tile borders, random) against the oracle."""
+    import ctypes
+
+    from arcquant_b200 import _lib
+    from tests.helpers import sf_take_rows
+
+    ops, O = _ops(), _oracle()
+    kq, ke = 4096, 128
+    k_eff = kq + ke
+    kind = ctypes.c_int(-1)
+    assert _lib.load().arcq_matmul_plan(m, n, k_eff, ctypes.byref(kind), None, None) == 0
+    assert kind.value == _lib.GEMM_KIND_PAIR
+    dev = "cuda:0"
+    out = synth.outlier_channels(kq, kq // 100, 1)
+    x = synth.activations(m, kq, m + 2, out, device=dev)
+    w = synth.weights(n, kq, n + 3, device=dev)
+    idx = synth.reorder_index_from_stats(x[:1000].abs().amax(0)).to(dev)
+    sx, sw = ops.absmax(x) / 2688.0, ops.absmax(w) / 2688.0
+    a, sfa = ops.reorder_quantize_x((x / sx).to(torch.bfloat16), idx, ke)
+    b, sfb = ops.reorder_quantize_w((w / sw).to(torch.bfloat16), idx, ke)
+    alpha = float(sx * sw)
+    guard = torch.full((m + 8, n), 7.0, dtype=torch.bfloat16, device=dev)      # rows beyond M must stay untouched
+    c = guard[:m]
+    rc = _lib.load().arcq_matmul_nvfp4(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, k_eff, alpha,
+                                       c.data_ptr(), None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert ops.gemm_poll_error() == 0
+    assert bool((guard[m:] == 7.0).all())
+
+    def sample(size, seed):
+        edges = [0, 1, 2, 3, size - 4, size - 3, size - 2, size - 1]
+        for t in range(256, size, 256):
+            edges += [t - 1, t]
+        edges += [(size // 256) * 256 + d for d in (0, 1, 127, 128) if (size // 256) * 256 + d < size]
+        g = torch.Generator().manual_seed(seed)
+        pick = sorted(set(e for e in edges if 0 <= e < size))
+        if len(pick) > 96:
+            pick = sorted(set(pick[:8] + pick[-24:] + [pick[i] for i in torch.randint(0, len(pick), (64,), generator=g).tolist()]))
+        pick = sorted(set(pick + torch.randint(0, size, (48,), generator=g).tolist()))
+        return np.asarray(pick, dtype=np.int64)
+
+    rows, cols = sample(m, 1), sample(n, 2)
+    rt, ct = torch.from_numpy(rows).to(dev), torch.from_numpy(cols).to(dev)
+    ref = O.gemm_fast(a[rt].cpu().numpy(), sf_take_rows(sfa, rows, k_eff), b[ct].cpu().numpy(),
+                      sf_take_rows(sfb, cols, k_eff), alpha)
+    got = c[rt][:, ct].float().cpu().numpy()
+    _assert_close(got, ref)

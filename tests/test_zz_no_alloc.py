@@ -59,6 +59,19 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row(m, n, kq):
         assert np.isfinite(g_).all()
         assert np.linalg.norm(g_ - w_) <= 1e-3 * np.linalg.norm(w_)
         assert np.array_equal(g_, w_), f"call {call}"
+        # and directly against the CPU oracle's dequantised fp32 matmul, rounded to the output type
+        from oracle import oracle as O
+        ref = O.gemm_fast(a.cpu().numpy(), sfa.cpu().numpy(), b.cpu().numpy(), sfb.cpu().numpy(), alpha)
+        refb = torch.from_numpy(ref).to(torch.bfloat16).float().numpy()
+        assert np.linalg.norm(g_ - refb) <= 1e-3 * np.linalg.norm(refb), f"call {call} against the oracle"
+    # the entry point allocates nothing: free device memory is the same before and after warmed-up calls
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert L.arcq_matmul_nvfp4_static(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, k_eff,
+                                          alpha, None, None, got.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, (free0, free1)
 
 
 def test_shapes_beyond_the_block_are_refused_and_unsplit_shapes_need_none():
