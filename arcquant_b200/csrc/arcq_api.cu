@@ -218,6 +218,39 @@ int arcq_moe_combine_bf16(const void* y, const int32_t* pos, const void* weights
   return launch_moe_combine(y, pos, weights, out, tokens, hidden, top_k, (cudaStream_t)stream);
 }
 
+int arcq_absmax_grouped_bf16(const void* x, const int32_t* row_map, const int32_t* groups, int ngroups, int K, float* out,
+                             void* stream) {
+  if (ngroups < 1 || ngroups > 64 || K <= 0 || K % 8) return ARCQ_ERR_BAD_SHAPE;
+  if (!x || !groups || !out) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(x)) return ARCQ_ERR_ALIGNMENT;
+  return launch_absmax_grouped(x, row_map, groups, ngroups, K, out, (cudaStream_t)stream);
+}
+
+int arcq_reorder_quantize_x_grouped(const void* x, const int32_t* row_map, const float* scales,
+                                    const int16_t* reorder_indices, const int32_t* groups, int ngroups,
+                                    int64_t rows_bound, int KQ, int KE, int mode, uint8_t* qx, uint8_t* sfx,
+                                    void* stream) {
+  int rc = check_quant_shape(rows_bound, KQ, KE, mode);
+  if (rc != ARCQ_OK) return rc;
+  if (ngroups < 1 || ngroups > 64) return ARCQ_ERR_BAD_SHAPE;
+  if (rows_bound == 0) return ARCQ_OK;
+  if (!x || !scales || !groups || !qx || !sfx) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(qx)) return ARCQ_ERR_ALIGNMENT;
+  return launch_quantize(x, nullptr, 0.f, reorder_indices, rows_bound, KQ, KE, mode, 0, qx, sfx, (cudaStream_t)stream,
+                         scales, groups, ngroups, row_map);
+}
+
+int arcq_matmul_nvfp4_grouped(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                              int64_t M_bound, int64_t N, int64_t K_eff, const int32_t* tile_group, int ngroups,
+                              const float* alpha_a, const float* alpha_b, void* C, void* stream) {
+  int rc = check_gemm(A, B, SFA, SFB, M_bound, N, K_eff, C);
+  if (rc != ARCQ_OK || M_bound == 0) return rc;
+  if (ngroups < 1 || N % 128 || N * (int64_t)ngroups > ((int64_t)1 << 30)) return ARCQ_ERR_BAD_SHAPE;
+  if (!tile_group || !alpha_a) return ARCQ_ERR_NULL_POINTER;
+  return launch_gemm_grouped(A, B, SFA, SFB, M_bound, N, K_eff, tile_group, ngroups, alpha_a, alpha_b, C,
+                             (cudaStream_t)stream);
+}
+
 int arcq_absmax_bf16(const void* x, int64_t n, float* out, int accumulate, void* stream) {
   if (n < 0) return ARCQ_ERR_BAD_SHAPE;
   if (!out || (n > 0 && !x)) return ARCQ_ERR_NULL_POINTER;

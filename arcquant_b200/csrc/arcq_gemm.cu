@@ -23,7 +23,6 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "arcq_internal.h"
@@ -69,7 +68,6 @@ struct GemmParams {
   int natoms;         // ceil((K_eff/16)/4): scale atoms per 128-row tile
   int tiles_m, tiles_n;
   int sfb_tiles;      // ceil(N/128): 128-row scale tiles of B that exist
-  int dbg;            // timing experiments only (ARCQ_GEMM_DBG): 1 = skip scale copies, 2 = skip MMAs
   float* ws;          // split-K: fp32 partial sums [splits][M][N] (scratch), else nullptr
   int splits;         // K is cut into this many ranges of whole stages (1 = no split)
 };
@@ -291,7 +289,6 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint32_t sfa_s = b_s + C::B_BYTES, sfb_s = sfa_s + C::SFA_BYTES;
           const uint32_t t_sfa = tmem_sf + (it & 1u) * C::SF_COLS;
           const uint32_t t_sfb = t_sfa + KSTEPS * 4;
-          if (!(p.dbg & 1))
           for (int k = 0; k < nk; ++k) {
             tc_cp_sf(t_sfa + k * 4, smem_desc(sfa_s + k * ATOM, 128, LAYOUT_NONE));
 #pragma unroll
@@ -299,7 +296,6 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               tc_cp_sf(t_sfb + k * 4 * C::NB + a * 4,
                        smem_desc(sfb_s + a * (KSTEPS * ATOM) + k * ATOM, 128, LAYOUT_NONE));
           }
-          if (!(p.dbg & 2))
           for (int k = 0; k < nk; ++k) {
             const uint64_t adesc = smem_desc(a_s + k * 32, 1024, LAYOUT_SW128);
             const uint64_t bdesc = smem_desc(b_s + k * 32, 1024, LAYOUT_SW128);
@@ -343,7 +339,7 @@ arcq_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               if (col + v * 4 < p.N)   // N is a multiple of 8, so groups of four are in or out
                 *reinterpret_cast<uint4*>(wrow + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
           }
-        } else if (row < p.M && col < p.N && !(p.dbg & 4)) {
+        } else if (row < p.M && col < p.N) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             if (col + v * 8 < p.N) {   // N is a multiple of 8: whole 16-byte pieces are in or out
@@ -463,9 +459,13 @@ struct Gemm2Params {
   int ksteps_total;   // K_eff / 64
   int natoms;         // scale atoms per 128-row tile
   int tiles_m, tiles_n;   // 256 x 256 tiles
-  int dbg;                // timing experiments only (ARCQ_GEMM_DBG)
   int tma_store;          // output leaves through shared memory and bulk tensor stores (else: per-thread stores)
   int group_m;            // tile rows per band of the tile order (see pair_tile_coords)
+  // Grouped problems (one launch over several weight matrices stacked in B): tile_group[tm] = which
+  // matrix the 256-row tile tm of A multiplies, or a negative number for a tile that holds no rows
+  // (device memory: the host never learns the split).  Matrix g owns rows [g*N, (g+1)*N) of B and of
+  // its scales, and alpha_a[g] * alpha_b[g].
+  const int* tile_group;
 };
 
 // Tile order of the persistent pairs: bands of group_m tile rows, and inside a band column by column.
@@ -480,15 +480,6 @@ __device__ __forceinline__ void pair_tile_coords(int tile, const Gemm2Params& p,
   tn = in_band / rows;
   tm = first + (in_band - tn * rows);
 }
-
-#ifdef ARCQ_GEMM_TRACE
-// Timing experiments only (never compiled into the library): cycle stamps of the first pair's
-// leader CTA, one row per pipeline event, one column per K stage.
-__device__ long long g_trace[8][2048];
-#define ARCQ_TRACE(k, it) do { if (cluster_id == 0 && rank == 0 && (it) < 2048u) g_trace[k][it] = clock64(); } while (0)
-#else
-#define ARCQ_TRACE(k, it) do { } while (0)
-#endif
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C2_THREADS, 1)
 arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -551,16 +542,16 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         int tm, tn;
         pair_tile_coords(tile, p, tm, tn);
+        int grp = 0;
+        if (p.tile_group != nullptr) { grp = __ldg(p.tile_group + tm); if (grp < 0) continue; }
         const int row_a = tm * 256 + (int)rank * 128;        // this CTA's rows of A (and of the output)
-        const int row_b = tn * 256 + (int)rank * 128;        // this CTA's rows of B (half of the N tile)
+        const int row_b = grp * p.N + tn * 256 + (int)rank * 128;   // this CTA's rows of B (half of the N tile)
         const int sfa_tile = tm * 2 + (int)rank;             // 128-row scale tiles
-        const int sfb_tile = tn * 2;
+        const int sfb_tile = grp * (p.N >> 7) + tn * 2;
         for (int ks = 0; ks < kstages; ++ks, ++it) {
           const int s = it % C2_STAGES;
           const uint32_t ph = (it / C2_STAGES) & 1u;
-          ARCQ_TRACE(6, it);
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
-          ARCQ_TRACE(0, it);
           const uint32_t st = base + s * C2_STAGE_BYTES;
           const uint32_t lbar = full_bar(s) & PEER_BIT_MASK;
           if (rank == 0) mbar_expect_tx(full_bar(s), AB_TX);
@@ -583,45 +574,56 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       constexpr uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tile_it) {
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        if (p.tile_group != nullptr) {
+          int tm, tn;
+          pair_tile_coords(tile, p, tm, tn);
+          if (__ldg(p.tile_group + tm) < 0) continue;      // a tile without rows: every role skips it
+        }
         if (!mbar_wait(tmem_empty_bar, (tile_it & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         for (int ks = 0; ks < kstages; ++ks, ++it) {
           const int s = it % C2_STAGES;
           const uint32_t ph = (it / C2_STAGES) & 1u;
           if (!mbar_wait(sf_ready_bar(s), ph, abort_flag)) { ok = false; break; }
-          ARCQ_TRACE(3, it);
           if (!mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
-          ARCQ_TRACE(4, it);
           tc_fence_after();
           const int nk = min(KSTEPS, p.ksteps_total - ks * KSTEPS);
           const uint32_t st = base + s * C2_STAGE_BYTES;
           const uint32_t a_s = st, b_s = st + C2_A_BYTES;
           const uint32_t t_sfa = tmem_sf + s * C2_SF_COLS;
           const uint32_t t_sfb = t_sfa + KSTEPS * 4;
-          if (!(p.dbg & 2))
           for (int k = 0; k < nk; ++k) {
             const uint64_t adesc = smem_desc(a_s + k * 32, 1024, LAYOUT_SW128);
             const uint64_t bdesc = smem_desc(b_s + k * 32, 1024, LAYOUT_SW128);
             tc_mma_nvf4_pair(tmem_base, adesc, bdesc, idesc, t_sfa + k * 4, t_sfb + k * 8, (ks | k) ? 1u : 0u);
           }
           tc_commit_pair(empty_bar(s));
-          ARCQ_TRACE(5, it);
         }
         if (ok) tc_commit_pair(tmem_full_bar);
+        ++tile_it;
       }
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue (both CTAs)
     const int quad = warp & 3;
     float alpha = p.alpha;
-    if (p.alpha_a) alpha *= __ldg(p.alpha_a);
-    if (p.alpha_b) alpha *= __ldg(p.alpha_b);
+    if (p.tile_group == nullptr) {
+      if (p.alpha_a) alpha *= __ldg(p.alpha_a);
+      if (p.alpha_b) alpha *= __ldg(p.alpha_b);
+    }
     uint32_t tile_it = 0;
     bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tile_it) {
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
       pair_tile_coords(tile, p, tm, tn);
+      if (p.tile_group != nullptr) {
+        const int grp = __ldg(p.tile_group + tm);
+        if (grp < 0) continue;
+        alpha = p.alpha;
+        if (p.alpha_a) alpha *= __ldg(p.alpha_a + grp);
+        if (p.alpha_b) alpha *= __ldg(p.alpha_b + grp);
+      }
       ok = mbar_wait(tmem_full_bar, tile_it & 1u, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -655,7 +657,7 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // columns >= N themselves, and keep the load/store pipe free for the scale warps.
         const int row0 = tm * 256 + (int)rank * 128 + quad * 32;
         const uint32_t cst = cstage_base + (uint32_t)quad * 8192u;
-        if (row0 < p.M && !(p.dbg & 4)) {
+        if (row0 < p.M) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging is free again
@@ -686,13 +688,14 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
           }
         }
-      } else if (row < p.M && !(p.dbg & 4)) {
+      } else if (row < p.M) {
 #pragma unroll
         for (int v = 0; v < 32; ++v) {          // 32 x 16 bytes = this row's 256 columns
           if (col0 + v * 8 < p.N)
             *reinterpret_cast<uint4*>(crow + col0 + v * 8) = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
         }
       }
+      ++tile_it;
     }
     // the last boxes must have left shared memory (and reached global memory) before the CTA goes
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -706,13 +709,17 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint32_t it = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      if (p.tile_group != nullptr) {
+        int tm, tn;
+        pair_tile_coords(tile, p, tm, tn);
+        if (__ldg(p.tile_group + tm) < 0) continue;
+      }
       for (int ks = 0; ks < kstages; ++ks, ++it) {
         const int s = it % C2_STAGES;
         const uint32_t ph = (it / C2_STAGES) & 1u;
         ok = mbar_wait(sf_full_bar(s), ph, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (quad == 0 && lane == 0) ARCQ_TRACE(1, it);
         const uint4* sf = reinterpret_cast<const uint4*>(base_ptr + s * C2_STAGE_BYTES + C2_A_BYTES + C2_B_BYTES);
         const uint32_t taddr = tmem_sf + s * C2_SF_COLS + ((uint32_t)(quad * 32) << 16);
         // TMEM columns: [SFA k0..k3 (4 each)] [SFB k0: tile0, tile1][k1: ...] ...
@@ -737,7 +744,6 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_leader(sf_ready_bar(s));
-        if (quad == 0 && lane == 0) ARCQ_TRACE(2, it);
       }
     }
   }
@@ -849,8 +855,11 @@ int make_c_map(CUtensorMap* map, const void* ptr, int64_t M, int64_t N) {
   return ARCQ_OK;
 }
 
+// ngroups > 1: B and SFB hold `ngroups` matrices of N rows each, tile_group says which one every
+// 256-row tile of A multiplies (see Gemm2Params).
 int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M, int64_t N,
-                int64_t K_eff, const GemmParams& gp, int num_sms, cudaStream_t stream) {
+                int64_t K_eff, const GemmParams& gp, int num_sms, cudaStream_t stream, const int* tile_group = nullptr,
+                int ngroups = 1) {
   Gemm2Params p;
   p.c = gp.c;
   p.alpha_a = gp.alpha_a;
@@ -862,25 +871,26 @@ int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   p.natoms = gp.natoms;
   p.tiles_m = (int)((M + 255) / 256);
   p.tiles_n = (int)((N + 255) / 256);
-  p.dbg = gp.dbg;
   p.tma_store = 1;
-  if (const char* e = getenv("ARCQ_GEMM_TMA_STORE")) p.tma_store = atoi(e) != 0;   // timing experiments
   // Column by column unless A alone overflows half of L2: then bands of 32 tile rows, whose A rows
   // (plus all of B) stay resident while the band lasts.  Measured on B200, the order makes no
   // difference beyond run-to-run noise for operands that fit.
   p.group_m = (double)M * (double)K_eff / 2.0 > 64e6 ? 32 : p.tiles_m;
-  if (const char* e = getenv("ARCQ_GEMM_GROUP_M")) p.group_m = atoi(e) > 0 ? atoi(e) : p.tiles_m;
+  // grouped: tile rows of one matrix are neighbours, so narrow bands keep a strip of B shared by the
+  // pairs that are in flight together
+  if (tile_group != nullptr) p.group_m = 4;
   if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
+  p.tile_group = tile_group;
   CUtensorMap ma, mb, msa, msb, mc;
   int rc = make_c_map(&mc, gp.c, M, N);
   if (rc != ARCQ_OK) return rc;
   rc = make_operand_map(&ma, A, M, K_eff / 2, 128);
   if (rc != ARCQ_OK) return rc;
-  rc = make_operand_map(&mb, B, N, K_eff / 2, 128);
+  rc = make_operand_map(&mb, B, N * ngroups, K_eff / 2, 128);
   if (rc != ARCQ_OK) return rc;
   rc = make_sf_map(&msa, SFA, ((M + 127) / 128) * (int64_t)gp.natoms);
   if (rc != ARCQ_OK) return rc;
-  rc = make_sf_map(&msb, SFB, ((N + 127) / 128) * (int64_t)gp.natoms);
+  rc = make_sf_map(&msb, SFB, ((N * ngroups + 127) / 128) * (int64_t)gp.natoms);
   if (rc != ARCQ_OK) return rc;
   auto kern = arcq_gemm2_kernel;
   ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C2_SMEM_BYTES));
@@ -916,15 +926,6 @@ static void plan_splitk(int64_t M, int64_t N, int64_t K_eff, int num_sms, int* b
   const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn);
   const int kstages = (int)((K_eff / 64 + KSTEPS - 1) / KSTEPS);
   int splits = 1;
-  static const int bn_env = [] { const char* e = getenv("ARCQ_GEMM_SK_BN"); return e ? atoi(e) : 0; }();
-  static const int sp_env = [] { const char* e = getenv("ARCQ_GEMM_SK_SPLITS"); return e ? atoi(e) : 0; }();
-  if (bn_env && sp_env) {   // tuning knob: force a tile width and a split count
-    splits = allow_split ? sp_env : 1;
-    while (splits > 1 && (splits - 1) * ((kstages + splits - 1) / splits) >= kstages) --splits;
-    *bn_out = bn_env;
-    *splits_out = splits;
-    return;
-  }
   if (tiles_m == 1) {
     // One row of tiles (M <= 128: weight streaming).  The K loop is a serial chain of stages whose
     // latency, not bandwidth, sets the time; splitting K shortens the chain at the price of a second
@@ -960,6 +961,25 @@ static void plan_splitk(int64_t M, int64_t N, int64_t K_eff, int num_sms, int* b
   }
   *bn_out = bn;
   *splits_out = splits;
+}
+
+int launch_gemm_grouped(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                        int64_t N, int64_t K_eff, const int* tile_group, int ngroups, const float* alpha_a,
+                        const float* alpha_b, void* Cout, cudaStream_t stream) {
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  GemmParams p = {};
+  p.c = static_cast<__nv_bfloat16*>(Cout);
+  p.alpha_a = alpha_a;
+  p.alpha_b = alpha_b;
+  p.alpha = 1.0f;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.ksteps_total = (int)(K_eff / 64);
+  p.natoms = (int)((K_eff / 16 + 3) / 4);
+  p.splits = 1;
+  return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream, tile_group, ngroups);
 }
 
 size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K_eff) {
@@ -1014,26 +1034,19 @@ int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   p.tiles_m = (int)((M + BM - 1) / BM);
   p.tiles_n = 0;
   p.sfb_tiles = (int)((N + 127) / 128);
-  p.dbg = 0;
-  if (const char* e = getenv("ARCQ_GEMM_DBG")) p.dbg = atoi(e);
   p.ws = nullptr;
   p.splits = 1;
 
   // Widest tile that still gives every SM work; narrow tiles for skinny problems.  Partial tiles
-  // are clipped by the TMA box (zero fill) and by the store guards.  ARCQ_GEMM_BN=32|64|128|256
-  // overrides the choice (tuning / testing knob).
+  // are clipped by the TMA box (zero fill) and by the store guards.
   int bn = 256;
   while (bn > 64 && (long long)p.tiles_m * ((N + bn - 1) / bn) < di.num_sms) bn >>= 1;
-  if (const char* e = getenv("ARCQ_GEMM_BN")) {
-    int v = atoi(e);
-    if (v == 64 || v == 128 || v == 256) bn = v;
-  }
 
   if (use_pair_kernel(M, N, di.num_sms)) return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream);
 
   // Skinny problems (few output tiles, long K): split K over otherwise idle SMs when the caller
   // provided scratch for the fp32 partial sums.
-  if (!getenv("ARCQ_GEMM_BN")) {
+  {
     int bn2, splits;
     plan_splitk(M, N, K_eff, di.num_sms, &bn2, &splits, workspace != nullptr);
     if (splits > 1 && workspace_bytes < (size_t)splits * (size_t)M * (size_t)N * sizeof(float))
@@ -1117,9 +1130,3 @@ int gemm_poll_error() {
 }
 
 }  // namespace arcq
-
-#ifdef ARCQ_GEMM_TRACE
-extern "C" int arcq_debug_trace_read(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, arcq::g_trace, sizeof(long long) * 8 * 2048);
-}
-#endif

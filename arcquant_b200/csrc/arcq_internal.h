@@ -28,7 +28,9 @@ int get_device_info(DeviceInfo* out);
 // in arcq_api.cu.
 int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* idx, int64_t rows, int KQ,
                     int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream,
-                    const float* scale = nullptr);   // scale (device): x is divided by it first; plain x only
+                    const float* scale = nullptr,    // scale (device): x is divided by it first; plain x only
+                    const int* groups = nullptr, int ngroups = 0,   // runs of rows with their own order and scale
+                    const int* row_map = nullptr);                  // input row of every output row
 int launch_absmax(const void* x, int64_t n, float* out, int accumulate, cudaStream_t stream);
 // workspace (may be null): scratch for split-K partial sums, see gemm_workspace_bytes().
 int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
@@ -47,6 +49,13 @@ int launch_rope(void* x, const float* cos_t, const float* sin_t, int64_t tokens,
 int launch_silu_mul(const void* gu, void* out, int64_t tokens, int F, float* amax, cudaStream_t stream);
 int launch_moe_combine(const void* y, const int* pos, const void* w, void* out, int64_t tokens, int hidden, int k,
                        cudaStream_t stream);
+// One launch over `ngroups` weight matrices stacked in B (each N rows): tile_group (device) names the
+// matrix of every 256-row tile of A, alpha_a / alpha_b are per-matrix arrays.
+int launch_gemm_grouped(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                        int64_t N, int64_t K_eff, const int* tile_group, int ngroups, const float* alpha_a,
+                        const float* alpha_b, void* C, cudaStream_t stream);
+int launch_absmax_grouped(const void* x, const int* row_map, const int* groups, int ngroups, int K, float* out,
+                          cudaStream_t stream);
 int gemm_poll_error();
 // Same for the bounded waits of the warp-specialised quantizer.
 int quant_poll_error();

@@ -191,7 +191,46 @@ __global__ void arcq_moe_combine_kernel(const uint16_t* __restrict__ y, const in
   }
 }
 
+// Per-run max|x| of grouped rows: run e holds rows [groups[e], groups[e] + groups[ngroups + e]) of the
+// (padded) row numbering; row r of that numbering is input row row_map[r] (or r).  One warp per row.
+__global__ void arcq_absmax_grouped_kernel(const uint16_t* __restrict__ x, const int* __restrict__ row_map,
+                                           const int* __restrict__ groups, int ngroups, int K, unsigned int* out) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int last = __ldg(groups + ngroups - 1) + __ldg(groups + 2 * ngroups - 1);   // end of the last run
+  int e = 0;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < last; r += warps) {
+    while (e + 1 < ngroups && r >= __ldg(groups + e + 1)) ++e;
+    if (r >= __ldg(groups + e) + __ldg(groups + ngroups + e)) continue;        // padding between runs
+    const uint4* row = reinterpret_cast<const uint4*>(x + (size_t)(row_map ? __ldg(row_map + r) : r) * (size_t)K);
+    uint32_t m = 0;
+    for (int v = lane; v < (K >> 3); v += 32) {
+      const uint4 a = __ldg(row + v);
+      asm("max.u16x2 %0, %0, %1;" : "+r"(m) : "r"(a.x & 0x7fff7fffu));
+      asm("max.u16x2 %0, %0, %1;" : "+r"(m) : "r"(a.y & 0x7fff7fffu));
+      asm("max.u16x2 %0, %0, %1;" : "+r"(m) : "r"(a.z & 0x7fff7fffu));
+      asm("max.u16x2 %0, %0, %1;" : "+r"(m) : "r"(a.w & 0x7fff7fffu));
+    }
+    uint32_t v = max(m & 0xffffu, m >> 16);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, d));
+    if (lane == 0) atomicMax(out + e, v << 16);   // non-negative floats order like their bit patterns
+  }
+}
+
 }  // namespace
+
+int launch_absmax_grouped(const void* x, const int* row_map, const int* groups, int ngroups, int K, float* out,
+                          cudaStream_t stream) {
+  ARCQ_CUDA_TRY(cudaMemsetAsync(out, 0, sizeof(float) * ngroups, stream));
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  arcq_absmax_grouped_kernel<<<(unsigned)di.num_sms * 8, 256, 0, stream>>>(
+      static_cast<const uint16_t*>(x), row_map, groups, ngroups, K, reinterpret_cast<unsigned int*>(out));
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
 
 int launch_moe_combine(const void* y, const int* pos, const void* w, void* out, int64_t tokens, int hidden, int k,
                        cudaStream_t stream) {

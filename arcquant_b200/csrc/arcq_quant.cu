@@ -51,6 +51,13 @@ struct QuantParams {
   int is_weight;  // residual slot = copy of the main codes
   float eps;
   const float* scale;   // warp-specialised plain kernel only: x is divided by *scale (device) first, or nullptr
+  // Grouped rows (warp-specialised kernel only): the rows form `ngroups` runs, run e starting at output
+  // row groups[e] with groups[ngroups + e] rows (device memory, so the host never learns the sizes);
+  // run e uses the channel order idx + e*KQ and the scale scale[e].  row_map (or nullptr): input row of
+  // every output row.
+  const int* groups;
+  int ngroups;
+  const int* row_map;
 };
 
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
@@ -728,7 +735,31 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x;
   const int KQ = p.KQ, G = p.G;
-  const uint32_t rows = (uint32_t)p.rows, npairs = (uint32_t)p.npairs;
+  uint32_t rows = (uint32_t)p.rows, npairs = (uint32_t)p.npairs;
+  // This CTA is number `cta` of the `stride` CTAs that share a run of rows: the whole input, or - with
+  // grouped rows - run e = blockIdx.x % ngroups, whose rows start at output row `row_base`.
+  uint32_t cta = blockIdx.x, stride = gridDim.x, row_base = 0;
+  const int16_t* idx_g = p.idx;
+  const float* scale_g = p.scale;
+  if (p.groups != nullptr) {
+    // (the table may have been written by the previous kernel of the stream)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t ng = (uint32_t)p.ngroups, e = blockIdx.x % ng;
+    cta = blockIdx.x / ng;
+    stride = (gridDim.x - e + ng - 1) / ng;
+    row_base = (uint32_t)__ldg(p.groups + e);
+    rows = (uint32_t)__ldg(p.groups + ng + e);
+    npairs = (rows + 1) >> 1;
+    if (idx_g) idx_g += (size_t)e * (size_t)KQ;
+    if (scale_g) scale_g += e;
+  }
+  if (cta >= npairs) return;   // (whole CTA: nothing was set up yet)
+  const int* row_map = p.row_map;
+  // input row of output row r of this run
+  auto in_row = [&](uint32_t r) -> const uint16_t* {
+    const uint32_t gr = row_base + r;
+    return p.x + (size_t)(row_map ? (uint32_t)__ldg(row_map + gr) : gr) * (size_t)KQ;
+  };
 
   // shared layout: [barriers, abort flag: 384 B][offsets][partial sums, rstd][gather ring][raw ring]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
@@ -755,7 +786,6 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   const uint32_t rawe0 = raw0 + 8 * R, psr0 = rawe0 + 8 * R, rsr0 = psr0 + 8 * 4;
 
   asm volatile("griddepcontrol.launch_dependents;");   // the next kernel of the stream may be set up now
-  const uint32_t stride = gridDim.x;
   // Bulk copies of the rows of `unit` into raw stage `rs` (one thread).
   auto issue = [&](uint32_t unit, uint32_t rs) {
     if (unit >= npairs) return;
@@ -763,25 +793,24 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     const bool has1 = (r0 + 1) < rows;
     const uint32_t bar = raw0 + 8 * rs;
     const uint32_t dst = smem_addr(raw + (size_t)rs * stage_bytes);
-    const uint16_t* src = p.x + (size_t)r0 * (size_t)KQ;
     mbar_expect_tx(bar, has1 ? 2 * row_in_bytes : row_in_bytes);
-    bulk_load(dst, src, row_in_bytes, bar);
-    if (has1) bulk_load(dst + row_in_bytes, src + KQ, row_in_bytes, bar);
+    bulk_load(dst, in_row(r0), row_in_bytes, bar);
+    if (has1) bulk_load(dst + row_in_bytes, in_row(r0 + 1), row_in_bytes, bar);
   };
   // WIDE: the raw ring holds half pairs (the same half of the channels of both rows), so that the
   // copies of the next half overlap the work on this one although only ~1.5 pairs of raw rows fit.
   // Half u of this CTA is half u & 1 of its pair u >> 1.
   auto issue_half = [&](uint32_t u, uint32_t rs) {
-    const uint32_t unit = blockIdx.x + (u >> 1) * stride;
+    const uint32_t unit = cta + (u >> 1) * stride;
     if (unit >= npairs) return;
     const uint32_t r0 = 2 * unit, hbytes = row_in_bytes >> 1;
     const bool has1 = (r0 + 1) < rows;
     const uint32_t bar = raw0 + 8 * rs;
     const uint32_t dst = smem_addr(raw + (size_t)rs * row_in_bytes);
-    const uint16_t* src = p.x + (size_t)r0 * (size_t)KQ + (size_t)(u & 1u) * (size_t)(KQ >> 1);
+    const size_t hoff = (size_t)(u & 1u) * (size_t)(KQ >> 1);
     mbar_expect_tx(bar, has1 ? 2 * hbytes : hbytes);
-    bulk_load(dst, src, hbytes, bar);
-    if (has1) bulk_load(dst + hbytes, src + KQ, hbytes, bar);
+    bulk_load(dst, in_row(r0) + hoff, hbytes, bar);
+    if (has1) bulk_load(dst + hbytes, in_row(r0 + 1) + hoff, hbytes, bar);
   };
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -804,7 +833,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t r = 0; r < (uint32_t)R; ++r) {
       if (WIDE) issue_half(r, r);
-      else issue(blockIdx.x + r * stride, r);
+      else issue(cta + r * stride, r);
     }
   }
   // Everything before this line touched shared memory only; global memory may still be written by
@@ -817,9 +846,9 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     if (WIDE) offs16[(((i >> 3) * G + g) << 3) | (i & 7)] = (uint16_t)word_offset((uint32_t)c);
     else offs32[(((i >> 2) * G + g) << 2) | (i & 3)] = word_offset((uint32_t)c);
   };
-  if (p.idx && (reinterpret_cast<uintptr_t>(p.idx) & 15u) == 0) {
+  if (idx_g && (reinterpret_cast<uintptr_t>(idx_g) & 15u) == 0) {
     // eight indices per 128-bit load: one round trip to global memory for rows of up to 8192 channels
-    const uint4* idx4 = reinterpret_cast<const uint4*>(p.idx);
+    const uint4* idx4 = reinterpret_cast<const uint4*>(idx_g);
     for (int v = tid; v < (KQ >> 3); v += blockDim.x) {
       const uint4 w = __ldg(idx4 + v);
       const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
@@ -830,7 +859,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       }
     }
   } else {
-    for (int j = tid; j < KQ; j += blockDim.x) put(j, p.idx ? (int)p.idx[j] : j);
+    for (int j = tid; j < KQ; j += blockDim.x) put(j, idx_g ? (int)idx_g[j] : j);
   }
   __syncthreads();
 
@@ -846,7 +875,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     const uint32_t NP = (uint32_t)npteams;
     const int c0 = ptid, c1 = ptid + npt;   // this thread's 16-byte chunks
     if (RMS) { psum += (size_t)pteam * 4 * npt; rstd_s += 4 * pteam; }
-    const uint32_t n = (npairs - blockIdx.x + stride - 1) / stride;   // row pairs of this CTA
+    const uint32_t n = (npairs - cta + stride - 1) / stride;   // row pairs of this CTA
     const uint32_t nt = n > (uint32_t)pteam ? (n - pteam + NP - 1) / NP : 0;   // pairs of this team
     const uint32_t psr = psr0 + 16 * pteam, rsr = rsr0 + 16 * pteam;           // this team's barrier pairs
     if (RMS && ptid >= npt) {
@@ -888,7 +917,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
             }
             if (!ok) break;
           }
-          if (next < n) { issue(blockIdx.x + next * stride, freed % R); next += NP; }
+          if (next < n) { issue(cta + next * stride, freed % R); next += NP; }
         }
         if (!ok) {
           // Giving up with bulk copies possibly in flight: wait (bounded) for those started here, so
@@ -966,7 +995,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       const int hc = KQ >> 4;   // 16-byte chunks of half a row
       float sc = 1.0f, rsc = 1.0f, qlo = 0.f;
       if (SCALED) {
-        sc = __uint_as_float(pack_bf16x2_rn(__ldg(p.scale), 0.f) << 16);   // (the divisor as bf16, see below)
+        sc = __uint_as_float(pack_bf16x2_rn(__ldg(scale_g), 0.f) << 16);   // (the divisor as bf16, see below)
         rsc = __frcp_rn(sc);
         qlo = div_guard(sc);
       }
@@ -975,7 +1004,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       landed = 0;
       for (uint32_t u = 0; u < nu; ++u) {
         const uint32_t it = u >> 1, h = u & 1u;
-        const uint32_t unit = blockIdx.x + it * stride;
+        const uint32_t unit = cta + it * stride;
         const bool has1 = (2 * unit + 1) < rows;
         if (!failed && !mbar_wait(raw0 + 8 * (u % R), (u / R) & 1u, abort_flag)) failed = true;
         if (!failed) landed = u + 1;
@@ -1018,12 +1047,12 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       float sc = 1.0f, rsc = 1.0f, qlo = 0.f;
       if (SCALED) {
         // torch's CUDA kernel for (bf16 tensor) / (fp32 scalar tensor) loads the divisor as bf16
-        sc = __uint_as_float(pack_bf16x2_rn(__ldg(p.scale), 0.f) << 16);
+        sc = __uint_as_float(pack_bf16x2_rn(__ldg(scale_g), 0.f) << 16);
         rsc = __frcp_rn(sc);
         qlo = div_guard(sc);
       }
       for (uint32_t it = 0; it < n; ++it) {
-        const uint32_t unit = blockIdx.x + it * stride;
+        const uint32_t unit = cta + it * stride;
         const bool has1 = (2 * unit + 1) < rows;
         if (!failed && !mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) failed = true;
         if (!failed) landed = it + 1;
@@ -1083,7 +1112,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
           fill_stage(j, a0, a1, b0, b1, rstd);
         }
         if (m < nt) {
-          const uint32_t unit = blockIdx.x + it * stride;
+          const uint32_t unit = cta + it * stride;
           const bool has1 = (2 * unit + 1) < rows;
           if (!mbar_wait(raw0 + 8 * (it % R), (it / R) & 1u, abort_flag)) break;
           read_raw(it, has1, a0, a1, b0, b1);
@@ -1132,10 +1161,10 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     int slot = warp;   // which 32 groups this warp takes; rotates so the critical groups move around
     // (npairs < 2^29 and at most a few grid strides beyond it: 32-bit unit numbers do not wrap)
     uint32_t it = (uint32_t)team;
-    for (uint32_t unit = blockIdx.x + it * stride; unit < npairs; unit += (uint32_t)nteams * stride, it += (uint32_t)nteams) {
+    for (uint32_t unit = cta + it * stride; unit < npairs; unit += (uint32_t)nteams * stride, it += (uint32_t)nteams) {
       const uint32_t s = it % S, ph = (it / S) & 1u;
-      const uint32_t r0 = 2 * unit;
-      const bool has1 = (r0 + 1) < rows;
+      const bool has1 = (2 * unit + 1) < rows;
+      const uint32_t r0 = row_base + 2 * unit;     // output row (runs start on even rows)
       uint8_t* q0 = p.q + (size_t)r0 * row_bytes;
       // 128-row tile, then 16 bytes per row % 32 and 4 per (row / 32) % 4; row 1 of the pair is the
       // next row of the same 32-row run
@@ -1144,7 +1173,13 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       uint8_t* sf1 = has1 ? sf0 + 16 : sf0;
       const uint8_t* buf = stages + (size_t)s * stage_bytes;
       if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) break;
-      for (int g = slot * 32 + lane; g < G; g += nct) {
+      // Whole warps walk the groups: a lane beyond the last group (rows whose group count is not a
+      // multiple of 32) gathers the last group again and stores nothing; a warp without any group for
+      // this pair still hands the stage back.
+      bool released = false;
+      for (int gb = slot * 32; gb < G; gb += nct) {
+        const bool live = gb + lane < G;
+        const int g = live ? gb + lane : G - 1;
         uint32_t w[16];
         if (WIDE) {
           const uint4* op = reinterpret_cast<const uint4*>(offs16) + g;
@@ -1169,12 +1204,14 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
             w[4 * v + 3] = *reinterpret_cast<const uint32_t*>(buf + o.w);
           }
         }
-        if (g + nct >= G) {   // last group of this thread: the stage can be refilled (warp-uniform)
+        if (gb + nct >= G) {   // last group of this warp: the stage can be refilled
           __syncwarp();
           if (lane == 0) mbar_arrive(empty0 + 8 * s);
+          released = true;
         }
-        quantize_group_pair_ws(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1);
+        if (live) quantize_group_pair_ws(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1);
       }
+      if (!released && lane == 0) mbar_arrive(empty0 + 8 * s);
       slot = slot + 1 == ncw ? 0 : slot + 1;
     }
   }
@@ -1217,7 +1254,8 @@ int launch_ws(const QuantParams& p, int nct, int npt, int nteams, int npteams, s
   }
   if (occ < 1) return ARCQ_ERR_UNSUPPORTED_K;
   long long grid = (long long)di.num_sms * occ;
-  if (grid > p.npairs) grid = p.npairs;
+  if (p.groups == nullptr && grid > p.npairs) grid = p.npairs;
+  if (p.groups != nullptr && grid < p.ngroups) return ARCQ_ERR_BAD_SHAPE;   // every run needs a CTA
   // Programmatic dependent launch: the grid may be set up while the previous kernel of the stream is
   // still draining; the kernel itself waits (griddepcontrol.wait) before it touches global memory.
   static const int pdl_env = [] { const char* e = getenv("ARCQ_QUANT_PDL"); return e ? atoi(e) : 1; }();
@@ -1254,7 +1292,8 @@ int launch_variant(const QuantParams& p, int nt, size_t smem, const DeviceInfo& 
 }  // namespace
 
 int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* idx, int64_t rows, int KQ,
-                    int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream, const float* scale) {
+                    int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream, const float* scale,
+                    const int* groups, int ngroups, const int* row_map) {
   if (rows == 0) return ARCQ_OK;
   DeviceInfo di;
   int rc = get_device_info(&di);
@@ -1278,6 +1317,9 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   p.is_weight = is_weight;
   p.eps = eps;
   p.scale = scale;
+  p.groups = groups;
+  p.ngroups = ngroups;
+  p.row_map = row_map;
 
   const bool rms = gamma != nullptr;
   int nt, cpt;
@@ -1303,7 +1345,8 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   static const int nct_env = [] { const char* e = getenv("ARCQ_QUANT_NCT"); return e ? atoi(e) : 0; }();
   const bool gamma_ok = !rms || (reinterpret_cast<uintptr_t>(gamma) & 15u) == 0;   // read with 128-bit loads
   const bool wide = p.G > 512;
-  if (gamma_ok && p.G % 32 == 0 && p.G >= 64 && rows < (1LL << 30) &&
+  // (RMSNorm: one producer per 16-channel group, in whole warps - the reference's summation order)
+  if (gamma_ok && p.G >= 32 && (!rms || (p.G % 32 == 0 && p.G >= 64)) && rows < (1LL << 30) &&
       (wide ? (!rms && p.G <= 1024) : true)) {
     const size_t stage = (size_t)KQ * 4;
     if (wide) {
@@ -1331,11 +1374,12 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
     } else {
       // Consumer teams of 128 threads (two groups per thread at hidden 4096) were measured faster than
       // teams of 256: more row pairs in flight for the same number of warps.
-      int nct = p.G < 128 ? p.G : 128;
-      if (nct_env >= 32 && nct_env % 32 == 0 && nct_env <= p.G && nct_env <= 256) nct = nct_env;
+      const int g32 = (p.G + 31) / 32 * 32;   // threads of a role are whole warps
+      int nct = g32 < 128 ? g32 : 128;
+      if (nct_env >= 32 && nct_env % 32 == 0 && nct_env <= g32 && nct_env <= 256) nct = nct_env;
       // producers: two 16-byte chunks of each row per thread (the RMSNorm summation order needs exactly
       // that); with the division by the tensor's scale, at least 512 of them share the arithmetic
-      const int npt = (p.scale && p.G < 512) ? 512 : p.G;
+      const int npt = (p.scale && p.G < 512) ? 512 : g32;
       // One CTA per SM, up to 1024 threads.  Plain: one producer team (it only moves data).  RMSNorm: two
       // producer teams, each with three helper warps.  The rest, up to three teams, are consumers.
       const int ptt = npt + (rms ? 96 : 0);   // threads of a producer team
@@ -1378,7 +1422,8 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
       }
     }
   }
-  if (p.scale) return ARCQ_ERR_UNSUPPORTED_K;   // only the warp-specialised kernel divides by the scale
+  // only the warp-specialised kernel divides by the scale, walks grouped rows or follows a row map
+  if (p.scale || p.groups || p.row_map) return ARCQ_ERR_UNSUPPORTED_K;
 
   const size_t table = 160 + (((size_t)KQ * (rawidx ? 2 : 4) + 15) & ~(size_t)15);
   auto smem_for = [&](int nbuf, int pairs) {

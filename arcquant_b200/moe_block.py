@@ -6,10 +6,18 @@ with its own per-call global scale and its own channel orders (w1/w3 share one, 
 outputs are scaled by the routing weight and summed per token.  What replaces the reference's
 serial Python loop over all experts on one device:
 
-  * tokens and experts are sharded over the expert-parallel group; rows travel to the rank that
-    owns their expert with one all-to-all (bf16 rows - the experts' channel orders differ, so rows
-    cannot be quantized at the source), and come back with a second one;
-  * w1 and w3 of an expert are one fused [gate;up] GEMM over the shared quantized activation.
+  * the routed rows of all local experts form ONE padded buffer, expert after expert, every expert's
+    run starting at a multiple of 256 rows.  Where the runs start and how long they are is computed
+    with tensor operations and stays on the device: no count ever travels to the host, nothing in
+    `dispatch` / `combine` synchronises;
+  * one absmax launch, one quantizer launch and one GEMM launch per projection serve all experts
+    (`ops.absmax_grouped`, `ops.reorder_quantize_x_grouped`, `ops.matmul_grouped`): per-expert global
+    scale, channel order and weight matrix are picked on the device from the run a row belongs to.
+    w1 and w3 of an expert are one fused [gate;up] matrix over the shared quantized activation;
+  * tokens and experts are sharded over the expert-parallel group; rows travel to the rank that owns
+    their expert with one all-to-all of fixed-capacity blocks (bf16 rows - the experts' channel orders
+    differ, so rows cannot be quantized at the source) and come back with a second one.  The counts
+    travel as a small all-to-all of their own and are consumed on the device.
 
 The dispatcher is plain torch + torch.distributed, so its bookkeeping runs (and is tested) on CPU
 with gloo; the expert arithmetic needs the CUDA library.
@@ -24,6 +32,8 @@ import torch.nn.functional as F
 
 from . import ops
 from .qlinear import NVFP4_reorder_quantize_x
+
+TILE = 256   # rows: every expert's run starts on a tile of the grouped GEMM
 
 
 @dataclass
@@ -44,75 +54,150 @@ def route_top_k(x: torch.Tensor, router_w: torch.Tensor, top_k: int):
     return ids, w.to(x.dtype)
 
 
-class ExpertParallelDispatcher:
-    """Moves token rows to the ranks that own their experts and back (all-to-all), and groups the
-    received rows by local expert."""
+def _counts(ids: torch.Tensor, n: int) -> torch.Tensor:
+    """int64 [n]: how often each of 0..n-1 occurs (values >= n are ignored).  No host synchronisation
+    (torch.bincount would need the maximum on the host)."""
+    return (ids.unsqueeze(1) == torch.arange(n, device=ids.device).unsqueeze(0)).sum(0)
 
-    def __init__(self, n_experts: int, ep_rank: int = 0, ep_size: int = 1, group=None):
+
+def padded_layout(slot_expert: torch.Tensor, n_groups: int, tile: int = TILE):
+    """Places `n` slots (slot i belongs to expert slot_expert[i], or to nobody if that is >= n_groups) into
+    a padded buffer: expert after expert, every run starting at a multiple of `tile` rows, slots of one
+    expert in their original order.  Returns
+      dest       int64 [n]: padded row of every slot (`rows_bound` for slots of nobody),
+      row_slot   int64 [rows_bound]: slot held by every padded row (0 for padding rows),
+      groups     int32 [2 * n_groups]: first row and number of rows of every run,
+      tile_group int32 [rows_bound / tile]: run of every tile, -1 for tiles without rows,
+      rows_bound int: size of the padded buffer - the only number the host knows, a worst-case bound."""
+    n, dev = slot_expert.numel(), slot_expert.device
+    order = torch.argsort(slot_expert, stable=True)
+    sorted_e = slot_expert[order]
+    counts = _counts(slot_expert, n_groups)
+    pad = (counts + tile - 1) // tile * tile
+    offs = torch.cumsum(pad, 0) - pad
+    starts = torch.cumsum(counts, 0) - counts
+    rows_bound = (n + tile - 1) // tile * tile + n_groups * tile
+    se = sorted_e.clamp(max=n_groups - 1)
+    ar = torch.arange(n, device=dev)
+    dest_sorted = torch.where(sorted_e < n_groups, offs[se] + ar - starts[se], torch.full_like(ar, rows_bound))
+    dest = torch.empty_like(dest_sorted)
+    dest[order] = dest_sorted
+    row_slot = torch.zeros(rows_bound + 1, dtype=torch.int64, device=dev)
+    row_slot[dest] = ar
+    groups = torch.cat([offs, counts]).to(torch.int32)
+    tile_start = torch.arange(rows_bound // tile, device=dev) * tile
+    e_of = (torch.searchsorted(offs, tile_start, right=True) - 1).clamp(min=0)
+    tile_group = torch.where(tile_start < (offs + counts)[e_of], e_of, torch.full_like(e_of, -1)).to(torch.int32)
+    return dest, row_slot[:rows_bound], groups, tile_group, rows_bound
+
+
+@dataclass
+class RoutedBatch:
+    """Device-resident description of the rows the local experts work on."""
+    src: torch.Tensor          # [*, hidden]: the rows are read from here (this rank's tokens, or the receive buffer)
+    row_map: torch.Tensor      # int32 [rows_bound]: row of `src` held by every padded row (0 for padding)
+    groups: torch.Tensor       # int32 [2 * local experts]
+    tile_group: torch.Tensor   # int32 [rows_bound / TILE]
+    rows_bound: int
+    n_local: int               # local experts
+    state: dict                # what `combine` needs
+
+    def rows(self) -> torch.Tensor:
+        """The padded buffer materialised: [rows_bound, hidden] (padding rows hold a copy of row 0)."""
+        return self.src.index_select(0, self.row_map.long())
+
+    def row_expert(self) -> torch.Tensor:
+        """int64 [rows_bound]: local expert of every padded row, -1 for padding."""
+        e = self.tile_group.long().repeat_interleave(TILE)
+        ends = (self.groups[:self.n_local] + self.groups[self.n_local:]).long()
+        r = torch.arange(self.rows_bound, device=e.device)
+        return torch.where((e >= 0) & (r < ends[e.clamp(min=0)]), e, torch.full_like(e, -1))
+
+
+class ExpertParallelDispatcher:
+    """Moves token rows to the ranks that own their experts and back (all-to-all of fixed-capacity
+    blocks), and lays the rows out by local expert - without a host synchronisation.
+
+    capacity: rows one rank may send to one peer (the same number on every rank).  Default: the largest
+    number of routed copies any rank holds at the first call (agreed once with an all-reduce and kept);
+    pass it explicitly when later calls may be larger."""
+
+    def __init__(self, n_experts: int, ep_rank: int = 0, ep_size: int = 1, group=None, capacity: int | None = None):
         if n_experts % ep_size:
             raise ValueError("experts must split evenly over the expert-parallel group")
         self.E, self.rank, self.ep, self.group = n_experts, ep_rank, ep_size, group
         self.e_local = n_experts // ep_size
+        self.capacity = capacity
 
-    def dispatch(self, x: torch.Tensor, ids: torch.Tensor):
-        """x [T,H], ids [T,k]  ->  (rows grouped by local expert [R,H], rows per local expert (list),
-        state for `combine`)."""
+    def _agree_capacity(self, n_copies: int, device) -> int:
+        import torch.distributed as dist
+
+        if self.capacity is None:            # first call only: one small all-reduce and one host read
+            t = torch.tensor([n_copies], dtype=torch.int64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            self.capacity = int(t.item())
+        if n_copies > self.capacity:
+            raise ValueError(f"{n_copies} routed copies exceed the dispatcher's capacity {self.capacity}; "
+                             "construct it with capacity=<largest number of copies per rank>")
+        return self.capacity
+
+    def dispatch(self, x: torch.Tensor, ids: torch.Tensor) -> RoutedBatch:
+        """x [T,H]: this rank's tokens; ids [T,k]: global expert of every copy."""
         import torch.distributed as dist
 
         T, k = ids.shape
         flat = ids.reshape(-1)
-        order = torch.argsort(flat, stable=True)               # (token,slot) pairs sorted by expert
-        token_of = torch.div(order, k, rounding_mode="floor")
-        send_rows = x.index_select(0, token_of)
-        counts = torch.bincount(flat, minlength=self.E)        # rows per expert, this rank's tokens
         if self.ep == 1:
-            state = dict(order=order, T=T, k=k, regroup=None, send_splits=None, recv_splits=None)
-            return send_rows, counts.tolist(), state
-        recv_counts = torch.empty_like(counts)                 # [src rank, local expert] flattened
-        dist.all_to_all_single(recv_counts, counts, group=self.group)
-        send_splits = counts.reshape(self.ep, self.e_local).sum(1).tolist()
-        rc = recv_counts.reshape(self.ep, self.e_local)
-        recv_splits = rc.sum(1).tolist()
-        recv_rows = x.new_empty((int(sum(recv_splits)), x.shape[1]))
-        dist.all_to_all_single(recv_rows, send_rows, recv_splits, send_splits, group=self.group)
-        # received rows are ordered (src rank, expert); regroup to (expert, src rank)
-        rc_cpu = rc.cpu()
-        starts = torch.zeros(self.ep * self.e_local + 1, dtype=torch.int64)
-        starts[1:] = torch.cumsum(rc_cpu.reshape(-1), 0)
-        pieces = []
-        for e in range(self.e_local):
-            for s in range(self.ep):
-                j = s * self.e_local + e
-                pieces.append(torch.arange(int(starts[j]), int(starts[j + 1])))
-        regroup = torch.cat(pieces).to(x.device) if pieces else torch.zeros(0, dtype=torch.int64, device=x.device)
-        rows = recv_rows.index_select(0, regroup)
-        per_expert = rc_cpu.sum(0).tolist()
-        state = dict(order=order, T=T, k=k, regroup=regroup, send_splits=send_splits, recv_splits=recv_splits)
-        return rows, per_expert, state
+            dest, row_slot, groups, tile_group, rows_bound = padded_layout(flat, self.e_local)
+            row_map = torch.div(row_slot, k, rounding_mode="floor").to(torch.int32)
+            return RoutedBatch(x, row_map, groups, tile_group, rows_bound, self.e_local,
+                               dict(T=T, k=k, copy_row=dest))
+        n = flat.numel()
+        cap = self._agree_capacity(n, x.device)
+        # send side: copies sorted by (destination rank, expert), block s of `cap` rows goes to rank s
+        order = torch.argsort(flat, stable=True)
+        sorted_e = flat[order]
+        counts = _counts(flat, self.E)
+        per_rank = counts.reshape(self.ep, self.e_local).sum(1)
+        rank_start = torch.cumsum(per_rank, 0) - per_rank
+        dst = torch.div(sorted_e, self.e_local, rounding_mode="floor")
+        send_slot_sorted = dst * cap + torch.arange(n, device=x.device) - rank_start[dst]
+        copy_slot = torch.empty_like(send_slot_sorted)
+        copy_slot[order] = send_slot_sorted                       # slot of every copy, in copy order
+        slot_token = torch.zeros(self.ep * cap, dtype=torch.int64, device=x.device)
+        slot_token[send_slot_sorted] = torch.div(order, k, rounding_mode="floor")
+        send = x.index_select(0, slot_token)
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts, group=self.group)      # [source rank, local expert]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)               # equal blocks: no sizes needed
+        # receive side: slot i of block s holds a row of the local expert whose cumulative count first exceeds i
+        cs = torch.cumsum(recv_counts.reshape(self.ep, self.e_local), 1)   # [ep, e_local]
+        i = torch.arange(cap, device=x.device)
+        slot_expert = (i.reshape(1, cap, 1) >= cs.reshape(self.ep, 1, self.e_local)).sum(-1).reshape(-1)
+        dest, row_slot, groups, tile_group, rows_bound = padded_layout(slot_expert, self.e_local)
+        return RoutedBatch(recv, row_slot.to(torch.int32), groups, tile_group, rows_bound, self.e_local,
+                           dict(T=T, k=k, copy_row=copy_slot, slot_row=dest.clamp(max=rows_bound - 1)))
 
-    def combine(self, y_rows: torch.Tensor, weights: torch.Tensor, state) -> torch.Tensor:
-        """y_rows: expert outputs in the grouped order `dispatch` returned.  -> [T,H] weighted sums."""
+    def combine(self, y_rows: torch.Tensor, weights: torch.Tensor, batch: RoutedBatch) -> torch.Tensor:
+        """y_rows [rows_bound, H]: expert outputs in the padded layout.  -> [T,H] weighted sums."""
         import torch.distributed as dist
 
+        st = batch.state
+        T, k = st["T"], st["k"]
         if self.ep > 1:
-            back = torch.empty_like(y_rows)
-            back.index_copy_(0, state["regroup"], y_rows)      # undo the regrouping
-            ret = y_rows.new_empty((int(sum(state["send_splits"])), y_rows.shape[1]))
-            dist.all_to_all_single(ret, back, state["send_splits"], state["recv_splits"], group=self.group)
+            back = y_rows.index_select(0, st["slot_row"])                  # slot order again (padding: any row)
+            ret = torch.empty_like(back)
+            dist.all_to_all_single(ret, back, group=self.group)
         else:
             ret = y_rows
-        T, k, order = state["T"], state["k"], state["order"]
+        pos = st["copy_row"].reshape(T, k)                                  # row of `ret` holding copy j of token t
         if ret.is_cuda and ret.dtype == torch.bfloat16:
-            # one gather per token instead of a scatter-add per copy: row of `ret` holding copy j of token t
-            pos = torch.empty_like(order)
-            pos[order] = torch.arange(order.numel(), device=order.device)
-            from . import ops
-            return ops.moe_combine(ret.contiguous(), pos.reshape(T, k).to(torch.int32).contiguous(),
+            return ops.moe_combine(ret.contiguous(), pos.to(torch.int32).contiguous(),
                                    weights.to(torch.bfloat16).contiguous())
-        token_of = torch.div(order, k, rounding_mode="floor")
-        w = weights.reshape(-1).index_select(0, order).unsqueeze(1)
         out = torch.zeros((T, ret.shape[1]), dtype=ret.dtype, device=ret.device)
-        out.index_add_(0, token_of, ret * w.to(ret.dtype))
+        for j in range(k):
+            out += ret.index_select(0, pos[:, j]) * weights[:, j:j + 1].to(ret.dtype)
         return out
 
 
@@ -132,13 +217,30 @@ def random_moe_weights(cfg: MoEConfig, seed: int = 0, std: float = 0.02):
     return out
 
 
+def _stack(linears):
+    """Packed weights of several linears of one shape behind one another: (codes [E*N, K/2], scales, global
+    scales [E], channel orders [E, KQ]).  The linears' own buffers become views of the stacked ones."""
+    n, kb = linears[0].W.shape
+    k_eff = kb * 2
+    span = (n // 128) * ((k_eff // 16 + 3) // 4) * 512          # bytes of the scale tiles of one matrix
+    W = torch.cat([l.W for l in linears], 0)
+    SF = torch.cat([l.SFW[:span] for l in linears], 0)
+    for e, l in enumerate(linears):
+        l.W = W[e * n:(e + 1) * n]
+        l.SFW = SF[e * span:(e + 1) * span]
+    scale = torch.stack([l.scale for l in linears]).contiguous()
+    index = torch.stack([l.index for l in linears]).contiguous()
+    return W, SF, scale, index
+
+
 class QMixtralMoEBlockEP(torch.nn.Module):
-    def __init__(self, cfg: MoEConfig, weights: dict, ep_rank: int = 0, ep_size: int = 1, group=None, device="cuda"):
+    def __init__(self, cfg: MoEConfig, weights: dict, ep_rank: int = 0, ep_size: int = 1, group=None, device="cuda",
+                 capacity: int | None = None):
         super().__init__()
         from .llama_layer import PackedLinear
 
         self.cfg = cfg
-        self.dispatcher = ExpertParallelDispatcher(cfg.n_experts, ep_rank, ep_size, group)
+        self.dispatcher = ExpertParallelDispatcher(cfg.n_experts, ep_rank, ep_size, group, capacity)
         dev = torch.device(device)
         self.router = weights["router"].to(dev)
         self.experts = []
@@ -148,11 +250,34 @@ class QMixtralMoEBlockEP(torch.nn.Module):
             gu = PackedLinear(torch.cat([ew["w1"], ew["w3"]], 0).to(dev), ew["w1_index"], cfg.select_num)
             dn = PackedLinear(ew["w2"].to(dev).contiguous(), ew["w2_index"], cfg.select_num)
             self.experts.append((gu, dn))
+        # one launch per projection for all local experts needs whole scale tiles per expert (N % 128)
+        # and row widths the grouped quantizer covers (512..16384 channels)
+        ok_width = lambda kq: kq % 16 == 0 and 512 <= kq <= 16384
+        self.grouped = (2 * cfg.ffn) % 128 == 0 and cfg.hidden % 128 == 0 and ok_width(cfg.hidden) and ok_width(cfg.ffn)
+        if self.grouped:
+            self.gu_W, self.gu_SF, self.gu_scale, self.gu_index = _stack([gu for gu, _ in self.experts])
+            self.dn_W, self.dn_SF, self.dn_scale, self.dn_index = _stack([dn for _, dn in self.experts])
 
-    n_streams = 4   # experts are independent: a few streams hide the launch gaps of their small kernels
+    @torch.no_grad()
+    def expert_forward_grouped(self, batch: RoutedBatch) -> torch.Tensor:
+        """All local experts in seven launches: [rows_bound, hidden] in the padded layout of `batch`."""
+        cfg, E = self.cfg, self.dispatcher.e_local
+        ke = cfg.select_num
+        s1 = ops.absmax_grouped(batch.src, batch.row_map, batch.groups, E) / (448.0 * 6.0)   # per-expert scales
+        a, sfa = ops.reorder_quantize_x_grouped(batch.src, batch.row_map, s1, self.gu_index, batch.groups,
+                                                batch.rows_bound, ke)
+        h = ops.matmul_grouped(a, self.gu_W, sfa, self.gu_SF, batch.tile_group, E, 2 * cfg.ffn, s1, self.gu_scale)
+        act, _ = ops.silu_mul(h, with_amax=False)
+        s2 = ops.absmax_grouped(act, None, batch.groups, E) / (448.0 * 6.0)
+        b, sfb = ops.reorder_quantize_x_grouped(act, None, s2, self.dn_index, batch.groups, batch.rows_bound, ke)
+        return ops.matmul_grouped(b, self.dn_W, sfb, self.dn_SF, batch.tile_group, E, cfg.hidden, s2, self.dn_scale)
+
+    n_streams = 4   # per-expert path: a few streams hide the launch gaps of the experts' small kernels
 
     @torch.no_grad()
     def expert_forward(self, rows: torch.Tensor, per_expert) -> torch.Tensor:
+        """The reference's organisation - one quantize / GEMM sequence per expert on `per_expert[e]`
+        consecutive rows - kept as the yardstick of the grouped path (needs the counts on the host)."""
         out = torch.empty_like(rows)
         start = 0
         use_streams = rows.is_cuda and self.n_streams > 1 and len(self.experts) > 1
@@ -180,10 +305,24 @@ class QMixtralMoEBlockEP(torch.nn.Module):
         return out
 
     @torch.no_grad()
+    def expert_forward_padded(self, batch: RoutedBatch) -> torch.Tensor:
+        """The per-expert path on a padded batch (reads the run sizes on the host): what
+        `expert_forward_grouped` must reproduce."""
+        E = self.dispatcher.e_local
+        g = batch.groups.tolist()
+        rows = batch.rows()
+        out = torch.zeros_like(rows)
+        for e in range(E):
+            off, cnt = g[e], g[E + e]
+            if cnt:
+                out[off:off + cnt] = self.expert_forward(rows[off:off + cnt].contiguous(), [0] * e + [cnt])
+        return out
+
+    @torch.no_grad()
     def forward(self, x: torch.Tensor, routing=None) -> torch.Tensor:
         """x: this rank's tokens [T, hidden] (bf16).  routing: optional precomputed
         (expert ids [T,k], weights [T,k]) - otherwise the block's own router decides."""
         ids, w = routing if routing is not None else route_top_k(x, self.router, self.cfg.top_k)
-        rows, per_expert, state = self.dispatcher.dispatch(x, ids)
-        y = self.expert_forward(rows, per_expert)
-        return self.dispatcher.combine(y, w, state)
+        batch = self.dispatcher.dispatch(x, ids)
+        y = self.expert_forward_grouped(batch) if self.grouped else self.expert_forward_padded(batch)
+        return self.dispatcher.combine(y, w, batch)

@@ -224,6 +224,81 @@ def silu_mul(gate_up: torch.Tensor, with_amax: bool = True):
     return out, amax
 
 
+def absmax_grouped(x: torch.Tensor, row_map, groups: torch.Tensor, ngroups: int) -> torch.Tensor:
+    """fp32 [ngroups]: max|x| over the rows of each run (see `reorder_quantize_x_grouped`)."""
+    lib = _lib.load()
+    _require(x, torch.bfloat16, "input")
+    _require(groups, torch.int32, "groups")
+    if row_map is not None:
+        _require(row_map, torch.int32, "row_map")
+    if groups.numel() != 2 * ngroups:
+        raise RuntimeError("groups must hold 2 * ngroups entries")
+    out = torch.empty((ngroups,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.arcq_absmax_grouped_bf16(x.data_ptr(), None if row_map is None else row_map.data_ptr(), groups.data_ptr(),
+                                          ngroups, x.shape[-1], out.data_ptr(), _stream())
+    _lib.check(rc, "absmax_grouped")
+    return out
+
+
+def reorder_quantize_x_grouped(x: torch.Tensor, row_map, scales: torch.Tensor, reorder_indices: torch.Tensor,
+                               groups: torch.Tensor, rows_bound: int, ke: int, mode: int = 16):
+    """ARC-NVFP4 of grouped rows in one launch.  The output has `rows_bound` rows in runs: run e starts at
+    row groups[e] (a multiple of 256), holds groups[E + e] rows, is divided by scales[e] and uses the channel
+    order reorder_indices[e]; output row r reads input row row_map[r] (or r).  Everything that describes
+    the split lives on the device.  Rows outside the runs are left unwritten."""
+    lib = _lib.load()
+    _require(x, torch.bfloat16, "input")
+    _require(scales, torch.float32, "scales")
+    _require(reorder_indices, torch.int16, "reorder_indices")
+    _require(groups, torch.int32, "groups")
+    ngroups, kq = reorder_indices.shape
+    if x.shape[-1] != kq or scales.numel() != ngroups or groups.numel() != 2 * ngroups:
+        raise RuntimeError("scales / reorder_indices / groups disagree on the number of runs or on KQ")
+    if row_map is not None:
+        _require(row_map, torch.int32, "row_map")
+        if row_map.numel() < rows_bound:
+            raise RuntimeError("row_map must cover rows_bound rows")
+    elif x.shape[0] < rows_bound:
+        raise RuntimeError("input has fewer rows than rows_bound")
+    k_eff = kq + ke
+    q = torch.empty((rows_bound, k_eff // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((sf_bytes(rows_bound, k_eff),), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.arcq_reorder_quantize_x_grouped(x.data_ptr(), None if row_map is None else row_map.data_ptr(),
+                                                 scales.data_ptr(), reorder_indices.data_ptr(), groups.data_ptr(),
+                                                 ngroups, rows_bound, kq, ke, mode, q.data_ptr(), sf.data_ptr(), _stream())
+    _lib.check(rc, f"grouped x-quantize KQ={kq} KE={ke}")
+    return q, sf
+
+
+def matmul_grouped(a, b, sfa, sfb, tile_group: torch.Tensor, ngroups: int, n: int, alpha_a: torch.Tensor,
+                   alpha_b: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 [rows, n]: every 256-row tile m of A times the weight matrix tile_group[m] of the `ngroups`
+    matrices stacked in b [ngroups * n, K_eff/2] (negative = tile skipped), scaled by
+    alpha_a[g] * alpha_b[g]."""
+    lib = _lib.load()
+    for t, name in ((a, "A"), (b, "B"), (sfa, "SFA"), (sfb, "SFB")):
+        _require(t, torch.uint8, name)
+    _require(tile_group, torch.int32, "tile_group")
+    _require(alpha_a, torch.float32, "alpha_a")
+    if alpha_b is not None:
+        _require(alpha_b, torch.float32, "alpha_b")
+    m, kb = a.shape
+    if b.shape != (ngroups * n, kb) or tile_group.numel() < (m + 255) // 256 or alpha_a.numel() != ngroups:
+        raise RuntimeError("operand shapes disagree")
+    atoms = (kb * 2 // 16 + 3) // 4
+    if sfa.numel() < ((m + 127) // 128) * atoms * 512 or sfb.numel() < ((ngroups * n + 127) // 128) * atoms * 512:
+        raise RuntimeError("scale buffers are smaller than the scale layout of their operands")
+    c = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    with torch.cuda.device(a.device):
+        rc = lib.arcq_matmul_nvfp4_grouped(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, kb * 2,
+                                           tile_group.data_ptr(), ngroups, alpha_a.data_ptr(),
+                                           None if alpha_b is None else alpha_b.data_ptr(), c.data_ptr(), _stream())
+    _lib.check(rc, f"grouped matmul M={m} N={n} K={kb * 2} groups={ngroups}")
+    return c
+
+
 def moe_combine(y: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
     """out [T, H] = sum_j bf16(y[pos[t, j]] * weights[t, j]) in bf16: the routed copies of every token,
     weighted and added (pos int32 [T, k], weights bf16 [T, k])."""

@@ -90,8 +90,8 @@ int arcq_reorder_quantize_x(const void* x, const int16_t* reorder_index, int64_t
  * Every element becomes bf16(fp32(x) / fp32(bf16(*scale))), round to nearest even - what torch's CUDA
  * kernel gives for (bf16 tensor) / (fp32 0-dim tensor), which loads the divisor in the tensor's type -
  * and is then quantized as by arcq_reorder_quantize_x.
- * Returns ARCQ_ERR_UNSUPPORTED_K for row widths the staging kernel does not cover (KQ/16 must be a
- * multiple of 32 and KQ at most 16384); the caller then divides first. */
+ * Returns ARCQ_ERR_UNSUPPORTED_K for row widths the staging kernel does not cover (KQ from 512 to
+ * 16384 is covered); the caller then divides first. */
 int arcq_reorder_quantize_x_scaled(const void* x, const float* scale, const int16_t* reorder_index, int64_t M, int KQ,
                                    int KE, int mode, uint8_t* qx, uint8_t* sfx, void* stream);
 
@@ -206,6 +206,37 @@ int arcq_silu_mul_bf16(const void* gate_up, void* out, int64_t tokens, int F, fl
  * sum_j bf16(y[pos[t][j]] * weights[t][j]), products and running sum rounded to bf16.  hidden % 8 == 0. */
 int arcq_moe_combine_bf16(const void* y, const int32_t* pos, const void* weights, void* out, int64_t tokens, int hidden,
                           int top_k, void* stream);
+
+/* ---- Grouped forms: all experts of a sparse MoE block in one launch ---------------------------------
+ * The reference runs its experts one after another from Python, each with its own quantize and GEMM
+ * calls on that expert's batch of tokens (model/qMixtralLayer.py:458-471, 524-543).  Here the routed
+ * rows of all experts lie in ONE buffer, expert after expert ("runs"), every run starting at a multiple
+ * of 256 rows; how many rows each run holds is known on the device only:
+ *   groups    int32 [2*ngroups] in device memory: groups[e] = first row of run e (a multiple of 256),
+ *             groups[ngroups + e] = its number of rows.  Rows between runs are padding: never read as
+ *             results, their content is unspecified.
+ *   row_map   int32 per (padded) row, or NULL: the row of x that row holds (the dispatch gather is
+ *             folded into the loads).
+ * No counterpart in the reference's bindings.
+ *
+ * arcq_absmax_grouped_bf16: out[e] = max|x| over the rows of run e (the per-call global scale of
+ *   NVFP4_reorder_quantize_x, per expert).
+ * arcq_reorder_quantize_x_grouped: arcq_reorder_quantize_x_scaled on every run with its own divisor
+ *   scales[e] and its own channel order reorder_indices + e*KQ (int16 [ngroups, KQ]).  rows_bound: rows of
+ *   the output buffers (>= end of the last run).  Row widths as arcq_reorder_quantize_x_scaled.
+ * arcq_matmul_nvfp4_grouped: C[r, :] = alpha_a[e]*alpha_b[e] * A[r, :] . B_e^T for the rows r of run e;
+ *   B [ngroups*N, K_eff/2] and SFB hold the experts' packed weights one after another (N % 128 == 0);
+ *   tile_group int32 [ceil(M_bound/256)] in device memory: the run that owns each 256-row tile of A, or
+ *   a negative number for a tile without rows (skipped).  alpha_b may be NULL. */
+int arcq_absmax_grouped_bf16(const void* x, const int32_t* row_map, const int32_t* groups, int ngroups, int K,
+                             float* out, void* stream);
+int arcq_reorder_quantize_x_grouped(const void* x, const int32_t* row_map, const float* scales,
+                                    const int16_t* reorder_indices, const int32_t* groups, int ngroups,
+                                    int64_t rows_bound, int KQ, int KE, int mode, uint8_t* qx, uint8_t* sfx,
+                                    void* stream);
+int arcq_matmul_nvfp4_grouped(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                              int64_t M_bound, int64_t N, int64_t K_eff, const int32_t* tile_group, int ngroups,
+                              const float* alpha_a, const float* alpha_b, void* C, void* stream);
 
 #ifdef __cplusplus
 }

@@ -190,8 +190,8 @@ def test_moe_block_matches_cpu_restatement_and_expert_parallel_emulation():
             if tok.numel() == 0:
                 continue
             local_ids = (ids[tok, j] - 2 * r).reshape(-1, 1)
-            rows, per_expert, state = blk.dispatcher.dispatch(x[tok].cuda(), local_ids.cuda())
-            out = blk.dispatcher.combine(blk.expert_forward(rows, per_expert), w[tok, j].reshape(-1, 1).cuda(), state)
+            batch = blk.dispatcher.dispatch(x[tok].cuda(), local_ids.cuda())
+            out = blk.dispatcher.combine(blk.expert_forward_grouped(batch), w[tok, j].reshape(-1, 1).cuda(), batch)
             total.index_add_(0, tok, out.float().cpu())
     # per-expert batches differ from the unsharded run only in how rows were grouped into calls
     assert _rel(total, exact) < 1.2 * e_ref + 0.01, (_rel(total, exact), e_ref)
@@ -380,7 +380,9 @@ def test_qlinear_layer_mirror():
     from oracle import oracle as O
 
     w = lin.weight.data
-    sw, sx = torch.max(w).float() / 2688.0, x.abs().max().float() / 2688.0
+    # (scales formed on the GPU, as the reference's callers do: torch's CUDA division by a Python scalar
+    # multiplies by its reciprocal, which can differ from the CPU quotient in the last place)
+    sw, sx = (torch.max(w.cuda()).float() / 2688.0).cpu(), (x.cuda().abs().max().float() / 2688.0).cpu()
     assert float(sw) == float(layer.scale) and float(sx) == float(scale)
     # (torch's CUDA kernel for bf16 / fp32-scalar rounds the divisor to bf16 first)
     div = lambda t, s: (t.float() / s.to(torch.bfloat16).float()).to(torch.bfloat16).contiguous()
@@ -407,3 +409,28 @@ def test_qlinear_layer_mirror():
     assert torch.equal(layer_nb((qx, scale_x, scale, bsz, q_len)), y3)
     with pytest.raises(NotImplementedError):
         QLinearLayer(lin, ke, idx, quant_type="MXFP4")
+
+
+def test_grouped_experts_equal_the_per_expert_loop():
+    """One absmax / quantize / GEMM launch per projection over all experts (run sizes known on the device
+    only) against the reference's organisation, one call sequence per expert: same bytes.  Includes an
+    expert without tokens and runs that are not multiples of the tile."""
+    from arcquant_b200.moe_block import MoEConfig, QMixtralMoEBlockEP, random_moe_weights, route_top_k
+
+    cfg = MoEConfig(hidden=1024, ffn=2048, n_experts=4, top_k=2, select_num=64)
+    W = random_moe_weights(cfg, 0)
+    block = QMixtralMoEBlockEP(cfg, W)
+    assert block.grouped
+    x = synth.activations(700, cfg.hidden, 5, synth.outlier_channels(cfg.hidden, 10, 3)).cuda()
+    ids, w = route_top_k(x, W["router"].cuda(), cfg.top_k)
+    ids = torch.where(ids == 2, torch.zeros_like(ids), ids)            # expert 2 gets nothing
+    batch = block.dispatcher.dispatch(x, ids)
+    y_grouped = block.expert_forward_grouped(batch)
+    y_loop = block.expert_forward_padded(batch)
+    valid = batch.row_expert() >= 0
+    assert int(valid.sum()) == ids.numel()
+    assert torch.equal(y_grouped[valid], y_loop[valid])
+    out = block.dispatcher.combine(y_grouped, w, batch)
+    assert bool(torch.isfinite(out).all())                             # padding rows never reach a token
+    from arcquant_b200 import ops
+    assert ops.gemm_poll_error() == 0

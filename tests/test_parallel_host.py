@@ -90,15 +90,14 @@ def _moe_worker(rank, world, port, q):
         router = torch.randn(E, H, generator=torch.Generator().manual_seed(1))
         ids, w = route_top_k(x, router, k)
         d = ExpertParallelDispatcher(E, rank, world)
-        rows, per_expert, state = d.dispatch(x, ids)
-        assert rows.shape[0] == sum(per_expert)
-        # fake expert e: y = x * (e + 1)
-        y = torch.empty_like(rows)
-        s = 0
-        for j, n in enumerate(per_expert):
-            e = rank * d.e_local + j
-            y[s:s + n] = rows[s:s + n] * (e + 1)
-            s += n
+        batch = d.dispatch(x, ids)
+        rows, owner = batch.rows(), batch.row_expert()
+        assert rows.shape[0] == batch.rows_bound and batch.rows_bound % 256 == 0
+        assert int((owner >= 0).sum()) == int(batch.groups[d.e_local:].sum())
+        # fake expert e: y = x * (e + 1); padding rows get a value that must never reach a token
+        y = torch.where(owner[:, None] >= 0, rows * (rank * d.e_local + owner[:, None] + 1).to(rows.dtype),
+                        torch.full_like(rows, float("nan")))
+        state = batch
         out = d.combine(y, w, state)
         ref = torch.zeros_like(x)
         for t in range(T):
@@ -131,12 +130,19 @@ def test_single_rank_dispatch_matches_dense():
     ids, w = route_top_k(x, router, k)
     assert torch.allclose(w.sum(1), torch.ones(T))
     d = ExpertParallelDispatcher(E)
-    rows, per_expert, state = d.dispatch(x, ids)
-    y = torch.empty_like(rows)
-    s = 0
-    for e, n in enumerate(per_expert):
-        y[s:s + n] = rows[s:s + n] * (e + 1)
-        s += n
+    batch = d.dispatch(x, ids)
+    rows, owner = batch.rows(), batch.row_expert()
+    # every run starts on a 256-row tile and holds exactly the copies routed to its expert, in token order
+    g = batch.groups.tolist()
+    for e in range(E):
+        assert g[e] % 256 == 0 and g[E + e] == int((ids == e).sum())
+        assert bool((owner[g[e]:g[e] + g[E + e]] == e).all())
+        tok = torch.where(ids == e)[0]
+        assert torch.equal(rows[g[e]:g[e] + g[E + e]], x[tok])
+        assert set(batch.tile_group[g[e] // 256:(g[e] + g[E + e] + 255) // 256].tolist()) <= {e}
+    assert int((batch.tile_group >= 0).sum()) == sum((g[E + e] + 255) // 256 for e in range(E))
+    y = torch.where(owner[:, None] >= 0, rows * (owner[:, None] + 1).to(rows.dtype), torch.full_like(rows, float("nan")))
+    state = batch
     out = d.combine(y, w, state)
     ref = sum(x * (ids[:, j:j + 1] + 1) * w[:, j:j + 1] for j in range(k))
     assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
