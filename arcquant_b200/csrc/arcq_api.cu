@@ -218,6 +218,16 @@ int arcq_moe_combine_bf16(const void* y, const int32_t* pos, const void* weights
   return launch_moe_combine(y, pos, weights, out, tokens, hidden, top_k, (cudaStream_t)stream);
 }
 
+int arcq_moe_layout(const int64_t* slot_group, int n, int ngroups, int tile, int rows_bound, int div, int32_t* dest,
+                    int32_t* row_map, int32_t* groups, int32_t* tile_group, void* stream) {
+  if (n < 0 || n > (1 << 20) || ngroups < 1 || ngroups > 64 || tile < 1 || div < 1 || rows_bound % tile ||
+      (int64_t)rows_bound < ((int64_t)n + tile - 1) / tile * tile + (int64_t)ngroups * tile)
+    return ARCQ_ERR_BAD_SHAPE;
+  if ((n > 0 && !slot_group) || !dest || !row_map || !groups || !tile_group) return ARCQ_ERR_NULL_POINTER;
+  return launch_moe_layout(reinterpret_cast<const long long*>(slot_group), n, ngroups, tile, rows_bound, div, dest,
+                           row_map, groups, tile_group, (cudaStream_t)stream);
+}
+
 int arcq_absmax_grouped_bf16(const void* x, const int32_t* row_map, const int32_t* groups, int ngroups, int K, float* out,
                              void* stream) {
   if (ngroups < 1 || ngroups > 64 || K <= 0 || K % 8) return ARCQ_ERR_BAD_SHAPE;

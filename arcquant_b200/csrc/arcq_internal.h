@@ -56,6 +56,8 @@ int launch_gemm_grouped(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, 
                         const float* alpha_b, void* C, cudaStream_t stream);
 int launch_absmax_grouped(const void* x, const int* row_map, const int* groups, int ngroups, int K, float* out,
                           cudaStream_t stream);
+int launch_moe_layout(const long long* slot_group, int n, int ngroups, int tile, int rows_bound, int div, int* dest,
+                      int* row_map, int* groups, int* tile_group, cudaStream_t stream);
 int gemm_poll_error();
 // Same for the bounded waits of the warp-specialised quantizer.
 int quant_poll_error();

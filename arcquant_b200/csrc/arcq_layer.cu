@@ -218,7 +218,91 @@ __global__ void arcq_absmax_grouped_kernel(const uint16_t* __restrict__ x, const
   }
 }
 
+// Padded layout of routed rows, one CTA: slot i belongs to run slot_group[i] (or to nobody if that is >=
+// ngroups); the runs follow one another, each starting at a multiple of `tile` rows, slots of one run in
+// their original order.  dest[i] = padded row of slot i (rows_bound for nobody), row_map[r] = i / div for
+// the padded row r that holds slot i (0 for padding), groups = [first row of every run | rows of every
+// run], tile_group[m] = run of tile m or -1.
+__global__ void __launch_bounds__(1024, 1)
+arcq_moe_layout_kernel(const long long* __restrict__ slot_group, int n, int ngroups, int tile, int rows_bound, int div,
+                       int* __restrict__ dest, int* __restrict__ row_map, int* __restrict__ groups,
+                       int* __restrict__ tile_group) {
+  __shared__ int s_cnt[64], s_off[64], s_warp[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int per = (n + 1023) >> 10;
+  const int lo = min(n, tid * per), hi = min(n, lo + per);
+  for (int r = tid; r < rows_bound; r += 1024) row_map[r] = 0;
+  // this thread's matches of run e, and the number of matches in all earlier threads (exclusive scan)
+  auto scan = [&](int e, int& mine, int& before, int& total) {
+    mine = 0;
+    for (int i = lo; i < hi; ++i) mine += (slot_group[i] == (long long)e) ? 1 : 0;
+    int inc = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += v;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane], winc = w;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, winc, d);
+        if (lane >= d) winc += v;
+      }
+      s_warp[lane] = winc - w;                         // matches in earlier warps
+      if (lane == 31) s_cnt[e] = winc;
+    }
+    __syncthreads();
+    before = s_warp[warp] + inc - mine;
+    total = s_cnt[e];
+    __syncthreads();                                   // s_warp is reused by the next scan
+  };
+  int mine, before, total;
+  for (int e = 0; e < ngroups; ++e) scan(e, mine, before, total);   // fills s_cnt
+  if (tid == 0) {
+    int off = 0;
+    for (int e = 0; e < ngroups; ++e) {
+      s_off[e] = off;
+      groups[e] = off;
+      groups[ngroups + e] = s_cnt[e];
+      off += (s_cnt[e] + tile - 1) / tile * tile;
+    }
+  }
+  __syncthreads();
+  for (int e = 0; e < ngroups; ++e) {
+    const int off = s_off[e];
+    scan(e, mine, before, total);
+    int r = off + before;
+    for (int i = lo; i < hi; ++i) {
+      if (slot_group[i] == (long long)e) {
+        dest[i] = r;
+        row_map[r] = i / div;
+        ++r;
+      }
+    }
+  }
+  for (int i = lo; i < hi; ++i)
+    if (slot_group[i] < 0 || slot_group[i] >= (long long)ngroups) dest[i] = rows_bound;
+  for (int m = tid; m < rows_bound / tile; m += 1024) {
+    const int start = m * tile;
+    int g = -1;
+    for (int e = 0; e < ngroups; ++e)
+      if (start >= s_off[e] && start < s_off[e] + s_cnt[e]) g = e;
+    tile_group[m] = g;
+  }
+}
+
 }  // namespace
+
+int launch_moe_layout(const long long* slot_group, int n, int ngroups, int tile, int rows_bound, int div, int* dest,
+                      int* row_map, int* groups, int* tile_group, cudaStream_t stream) {
+  arcq_moe_layout_kernel<<<1, 1024, 0, stream>>>(slot_group, n, ngroups, tile, rows_bound, div, dest, row_map, groups,
+                                                 tile_group);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
 
 int launch_absmax_grouped(const void* x, const int* row_map, const int* groups, int ngroups, int K, float* out,
                           cudaStream_t stream) {

@@ -14,6 +14,7 @@ one NCCL all-reduce follows each row-parallel GEMM.  Attention itself (RoPE, SDP
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from dataclasses import dataclass
 
@@ -147,7 +148,36 @@ class PackedLinear(torch.nn.Module):
         return ops.matmul_dev_alpha(qx, self.W, sfx, self.SFW, scale_x, self.scale)
 
 
+class PhaseTimer:
+    """Per-phase device time of a step (CUDA events around each phase; eager runs only - it synchronises
+    when read).  Phases: quantize, gemm, attention, glue, collective."""
+
+    def __init__(self):
+        self.spans = []
+
+    @contextlib.contextmanager
+    def phase(self, name: str):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        yield
+        e1.record()
+        self.spans.append((name, e0, e1))
+
+    def totals(self) -> dict:
+        torch.cuda.synchronize()
+        out: dict = {}
+        for name, e0, e1 in self.spans:
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        self.spans = []
+        return out
+
+
 class QLlamaDecoderLayerTP(torch.nn.Module):
+    timer: PhaseTimer | None = None     # set to a PhaseTimer to attribute the time of eager steps
+
+    def _ph(self, name: str):
+        return self.timer.phase(name) if self.timer is not None else contextlib.nullcontext()
+
     def __init__(self, cfg: LlamaLayerConfig, weights: dict, indices: dict, tp_rank: int = 0, tp_size: int = 1,
                  group=None, device="cuda"):
         super().__init__()
@@ -206,29 +236,40 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
     @torch.no_grad()
     def attn_partial(self, x2d: torch.Tensor, bsz: int, seq: int, positions: torch.Tensor) -> torch.Tensor:
         cfg, D = self.cfg, self.cfg.head_dim
-        a, sfa = ops.rmsnorm_quantize_x(x2d, self.ln1, cfg.eps, self.qkv.index, self.qkv.select_num)
-        qkv = self.qkv.gemm(a, sfa)
+        with self._ph("quantize"):
+            a, sfa = ops.rmsnorm_quantize_x(x2d, self.ln1, cfg.eps, self.qkv.index, self.qkv.select_num)
+        with self._ph("gemm"):
+            qkv = self.qkv.gemm(a, sfa)
         nq, nk = self.h_local * D, self.kv_local * D
         # rotary embedding in place on the q and k columns of the fused output (they are adjacent);
         # attention reads strided views of it, grouped-query heads are not materialised
-        cos, sin = rope_tables(positions, D, cfg.rope_theta)
-        ops.rope_inplace(qkv, cos, sin, self.h_local + self.kv_local, D)
-        q = qkv[:, :nq].reshape(bsz, seq, self.h_local, D).transpose(1, 2)
-        k = qkv[:, nq:nq + nk].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
-        v = qkv[:, nq + nk:].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
-        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.h_local != self.kv_local)
-        attn = attn.transpose(1, 2).reshape(bsz * seq, nq).contiguous()
-        qa, sfo, so = NVFP4_reorder_quantize_x(attn, self.o.index, self.o.select_num, mode=16)
-        return self.o.gemm(qa, sfo, so)
+        with self._ph("glue"):
+            cos, sin = rope_tables(positions, D, cfg.rope_theta)
+            ops.rope_inplace(qkv, cos, sin, self.h_local + self.kv_local, D)
+        with self._ph("attention"):
+            q = qkv[:, :nq].reshape(bsz, seq, self.h_local, D).transpose(1, 2)
+            k = qkv[:, nq:nq + nk].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
+            v = qkv[:, nq + nk:].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
+            attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.h_local != self.kv_local)
+            attn = attn.transpose(1, 2).reshape(bsz * seq, nq).contiguous()
+        with self._ph("quantize"):
+            qa, sfo, so = NVFP4_reorder_quantize_x(attn, self.o.index, self.o.select_num, mode=16)
+        with self._ph("gemm"):
+            return self.o.gemm(qa, sfo, so)
 
     @torch.no_grad()
     def mlp_partial(self, h2d: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
-        a, sfa = ops.rmsnorm_quantize_x(h2d, self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
-        gu = self.gate_up.gemm(a, sfa)
-        act, amax = ops.silu_mul(gu)      # silu(gate) * up and its max|.| in one pass
-        qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16, amax=amax)
-        return self.down.gemm(qd, sfd, sd)
+        with self._ph("quantize"):
+            a, sfa = ops.rmsnorm_quantize_x(h2d, self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
+        with self._ph("gemm"):
+            gu = self.gate_up.gemm(a, sfa)
+        with self._ph("glue"):
+            act, amax = ops.silu_mul(gu)      # silu(gate) * up and its max|.| in one pass
+        with self._ph("quantize"):
+            qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16, amax=amax)
+        with self._ph("gemm"):
+            return self.down.gemm(qd, sfd, sd)
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
@@ -238,8 +279,16 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         x2d = x.reshape(bsz * seq, hidden).contiguous()
         if self.tp > 1 and x2d.shape[0] >= 2 * self.overlap_rows and self._dist_ready():
             return self._forward_overlapped(x2d, bsz, seq, positions).reshape(bsz, seq, hidden)
-        h = x2d + tp.all_reduce_sum(self.attn_partial(x2d, bsz, seq, positions), self.group)
-        out = h + tp.all_reduce_sum(self.mlp_partial(h), self.group)
+        y = self.attn_partial(x2d, bsz, seq, positions)
+        with self._ph("collective"):
+            y = tp.all_reduce_sum(y, self.group)
+        with self._ph("glue"):
+            h = x2d + y
+        y = self.mlp_partial(h)
+        with self._ph("collective"):
+            y = tp.all_reduce_sum(y, self.group)
+        with self._ph("glue"):
+            out = h + y
         return out.reshape(bsz, seq, hidden)
 
     overlap_rows = 4096   # rows per chunk of the overlapped schedule (a multiple of 128)
@@ -276,29 +325,48 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         if positions is None:
             positions = torch.arange(seq, device=x_shard.device)
         k_eff = cfg.hidden + self.qkv.select_num
-        a_s, sfa_s = ops.rmsnorm_quantize_x(x_shard, self.ln1, cfg.eps, self.qkv.index, self.qkv.select_num)
-        a, sfa = self._gather_quantized(a_s, sfa_s, rows_s, k_eff)
-        qkv = self.qkv.gemm(a, sfa)
+        with self._ph("quantize"):
+            a_s, sfa_s = ops.rmsnorm_quantize_x(x_shard, self.ln1, cfg.eps, self.qkv.index, self.qkv.select_num)
+        with self._ph("collective"):
+            a, sfa = self._gather_quantized(a_s, sfa_s, rows_s, k_eff)
+        with self._ph("gemm"):
+            qkv = self.qkv.gemm(a, sfa)
         nq, nk = self.h_local * D, self.kv_local * D
-        cos, sin = rope_tables(positions, D, cfg.rope_theta)
-        ops.rope_inplace(qkv, cos, sin, self.h_local + self.kv_local, D)
-        q = qkv[:, :nq].reshape(bsz, seq, self.h_local, D).transpose(1, 2)
-        k = qkv[:, nq:nq + nk].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
-        v = qkv[:, nq + nk:].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
-        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.h_local != self.kv_local)
-        attn = attn.transpose(1, 2).reshape(T, nq).contiguous()
-        qa, sfo, so = NVFP4_reorder_quantize_x(attn, self.o.index, self.o.select_num, mode=16)
-        y = self.o.gemm(qa, sfo, so)
+        with self._ph("glue"):
+            cos, sin = rope_tables(positions, D, cfg.rope_theta)
+            ops.rope_inplace(qkv, cos, sin, self.h_local + self.kv_local, D)
+        with self._ph("attention"):
+            q = qkv[:, :nq].reshape(bsz, seq, self.h_local, D).transpose(1, 2)
+            k = qkv[:, nq:nq + nk].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
+            v = qkv[:, nq + nk:].reshape(bsz, seq, self.kv_local, D).transpose(1, 2)
+            attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.h_local != self.kv_local)
+            attn = attn.transpose(1, 2).reshape(T, nq).contiguous()
+        with self._ph("quantize"):
+            qa, sfo, so = NVFP4_reorder_quantize_x(attn, self.o.index, self.o.select_num, mode=16)
+        with self._ph("gemm"):
+            y = self.o.gemm(qa, sfo, so)
         y_s = torch.empty_like(x_shard)
-        dist.reduce_scatter_tensor(y_s, y, op=dist.ReduceOp.SUM, group=self.group)
-        h_s = x_shard + y_s
-        a_s, sfa_s = ops.rmsnorm_quantize_x(h_s, self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
-        a, sfa = self._gather_quantized(a_s, sfa_s, rows_s, k_eff)
-        act, amax = ops.silu_mul(self.gate_up.gemm(a, sfa))
-        qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16, amax=amax)
-        y = self.down.gemm(qd, sfd, sd)
-        dist.reduce_scatter_tensor(y_s, y, op=dist.ReduceOp.SUM, group=self.group)
-        return h_s + y_s
+        with self._ph("collective"):
+            dist.reduce_scatter_tensor(y_s, y, op=dist.ReduceOp.SUM, group=self.group)
+        with self._ph("glue"):
+            h_s = x_shard + y_s
+        with self._ph("quantize"):
+            a_s, sfa_s = ops.rmsnorm_quantize_x(h_s, self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
+        with self._ph("collective"):
+            a, sfa = self._gather_quantized(a_s, sfa_s, rows_s, k_eff)
+        with self._ph("gemm"):
+            gu = self.gate_up.gemm(a, sfa)
+        with self._ph("glue"):
+            act, amax = ops.silu_mul(gu)
+        with self._ph("quantize"):
+            qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16, amax=amax)
+        with self._ph("gemm"):
+            y = self.down.gemm(qd, sfd, sd)
+        with self._ph("collective"):
+            dist.reduce_scatter_tensor(y_s, y, op=dist.ReduceOp.SUM, group=self.group)
+        with self._ph("glue"):
+            out = h_s + y_s
+        return out
 
     def _dist_ready(self) -> bool:
         import torch.distributed as dist

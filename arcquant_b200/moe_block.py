@@ -70,13 +70,17 @@ def padded_layout(slot_expert: torch.Tensor, n_groups: int, tile: int = TILE):
       tile_group int32 [rows_bound / tile]: run of every tile, -1 for tiles without rows,
       rows_bound int: size of the padded buffer - the only number the host knows, a worst-case bound."""
     n, dev = slot_expert.numel(), slot_expert.device
+    rows_bound = (n + tile - 1) // tile * tile + n_groups * tile
+    if slot_expert.is_cuda and n_groups <= 64 and n <= (1 << 20):       # one small launch does all of it
+        dest, row_slot, groups, tile_group = ops.moe_layout(slot_expert.to(torch.int64).contiguous(), n_groups, tile,
+                                                            rows_bound)
+        return dest, row_slot, groups, tile_group, rows_bound
     order = torch.argsort(slot_expert, stable=True)
     sorted_e = slot_expert[order]
     counts = _counts(slot_expert, n_groups)
     pad = (counts + tile - 1) // tile * tile
     offs = torch.cumsum(pad, 0) - pad
     starts = torch.cumsum(counts, 0) - counts
-    rows_bound = (n + tile - 1) // tile * tile + n_groups * tile
     se = sorted_e.clamp(max=n_groups - 1)
     ar = torch.arange(n, device=dev)
     dest_sorted = torch.where(sorted_e < n_groups, offs[se] + ar - starts[se], torch.full_like(ar, rows_bound))

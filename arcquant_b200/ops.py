@@ -224,6 +224,23 @@ def silu_mul(gate_up: torch.Tensor, with_amax: bool = True):
     return out, amax
 
 
+def moe_layout(slot_group: torch.Tensor, ngroups: int, tile: int, rows_bound: int, div: int = 1):
+    """Padded layout of routed rows in one launch: (dest int32 [n], row_map int32 [rows_bound], groups int32
+    [2*ngroups], tile_group int32 [rows_bound/tile]); see `arcq_moe_layout` in arcq.h."""
+    lib = _lib.load()
+    _require(slot_group, torch.int64, "slot_group")
+    n, dev = slot_group.numel(), slot_group.device
+    dest = torch.empty((n,), dtype=torch.int32, device=dev)
+    row_map = torch.empty((rows_bound,), dtype=torch.int32, device=dev)
+    groups = torch.empty((2 * ngroups,), dtype=torch.int32, device=dev)
+    tile_group = torch.empty((rows_bound // tile,), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.arcq_moe_layout(slot_group.data_ptr(), n, ngroups, tile, rows_bound, div, dest.data_ptr(),
+                                 row_map.data_ptr(), groups.data_ptr(), tile_group.data_ptr(), _stream())
+    _lib.check(rc, "moe_layout")
+    return dest, row_map, groups, tile_group
+
+
 def absmax_grouped(x: torch.Tensor, row_map, groups: torch.Tensor, ngroups: int) -> torch.Tensor:
     """fp32 [ngroups]: max|x| over the rows of each run (see `reorder_quantize_x_grouped`)."""
     lib = _lib.load()

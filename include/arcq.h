@@ -228,6 +228,17 @@ int arcq_moe_combine_bf16(const void* y, const int32_t* pos, const void* weights
  *   B [ngroups*N, K_eff/2] and SFB hold the experts' packed weights one after another (N % 128 == 0);
  *   tile_group int32 [ceil(M_bound/256)] in device memory: the run that owns each 256-row tile of A, or
  *   a negative number for a tile without rows (skipped).  alpha_b may be NULL. */
+/* The padded layout itself, computed on the device in one small launch (no counterpart in the reference,
+ * whose Python loop asks torch.where for every expert's rows, model/qMixtralLayer.py:458-466).
+ * slot_group int64 [n]: the run (local expert) of every slot - a routed copy (token, j) or a row of the
+ * receive buffer - or a value outside [0, ngroups) for a slot that belongs to nobody.  Outputs, all int32
+ * in device memory: dest [n] = padded row of every slot (rows_bound for nobody); row_map [rows_bound] =
+ * slot / div of the slot every padded row holds (0 for padding; div = top_k turns copies into tokens);
+ * groups [2*ngroups]; tile_group [rows_bound / tile].  Slots of one run keep their order.
+ * rows_bound must be a multiple of tile and at least n rounded up to a tile plus ngroups * tile;
+ * n <= 1 << 20, ngroups <= 64. */
+int arcq_moe_layout(const int64_t* slot_group, int n, int ngroups, int tile, int rows_bound, int div, int32_t* dest,
+                    int32_t* row_map, int32_t* groups, int32_t* tile_group, void* stream);
 int arcq_absmax_grouped_bf16(const void* x, const int32_t* row_map, const int32_t* groups, int ngroups, int K,
                              float* out, void* stream);
 int arcq_reorder_quantize_x_grouped(const void* x, const int32_t* row_map, const float* scales,

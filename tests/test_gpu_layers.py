@@ -434,3 +434,20 @@ def test_grouped_experts_equal_the_per_expert_loop():
     assert bool(torch.isfinite(out).all())                             # padding rows never reach a token
     from arcquant_b200 import ops
     assert ops.gemm_poll_error() == 0
+
+
+@pytest.mark.parametrize("n,e", [(1, 1), (255, 4), (8192, 8), (8192, 64), (70001, 8), (1000, 3)])
+def test_moe_layout_kernel_equals_the_tensor_formulation(n, e):
+    """The single-launch layout (`arcq_moe_layout`) against the same layout written with torch operations
+    on the CPU: destinations, row map, run table and tile table are identical, slots of nobody included."""
+    from arcquant_b200.moe_block import padded_layout
+
+    g = torch.Generator().manual_seed(n + e)
+    slot = torch.randint(0, e + 1, (n,), generator=g)                   # value e = belongs to nobody
+    if n > 500:
+        slot[slot == min(1, e - 1)] = 0                                   # and an empty run
+    want = padded_layout(slot, e)
+    got = padded_layout(slot.cuda(), e)
+    assert want[4] == got[4]
+    for a, b in zip(want[:4], got[:4]):
+        assert torch.equal(a.long(), b.cpu().long())
