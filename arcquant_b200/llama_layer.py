@@ -368,6 +368,106 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
             out = h_s + y_s
         return out
 
+    # ---- the same with communication hidden behind compute
+    @staticmethod
+    def pipelined_shard_rows(total_rows: int, tp_size: int, tp_rank: int, chunks: int) -> torch.Tensor:
+        """Rows of the [total_rows, hidden] residual stream that rank `tp_rank` holds in the pipelined
+        sequence-parallel form: the stream is cut into `chunks` runs of whole sequences and every rank owns
+        its 1/tp slice of EVERY run (so each run's collectives involve all ranks evenly)."""
+        tc = total_rows // chunks
+        rc = tc // tp_size
+        base = torch.arange(chunks).repeat_interleave(rc) * tc + tp_rank * rc
+        return base + torch.arange(rc).repeat(chunks)
+
+    @torch.no_grad()
+    def forward_sequence_parallel_pipelined(self, x_shard: torch.Tensor, bsz: int, seq: int,
+                                            positions: torch.Tensor | None = None, chunks: int = 4) -> torch.Tensor:
+        """`forward_sequence_parallel` with its collectives overlapped with compute.  The batch is cut into
+        `chunks` runs of whole sequences; x_shard holds this rank's slice of every run
+        (`pipelined_shard_rows`).  Everything between two per-tensor scales is independent per row, so
+        inside each of the three segments that the two scales (o and down inputs) delimit, the all-gather
+        or reduce-scatter of one run (NCCL, asynchronous) runs under the GEMMs, attention and quantizers
+        of its neighbours.  Row for row the arithmetic is that of `forward_sequence_parallel`."""
+        import torch.distributed as dist
+
+        cfg, D, C = self.cfg, self.cfg.head_dim, chunks
+        T = bsz * seq
+        if bsz % C or x_shard.shape[0] * self.tp != T or (T // C // self.tp) % 128:
+            raise ValueError("runs must be whole sequences and every rank's slice of a run a multiple of 128 rows")
+        if positions is None:
+            positions = torch.arange(seq, device=x_shard.device)
+        tc, rc = T // C, T // C // self.tp            # rows of a run, rows of this rank's slice of it
+        bc = bsz // C
+        k_eff = cfg.hidden + self.qkv.select_num
+        tile = ((k_eff // 16 + 3) // 4) * 512
+        span = (rc // 128) * tile
+        nq, nk = self.h_local * D, self.kv_local * D
+        dev = x_shard.device
+        xs = x_shard.reshape(C, rc, cfg.hidden)
+
+        def gather_async(q_s, sf_s):
+            q = torch.empty((tc, k_eff // 2), dtype=torch.uint8, device=dev)
+            sf = torch.empty((ops.sf_bytes(tc, k_eff),), dtype=torch.uint8, device=dev)
+            w1 = dist.all_gather_into_tensor(q, q_s, group=self.group, async_op=True)
+            w2 = dist.all_gather_into_tensor(sf[:span * self.tp], sf_s[:span], group=self.group, async_op=True)
+            return q, sf, (w1, w2)
+
+        # segment A: fused RMSNorm + quantize of the slices, all-gather, qkv GEMM, attention per run
+        pend = []
+        for c in range(C):
+            a_s, sfa_s = ops.rmsnorm_quantize_x(xs[c], self.ln1, cfg.eps, self.qkv.index, self.qkv.select_num)
+            pend.append(gather_async(a_s, sfa_s))
+        cos, sin = rope_tables(positions, D, cfg.rope_theta)
+        attn = torch.empty((C, tc, nq), dtype=torch.bfloat16, device=dev)
+        amax = []
+        for c in range(C):
+            a, sfa, works = pend[c]
+            for w in works:
+                w.wait()
+            qkv = self.qkv.gemm(a, sfa)
+            ops.rope_inplace(qkv, cos, sin, self.h_local + self.kv_local, D)
+            q = qkv[:, :nq].reshape(bc, seq, self.h_local, D).transpose(1, 2)
+            k = qkv[:, nq:nq + nk].reshape(bc, seq, self.kv_local, D).transpose(1, 2)
+            v = qkv[:, nq + nk:].reshape(bc, seq, self.kv_local, D).transpose(1, 2)
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.h_local != self.kv_local)
+            attn[c].copy_(o.transpose(1, 2).reshape(tc, nq))
+            amax.append(ops.absmax(attn[c]))
+        scale_o = torch.stack(amax).max() / (448.0 * 6.0)
+        # segment B: o projection + reduce-scatter, residual, RMSNorm + quantize, all-gather, gate_up, SiLU
+        ys = torch.empty_like(xs)
+        pend = []
+        for c in range(C):
+            qa, sfo = ops.reorder_quantize_x(attn[c], self.o.index, self.o.select_num, mode=16, scale=scale_o)
+            y = self.o.gemm(qa, sfo, scale_o)
+            pend.append((y, dist.reduce_scatter_tensor(ys[c], y, op=dist.ReduceOp.SUM, group=self.group, async_op=True)))
+        hs = torch.empty_like(xs)
+        gathers = []
+        for c in range(C):
+            pend[c][1].wait()
+            torch.add(xs[c], ys[c], out=hs[c])
+            a_s, sfa_s = ops.rmsnorm_quantize_x(hs[c], self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
+            gathers.append(gather_async(a_s, sfa_s))
+        acts, amax = [], []
+        for c in range(C):
+            a, sfa, works = gathers[c]
+            for w in works:
+                w.wait()
+            act, am = ops.silu_mul(self.gate_up.gemm(a, sfa))
+            acts.append(act)
+            amax.append(am)
+        scale_d = torch.stack(amax).max() / (448.0 * 6.0)
+        # segment C: down projection + reduce-scatter, residual
+        pend = []
+        for c in range(C):
+            qd, sfd = ops.reorder_quantize_x(acts[c], self.down.index, self.down.select_num, mode=16, scale=scale_d)
+            y = self.down.gemm(qd, sfd, scale_d)
+            pend.append((y, dist.reduce_scatter_tensor(ys[c], y, op=dist.ReduceOp.SUM, group=self.group, async_op=True)))
+        out = torch.empty_like(xs)
+        for c in range(C):
+            pend[c][1].wait()
+            torch.add(hs[c], ys[c], out=out[c])
+        return out.reshape(C * rc, cfg.hidden)
+
     def _dist_ready(self) -> bool:
         import torch.distributed as dist
         return dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1

@@ -59,6 +59,16 @@ def _worker(rank, world, port, q):
         err_sp = float((y_sp.float() - ref_sp.float()).norm() / ref_sp.float().norm())
         if err_sp > 2e-3:      # (bit-equal with two ranks; a sum of more partials may be ordered differently)
             err_tp = max(err_tp, 1.0 + err_sp)
+        # pipelined sequence-parallel form: 4 runs of one sequence, this rank's slice of every run
+        xb = synth.activations(1024, cfg.hidden, 8, synth.outlier_channels(cfg.hidden, 10, 3)).reshape(4, 256, -1).to(dev)
+        posb = torch.arange(256, device=dev)
+        layer.overlap_rows = 1 << 30
+        y_ref = layer(xb, posb).reshape(1024, -1)
+        own = layer.pipelined_shard_rows(1024, world, rank, 4).to(dev)
+        y_pp = layer.forward_sequence_parallel_pipelined(xb.reshape(1024, -1)[own].contiguous(), 4, 256, posb, 4)
+        err_pp = float((y_pp.float() - y_ref[own].float()).norm() / y_ref[own].float().norm())
+        if err_pp > 2e-3:
+            err_tp = max(err_tp, 2.0 + err_pp)
         # --- expert-parallel MoE block: same per-expert batches as one rank owning every expert
         mcfg = MoEConfig(hidden=1024, ffn=2048, n_experts=4, top_k=2, select_num=64)
         MW = random_moe_weights(mcfg, 0)
