@@ -32,6 +32,7 @@ SIGNATURES = {
     "arcq_status_string": (C.c_char_p, [_i32]),
     "arcq_last_cuda_error": (_i32, []),
     "arcq_version": (_i32, []),
+    "arcq_set_sm_limit": (_i32, [_i32]),
     "arcq_sf_bytes": (C.c_size_t, [_i64, _i64]),
     "arcq_reference_mode": (_i32, [_i32]),
     "arcq_reorder_quantize_x": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),

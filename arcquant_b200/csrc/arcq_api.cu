@@ -2,6 +2,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "arcq_internal.h"
@@ -15,6 +16,9 @@ int cuda_fail(cudaError_t e) {
   (void)cudaGetLastError();  // clear the sticky "last error" of non-fatal failures
   return ARCQ_ERR_CUDA;
 }
+
+// Upper bound on the SMs the persistent kernels spread over (0 = all of them), see arcq_set_sm_limit.
+static std::atomic<int> g_sm_limit{0};
 
 int get_device_info(DeviceInfo* out) {
   static std::mutex mu;
@@ -33,6 +37,8 @@ int get_device_info(DeviceInfo* out) {
     have[dev] = true;
   }
   *out = cache[dev];
+  const int limit = g_sm_limit.load(std::memory_order_relaxed);
+  if (limit > 0 && limit < out->num_sms) out->num_sms = limit;
   return ARCQ_OK;
 }
 
@@ -71,7 +77,12 @@ const char* arcq_status_string(int status) {
 
 int arcq_last_cuda_error(void) { return g_last_cuda_error; }
 
-int arcq_version(void) { return 100; }
+int arcq_version(void) { return 200; }
+
+int arcq_set_sm_limit(int sms) {
+  if (sms < 0) sms = 0;
+  return g_sm_limit.exchange(sms, std::memory_order_relaxed);
+}
 
 size_t arcq_sf_bytes(int64_t rows, int64_t k_eff) {
   if (rows < 0 || k_eff < 0) return 0;

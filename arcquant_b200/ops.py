@@ -54,6 +54,12 @@ def _require(t: torch.Tensor, dtype, name: str) -> None:
         raise RuntimeError(f"{name} must be contiguous")
 
 
+def set_sm_limit(sms: int) -> int:
+    """Later launches use at most `sms` SMs (0 = all), so that collectives on other streams find room to
+    run beside them; returns the previous limit."""
+    return int(_lib.load().arcq_set_sm_limit(int(sms)))
+
+
 def sf_bytes(rows: int, k_eff: int) -> int:
     return int(_lib.load().arcq_sf_bytes(rows, k_eff))
 

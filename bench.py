@@ -499,6 +499,30 @@ def layer_roofline(world: int, hbm_peak: float, tf_peak: float, sp: bool):
     return t
 
 
+NCCL_CTAS = int(os.environ.get("ARCQ_BENCH_NCCL_CTAS", "16"))      # CTAs NCCL may use per collective
+SM_RESERVE = int(os.environ.get("ARCQ_BENCH_SM_RESERVE", "16"))    # SMs the compute kernels leave to them
+
+
+SP_CHUNKS = int(os.environ.get("ARCQ_BENCH_CHUNKS", "4"))          # runs of the pipelined sequence-parallel form
+
+
+def init_nccl(dist, dev):
+    """NCCL process group whose collectives use a bounded number of CTAs: the layer's compute kernels are
+    told to leave that many SMs free (`ops.set_sm_limit`), so a collective on NCCL's stream runs beside
+    them instead of waiting for a persistent kernel to drain."""
+    opts = None
+    try:
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.config.max_ctas = NCCL_CTAS
+        opts.config.min_ctas = min(NCCL_CTAS, 4)
+    except Exception:
+        opts = None
+    if opts is not None:
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
+    else:
+        dist.init_process_group("nccl", device_id=dev)
+
+
 def build_layer(dev, world, rank, group=None):
     from arcquant_b200.llama_layer import (LlamaLayerConfig, QLlamaDecoderLayerTP, random_layer_weights,
                                            random_reorder_indices)
@@ -525,13 +549,18 @@ def layer_measure(dev, world, rank, steps, hbm_peak, tf_peak):
     x3 = x.reshape(LAYER_BATCH, LAYER_SEQ, cfg.hidden)
     rows = T // world
     sp = world > 1
-    chunks = 4
+    chunks = SP_CHUNKS
     # this rank's rows of the residual stream (static graph input): its slice of each of the `chunks` runs
     own = layer.pipelined_shard_rows(T, world, rank, chunks).to(dev) if sp else None
     xs = x[own].clone() if sp else None
     step = (lambda: layer.forward_sequence_parallel_pipelined(xs, LAYER_BATCH, LAYER_SEQ, pos, chunks)) if sp else \
         (lambda: layer(x3, pos))
     res = {"tokens": T, "parallelism": f"tp{world}" + ("+sp" if sp else ""), "scaling": "strong"}
+    if sp and SM_RESERVE > 0:
+        from arcquant_b200 import ops
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        ops.set_sm_limit(sms - SM_RESERVE)
+        res["sm_carve_out"] = {"compute_sms": sms - SM_RESERVE, "nccl_max_ctas": NCCL_CTAS}
     if sp:
         res["form"] = (f"sequence-parallel, {chunks} runs of {LAYER_BATCH // chunks} sequences: all-gathers of packed codes "
                        "and reduce-scatters (NCCL, asynchronous) overlapped with the neighbouring runs' compute")
@@ -580,6 +609,9 @@ def layer_measure(dev, world, rank, steps, hbm_peak, tf_peak):
     e2e_ms = max_over_ranks(time_ms(e2e_step, max(3, steps // 2)), dev)
     res["e2e"] = {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                   "h2d_bytes_per_step": int(hin.numel() * 2) * world, "d2h_bytes_per_step": int(hout.numel() * 2) * world}
+    if sp and SM_RESERVE > 0:
+        from arcquant_b200 import ops
+        ops.set_sm_limit(0)
     return res
 
 
@@ -694,7 +726,7 @@ def run_side_workload(args):
     hbm_peak, tf_peak, peak_kind = measured_peaks()
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        init_nccl(dist, dev)
     if args.workload in ("layer", "moe"):
         fn = layer_measure if args.workload == "layer" else moe_measure
         res = fn(dev, world, rank, args.steps, hbm_peak, tf_peak)
@@ -857,7 +889,7 @@ def run_ours(args):
         import torch.distributed as dist_mod
 
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=dev)
+        init_nccl(dist, dev)
     hbm_peak, tf_peak, peak_kind = measured_peaks()
     warm = max(args.warmup, 3)
 

@@ -63,6 +63,14 @@ int arcq_last_cuda_error(void);
 /* Library version: major*10000 + minor*100 + patch. */
 int arcq_version(void);
 
+/* The quantizer and GEMM kernels are persistent: by default every launch spreads over all SMs of the
+ * device, with one CTA that fills its SM.  A collective that should run at the same time on another
+ * stream (an NCCL all-gather or reduce-scatter under the next GEMM) then finds no SM to start on.
+ * arcq_set_sm_limit(n) makes every later launch of this process use at most n SMs (0 = all), leaving the
+ * rest to whatever else runs; it returns the previous limit.  Process-wide, not per stream; a CUDA graph
+ * keeps the grid sizes it was captured with.  No counterpart in the reference (it has no collectives). */
+int arcq_set_sm_limit(int sms);
+
 /* Bytes to allocate for the scale-factor buffer of `rows` rows and K_eff =
  * KQ+KE columns.  Never smaller than the reference's own size
  * (rows/128+1)*128*K_eff/16 (kernels/src/bindings.cpp:83-95) and never smaller

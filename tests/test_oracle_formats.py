@@ -70,3 +70,35 @@ def test_rsqrt_rn_is_nearest():
         err = abs(Decimal(float(r)) - exact)
         for nb in (np.nextafter(r, np.float32(np.inf)), np.nextafter(r, np.float32(0))):
             assert err <= abs(Decimal(float(nb)) - exact)
+
+
+def test_formats_against_the_dependency_itself(golden_dir):
+    """The same conversions as answered by CUTLASS's own host-side converters - the templates the
+    reference's kernels call (kernels/src/reorder.cu:98-104 of ARCQuant: NumericConverter<float_e2m1_t |
+    float_ue4m3_t, float, round_to_nearest>) - tabulated by tests/golden/make_kat_cutlass.py.  The oracle
+    is held to them on the domain the kernels feed the converters: |x| <= 6 for e2m1 (the kernels clamp
+    first, reorder.cu:153-164) and [2^-9, 448] for the block scale (reorder.cu:138)."""
+    kat = json.load(open(os.path.join(golden_dir, "kat_formats_cutlass.json")))
+    L = O.lib()
+    n = 0
+    for bits, code in kat["e2m1_encode"]:
+        x = _f(bits)
+        if abs(x) <= 6.0:
+            assert L.arcq_e2m1_encode(x) == code, (x, code)
+            n += 1
+    assert n > 4000
+    n = 0
+    for bits, code in kat["ue4m3_encode"]:
+        x = _f(bits)
+        if 0.001953125 <= x <= 448.0:
+            assert L.arcq_ue4m3_encode(x) == code, (x, code)
+            n += 1
+    assert n > 3000
+    for code, bits in kat["ue4m3_decode"]:
+        assert L.arcq_ue4m3_decode(code) == _f(bits)
+    # and the two tables agree with one another wherever both have an entry
+    exact = json.load(open(os.path.join(golden_dir, "kat_formats.json")))
+    lib = dict(map(tuple, kat["e2m1_encode"]))
+    assert all(lib[b] == c for b, c in exact["e2m1_encode"] if abs(_f(b)) <= 6.0)
+    lib = dict(map(tuple, kat["ue4m3_encode"]))
+    assert all(lib[b] == c for b, c in exact["ue4m3_encode"] if 0.001953125 <= _f(b) <= 448.0)
