@@ -49,7 +49,9 @@ SIGNATURES = {
     "arcq_absmax_bf16": (_i32, [_vp, _i64, _vp, _i32, _vp]),
     "arcq_rope_bf16": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp]),
     "arcq_silu_mul_bf16": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
+    "arcq_calib_stats_bf16": (_i32, [_vp, _i64, _i32, _vp, _vp, _vp]),
     "arcq_moe_layout": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "arcq_silu_mul_grouped_bf16": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp, _i32, _vp, _vp]),
     "arcq_absmax_grouped_bf16": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp]),
     "arcq_reorder_quantize_x_grouped": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
     "arcq_matmul_nvfp4_grouped": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _vp, _vp, _vp, _vp]),

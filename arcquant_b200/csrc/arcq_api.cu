@@ -229,6 +229,16 @@ int arcq_moe_combine_bf16(const void* y, const int32_t* pos, const void* weights
   return launch_moe_combine(y, pos, weights, out, tokens, hidden, top_k, (cudaStream_t)stream);
 }
 
+int arcq_calib_stats_bf16(const void* x, int64_t rows, int K, float* chan_absmax, unsigned long long* above,
+                          void* stream) {
+  if (rows < 0 || K <= 0 || K % 8) return ARCQ_ERR_BAD_SHAPE;
+  if (K > 32768) return ARCQ_ERR_UNSUPPORTED_K;
+  if (rows == 0) return ARCQ_OK;
+  if (!x || !chan_absmax) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(x)) return ARCQ_ERR_ALIGNMENT;
+  return launch_calib_stats(x, rows, K, chan_absmax, above, (cudaStream_t)stream);
+}
+
 int arcq_moe_layout(const int64_t* slot_group, int n, int ngroups, int tile, int rows_bound, int div, int32_t* dest,
                     int32_t* row_map, int32_t* groups, int32_t* tile_group, void* stream) {
   if (n < 0 || n > (1 << 20) || ngroups < 1 || ngroups > 64 || tile < 1 || div < 1 || rows_bound % tile ||
@@ -237,6 +247,15 @@ int arcq_moe_layout(const int64_t* slot_group, int n, int ngroups, int tile, int
   if ((n > 0 && !slot_group) || !dest || !row_map || !groups || !tile_group) return ARCQ_ERR_NULL_POINTER;
   return launch_moe_layout(reinterpret_cast<const long long*>(slot_group), n, ngroups, tile, rows_bound, div, dest,
                            row_map, groups, tile_group, (cudaStream_t)stream);
+}
+
+int arcq_silu_mul_grouped_bf16(const void* gate_up, void* out, int64_t rows_bound, int F, const int32_t* tile_group,
+                               const int32_t* groups, int ngroups, float* amax, void* stream) {
+  if (rows_bound < 0 || rows_bound % 256 || F <= 0 || F % 256 || ngroups < 1 || ngroups > 64) return ARCQ_ERR_BAD_SHAPE;
+  if (rows_bound == 0) return ARCQ_OK;
+  if (!gate_up || !out || !tile_group || !groups) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(gate_up) || !aligned16(out)) return ARCQ_ERR_ALIGNMENT;
+  return launch_silu_mul_grouped(gate_up, out, rows_bound, F, tile_group, groups, ngroups, amax, (cudaStream_t)stream);
 }
 
 int arcq_absmax_grouped_bf16(const void* x, const int32_t* row_map, const int32_t* groups, int ngroups, int K, float* out,

@@ -58,6 +58,10 @@ int launch_absmax_grouped(const void* x, const int* row_map, const int* groups, 
                           cudaStream_t stream);
 int launch_moe_layout(const long long* slot_group, int n, int ngroups, int tile, int rows_bound, int div, int* dest,
                       int* row_map, int* groups, int* tile_group, cudaStream_t stream);
+int launch_calib_stats(const void* x, int64_t rows, int K, float* chan_absmax, unsigned long long* above,
+                       cudaStream_t stream);
+int launch_silu_mul_grouped(const void* gu, void* out, int64_t rows, int F, const int* tile_group, const int* groups,
+                            int ngroups, float* amax, cudaStream_t stream);
 int gemm_poll_error();
 // Same for the bounded waits of the warp-specialised quantizer.
 int quant_poll_error();

@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <math.h>
 #include <stdlib.h>
 
 #include "arcq_internal.h"
@@ -159,6 +160,65 @@ __global__ void __launch_bounds__(1024, 1) arcq_silu_mul_table_kernel(const uint
   }
 }
 
+// SiLU(gate) * up over grouped rows (see arcq_silu_mul_grouped_bf16): tiles of 256 rows without rows are
+// skipped, padding rows inside a tile are computed but kept out of the maxima, and amax[e] receives max|out|
+// over the rows of run e.  F/8 is a multiple of 32, so the 32 vectors a warp takes per step lie in one row
+// and the warp's run is uniform: its running maximum is flushed (one atomic per warp) when the run changes.
+template <bool TABLE>
+__global__ void __launch_bounds__(1024, 1)
+arcq_silu_mul_grouped_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ out, long long rows, int F,
+                             const int* __restrict__ tile_group, const int* __restrict__ groups, int ngroups,
+                             unsigned int* amax) {
+  extern __shared__ __align__(16) uint16_t tab[];
+  if (TABLE) {
+    const uint4* src = reinterpret_cast<const uint4*>(g_silu_table);
+    uint4* dst = reinterpret_cast<uint4*>(tab);
+    for (int i = threadIdx.x; i < 65536 / 8; i += blockDim.x) dst[i] = src[i];
+    __syncthreads();
+  }
+  const int vec_per_row = F >> 3;
+  const long long total = rows * vec_per_row;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  uint32_t m = 0;
+  int cur = -1;
+  auto flush = [&]() {
+    if (cur >= 0 && amax != nullptr) {
+      uint32_t r = max(m & 0xffffu, m >> 16);
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) r = max(r, __shfl_xor_sync(0xffffffffu, r, d));
+      if ((threadIdx.x & 31) == 0 && r) atomicMax(amax + cur, r << 16);
+    }
+    m = 0;
+  };
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += step) {
+    const long long t = i / vec_per_row;
+    const int v = (int)(i - t * vec_per_row);
+    const int e = __ldg(tile_group + (t >> 8));
+    if (e < 0) continue;                                   // (warp-uniform)
+    if (e != cur) { flush(); cur = e; }
+    const bool valid = t < (long long)__ldg(groups + e) + __ldg(groups + ngroups + e);
+    const uint16_t* row = gu + t * 2LL * F + v * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(row), u = *reinterpret_cast<const uint4*>(row + F);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float sa, sb;
+      if (TABLE) {
+        sa = __uint_as_float((uint32_t)tab[gw[k] & 0xffffu] << 16);
+        sb = __uint_as_float((uint32_t)tab[gw[k] >> 16] << 16);
+      } else {
+        sa = silu_bf16(lo_f(gw[k]));
+        sb = silu_bf16(hi_f(gw[k]));
+      }
+      o[k] = pack2(__fmul_rn(sa, lo_f(uw[k])), __fmul_rn(sb, hi_f(uw[k])));
+      if (valid) asm("max.u16x2 %0, %0, %1;" : "+r"(m) : "r"(o[k] & 0x7fff7fffu));
+    }
+    *reinterpret_cast<uint4*>(out + t * (long long)F + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  flush();
+}
+
 // out[t] = sum over the k routed copies of token t of bf16(y[pos[t][j]] * w[t][j]), accumulated in the
 // output type in the order j = 0..k-1 (a bf16 index_add over the copies adds them in bf16 as well; with
 // k = 2 the order does not matter).  One thread = 8 channels of one token.
@@ -294,7 +354,96 @@ arcq_moe_layout_kernel(const long long* __restrict__ slot_group, int n, int ngro
   }
 }
 
+// Calibration statistics in one pass over the activations (utilize.py:108 and :546-547 of ARCQuant):
+// per-channel running max|x| and the number of elements larger than an eighth of their row's (signed)
+// maximum.  A CTA of 256 threads walks rows b, b + grid, ...; thread t owns the 16-byte chunks t, t + 256,
+// ... of every row, so its channels' maxima stay in registers and leave with one atomic each at the end.
+template <int CPT>
+__global__ void __launch_bounds__(256) arcq_calib_stats_kernel(const uint16_t* __restrict__ x, long long rows, int K,
+                                                               unsigned int* chan_absmax, unsigned long long* above) {
+  __shared__ float s_max[2][8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nchunks = K >> 3;
+  uint32_t cmax[CPT][4];
+#pragma unroll
+  for (int j = 0; j < CPT; ++j) cmax[j][0] = cmax[j][1] = cmax[j][2] = cmax[j][3] = 0;
+  unsigned long long count = 0;
+  int buf = 0;
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x, buf ^= 1) {
+    const uint4* row = reinterpret_cast<const uint4*>(x + r * (long long)K);
+    uint4 v[CPT];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) {
+      const int c = tid + j * 256;
+      v[j] = c < nchunks ? __ldg(row + c) : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);   // -inf
+      const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        m = fmaxf(m, fmaxf(lo_f(w[k]), hi_f(w[k])));
+        if (c < nchunks) asm("max.u16x2 %0, %0, %1;" : "+r"(cmax[j][k]) : "r"(w[k] & 0x7fff7fffu));
+      }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    if (lane == 0) s_max[buf][warp] = m;
+    __syncthreads();
+    float rm = s_max[buf][0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) rm = fmaxf(rm, s_max[buf][k]);
+    // the threshold in the tensor's own type, as torch computes `max * 0.125` on a bf16 tensor
+    const float thr = __uint_as_float(pack2(__fmul_rn(rm, 0.125f), 0.f) << 16);
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) {
+      if (tid + j * 256 < nchunks) {
+        const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) count += (lo_f(w[k]) > thr ? 1 : 0) + (hi_f(w[k]) > thr ? 1 : 0);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < CPT; ++j) {
+    const int c = tid + j * 256;
+    if (c < nchunks) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        atomicMax(chan_absmax + 8 * c + 2 * k, (cmax[j][k] & 0xffffu) << 16);
+        atomicMax(chan_absmax + 8 * c + 2 * k + 1, cmax[j][k] & 0xffff0000u);
+      }
+    }
+  }
+  if (above != nullptr) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) count += __shfl_xor_sync(0xffffffffu, count, d);
+    if (lane == 0 && count) atomicAdd(above, count);
+  }
+}
+
 }  // namespace
+
+int launch_calib_stats(const void* x, int64_t rows, int K, float* chan_absmax, unsigned long long* above,
+                       cudaStream_t stream) {
+  if (rows == 0) return ARCQ_OK;
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  long long grid = (long long)di.num_sms * 8;
+  if (grid > rows) grid = rows;
+  const int cpt = (K / 8 + 255) / 256;
+  auto xs = static_cast<const uint16_t*>(x);
+  auto cm = reinterpret_cast<unsigned int*>(chan_absmax);
+#define ARCQ_CALIB(CPT_) arcq_calib_stats_kernel<CPT_><<<(unsigned)grid, 256, 0, stream>>>(xs, rows, K, cm, above)
+  if (cpt <= 1) ARCQ_CALIB(1);
+  else if (cpt <= 2) ARCQ_CALIB(2);
+  else if (cpt <= 4) ARCQ_CALIB(4);
+  else if (cpt <= 8) ARCQ_CALIB(8);
+  else if (cpt <= 16) ARCQ_CALIB(16);
+  else return ARCQ_ERR_UNSUPPORTED_K;
+#undef ARCQ_CALIB
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
 
 int launch_moe_layout(const long long* slot_group, int n, int ngroups, int tile, int rows_bound, int div, int* dest,
                       int* row_map, int* groups, int* tile_group, cudaStream_t stream) {
@@ -345,6 +494,36 @@ int launch_rope(void* x, const float* cos_t, const float* sin_t, int64_t tokens,
   if (blocks > cap) blocks = cap;
   arcq_rope_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<uint16_t*>(x), cos_t, sin_t, tokens, row_elems, heads,
                                                          dim, seq);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
+
+int launch_silu_mul_grouped(const void* gu, void* out, int64_t rows, int F, const int* tile_group, const int* groups,
+                            int ngroups, float* amax, cudaStream_t stream) {
+  if (amax) ARCQ_CUDA_TRY(cudaMemsetAsync(amax, 0, sizeof(float) * ngroups, stream));
+  if (rows == 0) return ARCQ_OK;
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  const long long total = (long long)rows * (F / 8);
+  auto g = static_cast<const uint16_t*>(gu);
+  auto o = static_cast<uint16_t*>(out);
+  auto am = reinterpret_cast<unsigned int*>(amax);
+  if (total >= (1LL << 21) && di.max_smem_optin >= 131072) {
+    arcq_silu_table_kernel<<<65536 / 256, 256, 0, stream>>>();
+    ARCQ_CUDA_TRY(cudaGetLastError());
+    auto kern = arcq_silu_mul_grouped_kernel<true>;
+    static thread_local int attr_dev = -1;
+    if (attr_dev != di.device) {
+      ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
+      attr_dev = di.device;
+    }
+    kern<<<(unsigned)di.num_sms, 1024, 131072, stream>>>(g, o, rows, F, tile_group, groups, ngroups, am);
+  } else {
+    long long blocks = (total + 1023) / 1024;
+    if (blocks > (long long)di.num_sms * 2) blocks = (long long)di.num_sms * 2;
+    arcq_silu_mul_grouped_kernel<false><<<(unsigned)blocks, 1024, 0, stream>>>(g, o, rows, F, tile_group, groups, ngroups, am);
+  }
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
 }

@@ -123,15 +123,27 @@ class ExpertParallelDispatcher:
     blocks), and lays the rows out by local expert - without a host synchronisation.
 
     capacity: rows one rank may send to one peer (the same number on every rank).  Default: the largest
-    number of routed copies any rank holds at the first call (agreed once with an all-reduce and kept);
-    pass it explicitly when later calls may be larger."""
+    number of routed copies any rank holds at the first call (agreed once with an all-reduce and kept) -
+    the worst case, every copy of a rank going to one peer, so nothing can overflow; pass it explicitly
+    when later calls may be larger.
+    capacity_factor: instead of the worst case, `capacity_factor` times the even share (copies / ranks,
+    rounded up to 128 rows): the all-to-alls then move that much less padding.  Copies beyond a block's
+    capacity are dropped (they contribute zero) and `overflowed()` reports it - the caller then repeats the
+    step with a dispatcher of larger capacity."""
 
-    def __init__(self, n_experts: int, ep_rank: int = 0, ep_size: int = 1, group=None, capacity: int | None = None):
+    def __init__(self, n_experts: int, ep_rank: int = 0, ep_size: int = 1, group=None, capacity: int | None = None,
+                 capacity_factor: float | None = None):
         if n_experts % ep_size:
             raise ValueError("experts must split evenly over the expert-parallel group")
         self.E, self.rank, self.ep, self.group = n_experts, ep_rank, ep_size, group
         self.e_local = n_experts // ep_size
         self.capacity = capacity
+        self.capacity_factor = capacity_factor
+        self._overflow = None          # device flag, sticky
+
+    def overflowed(self) -> bool:
+        """True if any call so far dropped copies for lack of capacity (reads the device: synchronises)."""
+        return self._overflow is not None and bool(self._overflow.item())
 
     def _agree_capacity(self, n_copies: int, device) -> int:
         import torch.distributed as dist
@@ -140,7 +152,11 @@ class ExpertParallelDispatcher:
             t = torch.tensor([n_copies], dtype=torch.int64, device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
             self.capacity = int(t.item())
-        if n_copies > self.capacity:
+            if self.capacity_factor is not None:
+                share = -(-self.capacity // self.ep)
+                self.capacity = min(self.capacity, -(-int(share * self.capacity_factor) // 128) * 128)
+                n_copies = 0          # (a factor below the worst case can overflow: flagged, not raised)
+        if self.capacity_factor is None and n_copies > self.capacity:
             raise ValueError(f"{n_copies} routed copies exceed the dispatcher's capacity {self.capacity}; "
                              "construct it with capacity=<largest number of copies per rank>")
         return self.capacity
@@ -165,12 +181,19 @@ class ExpertParallelDispatcher:
         per_rank = counts.reshape(self.ep, self.e_local).sum(1)
         rank_start = torch.cumsum(per_rank, 0) - per_rank
         dst = torch.div(sorted_e, self.e_local, rounding_mode="floor")
-        send_slot_sorted = dst * cap + torch.arange(n, device=x.device) - rank_start[dst]
+        in_block = torch.arange(n, device=x.device) - rank_start[dst]
+        kept = in_block < cap                                     # (always, at worst-case capacity)
+        if self.capacity_factor is not None:
+            over = (~kept).any()
+            self._overflow = over if self._overflow is None else (self._overflow | over)
+            counts = _counts(torch.where(kept, sorted_e, torch.full_like(sorted_e, self.E)), self.E)
+        dummy = self.ep * cap                                      # where dropped copies point: a row of zeros
+        send_slot_sorted = torch.where(kept, dst * cap + in_block, torch.full_like(in_block, dummy))
         copy_slot = torch.empty_like(send_slot_sorted)
         copy_slot[order] = send_slot_sorted                       # slot of every copy, in copy order
-        slot_token = torch.zeros(self.ep * cap, dtype=torch.int64, device=x.device)
+        slot_token = torch.zeros(self.ep * cap + 1, dtype=torch.int64, device=x.device)
         slot_token[send_slot_sorted] = torch.div(order, k, rounding_mode="floor")
-        send = x.index_select(0, slot_token)
+        send = x.index_select(0, slot_token[:dummy])
         recv_counts = torch.empty_like(counts)
         dist.all_to_all_single(recv_counts, counts, group=self.group)      # [source rank, local expert]
         recv = torch.empty_like(send)
@@ -191,8 +214,8 @@ class ExpertParallelDispatcher:
         T, k = st["T"], st["k"]
         if self.ep > 1:
             back = y_rows.index_select(0, st["slot_row"])                  # slot order again (padding: any row)
-            ret = torch.empty_like(back)
-            dist.all_to_all_single(ret, back, group=self.group)
+            ret = back.new_zeros((back.shape[0] + 1, back.shape[1]))       # last row: what dropped copies read
+            dist.all_to_all_single(ret[:-1], back, group=self.group)
         else:
             ret = y_rows
         pos = st["copy_row"].reshape(T, k)                                  # row of `ret` holding copy j of token t
@@ -239,12 +262,12 @@ def _stack(linears):
 
 class QMixtralMoEBlockEP(torch.nn.Module):
     def __init__(self, cfg: MoEConfig, weights: dict, ep_rank: int = 0, ep_size: int = 1, group=None, device="cuda",
-                 capacity: int | None = None):
+                 capacity: int | None = None, capacity_factor: float | None = None):
         super().__init__()
         from .llama_layer import PackedLinear
 
         self.cfg = cfg
-        self.dispatcher = ExpertParallelDispatcher(cfg.n_experts, ep_rank, ep_size, group, capacity)
+        self.dispatcher = ExpertParallelDispatcher(cfg.n_experts, ep_rank, ep_size, group, capacity, capacity_factor)
         dev = torch.device(device)
         self.router = weights["router"].to(dev)
         self.experts = []
@@ -264,15 +287,19 @@ class QMixtralMoEBlockEP(torch.nn.Module):
 
     @torch.no_grad()
     def expert_forward_grouped(self, batch: RoutedBatch) -> torch.Tensor:
-        """All local experts in seven launches: [rows_bound, hidden] in the padded layout of `batch`."""
+        """All local experts in six launches: [rows_bound, hidden] in the padded layout of `batch`."""
         cfg, E = self.cfg, self.dispatcher.e_local
         ke = cfg.select_num
         s1 = ops.absmax_grouped(batch.src, batch.row_map, batch.groups, E) / (448.0 * 6.0)   # per-expert scales
         a, sfa = ops.reorder_quantize_x_grouped(batch.src, batch.row_map, s1, self.gu_index, batch.groups,
                                                 batch.rows_bound, ke)
         h = ops.matmul_grouped(a, self.gu_W, sfa, self.gu_SF, batch.tile_group, E, 2 * cfg.ffn, s1, self.gu_scale)
-        act, _ = ops.silu_mul(h, with_amax=False)
-        s2 = ops.absmax_grouped(act, None, batch.groups, E) / (448.0 * 6.0)
+        if cfg.ffn % 256 == 0:      # SiLU * up and the per-expert maxima in one pass, empty tiles skipped
+            act, amax2 = ops.silu_mul_grouped(h, batch.tile_group, batch.groups, E)
+        else:
+            act, _ = ops.silu_mul(h, with_amax=False)
+            amax2 = ops.absmax_grouped(act, None, batch.groups, E)
+        s2 = amax2 / (448.0 * 6.0)
         b, sfb = ops.reorder_quantize_x_grouped(act, None, s2, self.dn_index, batch.groups, batch.rows_bound, ke)
         return ops.matmul_grouped(b, self.dn_W, sfb, self.dn_SF, batch.tile_group, E, cfg.hidden, s2, self.dn_scale)
 

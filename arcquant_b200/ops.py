@@ -230,6 +230,24 @@ def silu_mul(gate_up: torch.Tensor, with_amax: bool = True):
     return out, amax
 
 
+def calib_stats(x: torch.Tensor, chan_absmax: torch.Tensor, above: torch.Tensor | None = None) -> None:
+    """Accumulates the calibration statistics of x [..., K] (bf16, CUDA) in one pass: per-channel running
+    max|x| into chan_absmax (fp32 [K]) and, if given, the count of elements above an eighth of their row's
+    maximum into `above` (int64 scalar tensor)."""
+    lib = _lib.load()
+    x2 = x.reshape(-1, x.shape[-1])
+    _require(x2, torch.bfloat16, "input")
+    _require(chan_absmax, torch.float32, "chan_absmax")
+    if chan_absmax.numel() != x2.shape[1]:
+        raise RuntimeError("chan_absmax must have one entry per channel")
+    if above is not None:
+        _require(above, torch.int64, "above")
+    with torch.cuda.device(x.device):
+        rc = lib.arcq_calib_stats_bf16(x2.data_ptr(), x2.shape[0], x2.shape[1], chan_absmax.data_ptr(),
+                                       None if above is None else above.data_ptr(), _stream())
+    _lib.check(rc, "calib_stats")
+
+
 def moe_layout(slot_group: torch.Tensor, ngroups: int, tile: int, rows_bound: int, div: int = 1):
     """Padded layout of routed rows in one launch: (dest int32 [n], row_map int32 [rows_bound], groups int32
     [2*ngroups], tile_group int32 [rows_bound/tile]); see `arcq_moe_layout` in arcq.h."""
@@ -245,6 +263,23 @@ def moe_layout(slot_group: torch.Tensor, ngroups: int, tile: int, rows_bound: in
                                  row_map.data_ptr(), groups.data_ptr(), tile_group.data_ptr(), _stream())
     _lib.check(rc, "moe_layout")
     return dest, row_map, groups, tile_group
+
+
+def silu_mul_grouped(gate_up: torch.Tensor, tile_group: torch.Tensor, groups: torch.Tensor, ngroups: int):
+    """(out bf16 [rows, F], amax fp32 [ngroups]) for grouped rows of gate_up [rows, 2F]: empty 256-row tiles
+    are skipped, amax[e] = max|out| over the rows of run e."""
+    lib = _lib.load()
+    _require(gate_up, torch.bfloat16, "gate_up")
+    _require(tile_group, torch.int32, "tile_group")
+    _require(groups, torch.int32, "groups")
+    rows, f2 = gate_up.shape
+    out = torch.empty((rows, f2 // 2), dtype=torch.bfloat16, device=gate_up.device)
+    amax = torch.empty((ngroups,), dtype=torch.float32, device=gate_up.device)
+    with torch.cuda.device(gate_up.device):
+        rc = lib.arcq_silu_mul_grouped_bf16(gate_up.data_ptr(), out.data_ptr(), rows, f2 // 2, tile_group.data_ptr(),
+                                            groups.data_ptr(), ngroups, amax.data_ptr(), _stream())
+    _lib.check(rc, "silu_mul_grouped")
+    return out, amax
 
 
 def absmax_grouped(x: torch.Tensor, row_map, groups: torch.Tensor, ngroups: int) -> torch.Tensor:

@@ -499,28 +499,34 @@ def layer_roofline(world: int, hbm_peak: float, tf_peak: float, sp: bool):
     return t
 
 
-NCCL_CTAS = int(os.environ.get("ARCQ_BENCH_NCCL_CTAS", "16"))      # CTAs NCCL may use per collective
-SM_RESERVE = int(os.environ.get("ARCQ_BENCH_SM_RESERVE", "16"))    # SMs the compute kernels leave to them
+NCCL_CTAS = int(os.environ.get("ARCQ_BENCH_NCCL_CTAS", "0"))       # CTAs NCCL may use per collective (0 = its own choice)
+SM_RESERVE = int(os.environ.get("ARCQ_BENCH_SM_RESERVE", "0"))     # SMs the compute kernels leave to them
 
 
-SP_CHUNKS = int(os.environ.get("ARCQ_BENCH_CHUNKS", "4"))          # runs of the pipelined sequence-parallel form
+SP_CHUNKS = int(os.environ.get("ARCQ_BENCH_CHUNKS", "2"))          # runs of the pipelined sequence-parallel form
 
 
 def init_nccl(dist, dev):
-    """NCCL process group whose collectives use a bounded number of CTAs: the layer's compute kernels are
-    told to leave that many SMs free (`ops.set_sm_limit`), so a collective on NCCL's stream runs beside
-    them instead of waiting for a persistent kernel to drain."""
+    """NCCL process group.  ARCQ_BENCH_NCCL_CTAS / ARCQ_BENCH_SM_RESERVE (tuning runs of the pipelined form):
+    bound the CTAs of a collective and tell the compute kernels to leave that many SMs free
+    (`ops.set_sm_limit`), so that a collective on NCCL's stream runs beside a persistent kernel."""
     opts = None
-    try:
-        opts = dist.ProcessGroupNCCL.Options()
-        opts.config.max_ctas = NCCL_CTAS
-        opts.config.min_ctas = min(NCCL_CTAS, 4)
-    except Exception:
-        opts = None
+    if NCCL_CTAS > 0:
+        try:
+            opts = dist.ProcessGroupNCCL.Options()
+            opts.config.max_ctas = NCCL_CTAS
+            opts.config.min_ctas = min(NCCL_CTAS, 4)
+        except Exception:
+            opts = None
     if opts is not None:
         dist.init_process_group("nccl", device_id=dev, pg_options=opts)
     else:
         dist.init_process_group("nccl", device_id=dev)
+    if SM_RESERVE > 0:
+        import torch
+
+        from arcquant_b200 import ops
+        ops.set_sm_limit(torch.cuda.get_device_properties(dev).multi_processor_count - SM_RESERVE)
 
 
 def build_layer(dev, world, rank, group=None):
@@ -549,43 +555,41 @@ def layer_measure(dev, world, rank, steps, hbm_peak, tf_peak):
     x3 = x.reshape(LAYER_BATCH, LAYER_SEQ, cfg.hidden)
     rows = T // world
     sp = world > 1
-    chunks = SP_CHUNKS
-    # this rank's rows of the residual stream (static graph input): its slice of each of the `chunks` runs
-    own = layer.pipelined_shard_rows(T, world, rank, chunks).to(dev) if sp else None
-    xs = x[own].clone() if sp else None
-    step = (lambda: layer.forward_sequence_parallel_pipelined(xs, LAYER_BATCH, LAYER_SEQ, pos, chunks)) if sp else \
-        (lambda: layer(x3, pos))
+    xs = x[rank * rows:(rank + 1) * rows].clone() if sp else None      # this rank's run of tokens (static graph input)
+    step = (lambda: layer.forward_sequence_parallel(xs, LAYER_BATCH, LAYER_SEQ, pos)) if sp else (lambda: layer(x3, pos))
     res = {"tokens": T, "parallelism": f"tp{world}" + ("+sp" if sp else ""), "scaling": "strong"}
-    if sp and SM_RESERVE > 0:
-        from arcquant_b200 import ops
-        sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        ops.set_sm_limit(sms - SM_RESERVE)
-        res["sm_carve_out"] = {"compute_sms": sms - SM_RESERVE, "nccl_max_ctas": NCCL_CTAS}
     if sp:
-        res["form"] = (f"sequence-parallel, {chunks} runs of {LAYER_BATCH // chunks} sequences: all-gathers of packed codes "
-                       "and reduce-scatters (NCCL, asynchronous) overlapped with the neighbouring runs' compute")
+        res["form"] = ("sequence-parallel: residual stream sharded by tokens, RMSNorm + quantize on the shard, all-gather "
+                       "of packed codes and block scales, reduce-scatter after the row-parallel GEMMs")
     res["eager_ms"] = max_over_ranks(time_ms(step, steps), dev)
     graphed = GraphedStep(step)
     res["ms"] = max_over_ranks(time_ms(graphed, steps), dev)
     res["tokens_per_s"] = T / (res["ms"] * 1e-3)
     res["launch"] = "one CUDA graph per step (captured once; NCCL collectives inside)"
-    # per-phase device time of one eager step of the unpipelined form (phases do not overlap there)
-    xc = x[rank * rows:(rank + 1) * rows].contiguous()
-    plain = (lambda: layer.forward_sequence_parallel(xc, LAYER_BATCH, LAYER_SEQ, pos)) if sp else step
+    # per-phase device time of an eager step (phases run one after another on one stream)
     layer.timer = PhaseTimer()
-    plain()
+    step()
     layer.timer.totals()
     for _ in range(3):
-        plain()
+        step()
     tot = layer.timer.totals()
     layer.timer = None
     res["eager_phase_ms"] = {k: v / 3 for k, v in tot.items()}
     if sp:
-        ms_sp = max_over_ranks(time_ms(plain, max(3, steps // 2)), dev)
-        res["unpipelined_sequence_parallel_form"] = {"eager_ms": ms_sp, "tokens_per_s": T / (ms_sp * 1e-3)}
-        res["collective_exposed_ms"] = res["ms"] - sum(v for k, v in res["eager_phase_ms"].items() if k != "collective")
+        ph = res["eager_phase_ms"]
+        res["limiter"] = ("collectives: two reduce-scatters of the bf16 partial sums [16384, 4096] (134 MB each) and two "
+                          "all-gathers of packed codes (39 MB each), %.2f ms of the %.2f ms eager step, not overlapped with "
+                          "compute (the per-tensor scales of the o and down inputs order the phases)" %
+                          (ph.get("collective", 0.0), sum(ph.values())))
         ms_ar = max_over_ranks(time_ms(lambda: layer(x3, pos), max(3, steps // 2)), dev)
         res["all_reduce_form"] = {"eager_ms": ms_ar, "tokens_per_s": T / (ms_ar * 1e-3)}
+        if SP_CHUNKS > 1 and LAYER_BATCH % SP_CHUNKS == 0 and (T // SP_CHUNKS // world) % 128 == 0:
+            # the pipelined form (runs of whole sequences, asynchronous collectives under the neighbours' compute)
+            own = layer.pipelined_shard_rows(T, world, rank, SP_CHUNKS).to(dev)
+            xp = x[own].contiguous()
+            ms_pp = max_over_ranks(time_ms(lambda: layer.forward_sequence_parallel_pipelined(
+                xp, LAYER_BATCH, LAYER_SEQ, pos, SP_CHUNKS), max(3, steps // 2)), dev)
+            res["pipelined_form"] = {"runs": SP_CHUNKS, "eager_ms": ms_pp, "tokens_per_s": T / (ms_pp * 1e-3)}
     rf = layer_roofline(world, hbm_peak, tf_peak, sp)
     res["roofline"] = dict(rf, frac=rf["sum_ms"] / res["ms"], bound="sum of the rooflines of the phases (tensor, hbm, "
                            "nvlink)", achieved_ms=res["ms"])
@@ -609,9 +613,6 @@ def layer_measure(dev, world, rank, steps, hbm_peak, tf_peak):
     e2e_ms = max_over_ranks(time_ms(e2e_step, max(3, steps // 2)), dev)
     res["e2e"] = {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                   "h2d_bytes_per_step": int(hin.numel() * 2) * world, "d2h_bytes_per_step": int(hout.numel() * 2) * world}
-    if sp and SM_RESERVE > 0:
-        from arcquant_b200 import ops
-        ops.set_sm_limit(0)
     return res
 
 
@@ -636,7 +637,10 @@ def moe_measure(dev, world, rank, steps, hbm_peak, tf_peak):
     from arcquant_b200.moe_block import MoEConfig, QMixtralMoEBlockEP, random_moe_weights
 
     cfg = MoEConfig()
-    block = QMixtralMoEBlockEP(cfg, random_moe_weights(cfg, 0), ep_rank=rank, ep_size=world, device=dev)
+    # blocks of twice the even share travel between ranks (the worst case - every copy of a rank to one peer -
+    # would move `world` times the even share); an overflow would be flagged and fails the measurement
+    block = QMixtralMoEBlockEP(cfg, random_moe_weights(cfg, 0), ep_rank=rank, ep_size=world, device=dev,
+                               capacity_factor=2.0 if world > 1 else None)
     x = synth.activations(MOE_TOKENS, cfg.hidden, 11, synth.outlier_channels(cfg.hidden, 41, 1), device=dev)
     lo, hi = rank * MOE_TOKENS // world, (rank + 1) * MOE_TOKENS // world
     xs = x[lo:hi].contiguous()
@@ -653,6 +657,10 @@ def moe_measure(dev, world, rank, steps, hbm_peak, tf_peak):
         res["ms"] = res["eager_ms"]
         res["graph_error"] = repr(exc)[:160]
     res["tokens_per_s"] = MOE_TOKENS / (res["ms"] * 1e-3)
+    if block.dispatcher.overflowed():
+        raise RuntimeError("expert-parallel dispatch dropped copies: capacity factor too small for this routing")
+    if world > 1:
+        res["dispatch"] = f"all-to-all blocks of {block.dispatcher.capacity} rows per peer (2 x the even share)"
     rf = moe_roofline(world, hbm_peak, tf_peak)
     res["roofline"] = dict(rf, frac=rf["sum_ms"] / res["ms"], achieved_ms=res["ms"])
     return res

@@ -215,6 +215,16 @@ int arcq_silu_mul_bf16(const void* gate_up, void* out, int64_t tokens, int F, fl
 int arcq_moe_combine_bf16(const void* y, const int32_t* pos, const void* weights, void* out, int64_t tokens, int hidden,
                           int top_k, void* stream);
 
+/* Calibration statistics of a batch of activations x [rows, K] (bf16) in one pass, accumulated into
+ * running values in device memory (the caller zero-fills them before the first batch):
+ *   chan_absmax [K] fp32: per-channel max |x| - the statistic the reference's get_act_stats keeps with its
+ *     max metric (utilize.py:108) and reorders the channels by (utilize.py:42);
+ *   above (may be NULL): number of elements larger than an eighth of their row's (signed) maximum - the
+ *     numerator of the select_num rule (utilize.py:546-547); the caller divides by rows * K.
+ * Replaces torch's abs / amax / max / compare passes over the same tensor.  K % 8 == 0, K <= 32768. */
+int arcq_calib_stats_bf16(const void* x, int64_t rows, int K, float* chan_absmax, unsigned long long* above,
+                          void* stream);
+
 /* ---- Grouped forms: all experts of a sparse MoE block in one launch ---------------------------------
  * The reference runs its experts one after another from Python, each with its own quantize and GEMM
  * calls on that expert's batch of tokens (model/qMixtralLayer.py:458-471, 524-543).  Here the routed
@@ -247,6 +257,11 @@ int arcq_moe_combine_bf16(const void* y, const int32_t* pos, const void* weights
  * n <= 1 << 20, ngroups <= 64. */
 int arcq_moe_layout(const int64_t* slot_group, int n, int ngroups, int tile, int rows_bound, int div, int32_t* dest,
                     int32_t* row_map, int32_t* groups, int32_t* tile_group, void* stream);
+/* arcq_silu_mul_grouped_bf16: arcq_silu_mul_bf16 over grouped rows: 256-row tiles that tile_group marks
+ *   as empty are skipped altogether, and amax[e] (fp32 [ngroups], may be NULL) receives max|out| over the
+ *   rows of run e - the down projection's per-expert global scale - in the same pass.  F % 256 == 0. */
+int arcq_silu_mul_grouped_bf16(const void* gate_up, void* out, int64_t rows_bound, int F, const int32_t* tile_group,
+                               const int32_t* groups, int ngroups, float* amax, void* stream);
 int arcq_absmax_grouped_bf16(const void* x, const int32_t* row_map, const int32_t* groups, int ngroups, int K,
                              float* out, void* stream);
 int arcq_reorder_quantize_x_grouped(const void* x, const int32_t* row_map, const float* scales,

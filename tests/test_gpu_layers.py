@@ -451,3 +451,30 @@ def test_moe_layout_kernel_equals_the_tensor_formulation(n, e):
     assert want[4] == got[4]
     for a, b in zip(want[:4], got[:4]):
         assert torch.equal(a.long(), b.cpu().long())
+
+
+@pytest.mark.parametrize("k,rows", [(4096, 3000), (14336, 777), (1024, 5000), (28672, 40), (64, 1000)])
+def test_calibration_statistics_in_one_pass(k, rows):
+    """`arcq_calib_stats_bf16` (running per-channel max|x| and the count behind the residual-width rule)
+    against the reference's formulation in eager torch (utilize.py:108, 546-549 of ARCQuant), over two
+    batches; the channel order and the residual width derived from them must be the same."""
+    from arcquant_b200 import calibrate
+
+    out = synth.outlier_channels(k, max(1, k // 100), 3)
+    batches = [synth.activations(rows, k, 20 + i, out, device="cuda") * (1 + i) for i in range(2)]
+    batches[1][5, :8] = torch.tensor([0.0, -0.0, 1e-30, -3e38, 3e38, 1.0, -1.0, 0.5], dtype=torch.bfloat16)
+    stat = calibrate.ChannelAbsMax()
+    for b in batches:
+        stat.update(b)
+    want = torch.stack([b.abs().amax(0).float() for b in batches]).amax(0)
+    assert torch.equal(stat.value, want)
+    assert torch.equal(stat.reorder_index().long().cpu(), torch.argsort(want).cpu())
+    above = sum(int((b > b.max(dim=-1, keepdim=True)[0] * 0.125).sum()) for b in batches)
+    assert int(stat._above) == above
+    allx = torch.cat(batches)
+    assert stat.select_num() == calibrate.select_num_rule(allx)
+    # the eager path (here: a non-contiguous view) accumulates the same numbers
+    eager = calibrate.ChannelAbsMax()
+    for b in batches:
+        eager.update(b.float())
+    assert torch.equal(eager.value, want) and eager.select_num() == stat.select_num()

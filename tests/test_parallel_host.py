@@ -108,7 +108,35 @@ def _moe_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("worker", [_row_parallel_worker, _moe_worker])
+def _moe_overflow_worker(rank, world, port, q):
+    """Blocks of limited capacity: every copy is routed to rank 0's first expert, more than a block holds.
+    The copies that fit are exact, the dropped ones contribute zero, and the dispatcher says so."""
+    _init(rank, world, port)
+    try:
+        E, H, T, k = 4, 16, 200, 2
+        x = torch.randn(T, H, generator=torch.Generator().manual_seed(7 + rank))
+        ids = torch.zeros(T, k, dtype=torch.int64)
+        w = torch.full((T, k), 0.5)
+        d = ExpertParallelDispatcher(E, rank, world, capacity_factor=1.0)
+        batch = d.dispatch(x, ids)
+        assert d.capacity == 256                                           # even share 200, rounded up to 128s
+        rows, owner = batch.rows(), batch.row_expert()
+        y = torch.where(owner[:, None] >= 0, rows * 3.0, torch.full_like(rows, float("nan")))
+        out = d.combine(y, w, batch)
+        kept = torch.arange(T * k).reshape(T, k) < 256                     # copies in token order fill the block
+        ref = (x[:, None, :] * 3.0 * 0.5 * kept[:, :, None]).sum(1)
+        ok = torch.allclose(out, ref, rtol=1e-5, atol=1e-5) and d.overflowed()
+        exact = ExpertParallelDispatcher(E, rank, world)                   # worst-case capacity: nothing dropped
+        b2 = exact.dispatch(x, ids)
+        r2, o2 = b2.rows(), b2.row_expert()
+        out2 = exact.combine(torch.where(o2[:, None] >= 0, r2 * 3.0, torch.full_like(r2, float("nan"))), w, b2)
+        ok = ok and torch.allclose(out2, x * 3.0, rtol=1e-5, atol=1e-5) and not exact.overflowed()
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("worker", [_row_parallel_worker, _moe_worker, _moe_overflow_worker])
 def test_two_rank_gloo(worker):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
