@@ -144,6 +144,8 @@ static int check_gemm(const void* A, const void* B, const void* SFA, const void*
   if (M < 0 || N <= 0 || K <= 0) return ARCQ_ERR_BAD_SHAPE;
   if (K % 64 || N % 8) return ARCQ_ERR_BAD_SHAPE;
   if (M > (int64_t)1 << 30 || N > (int64_t)1 << 30 || K > (int64_t)1 << 20) return ARCQ_ERR_BAD_SHAPE;
+  // the kernels count work items (128 x 64 tiles, up to eight K ranges each) in 32-bit integers
+  if (((M + 127) / 128) * ((N + 63) / 64) * 8 > (int64_t)0x7fffffff) return ARCQ_ERR_BAD_SHAPE;
   if (M == 0) return ARCQ_OK;
   if (!A || !B || !SFA || !SFB || !C) return ARCQ_ERR_NULL_POINTER;
   if (!aligned16(A) || !aligned16(B) || !aligned16(SFA) || !aligned16(SFB) || !aligned16(C))

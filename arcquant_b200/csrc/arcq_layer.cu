@@ -11,6 +11,8 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "arcq_internal.h"
 
 namespace arcq {
@@ -103,13 +105,40 @@ __global__ void arcq_silu_mul_kernel(const uint16_t* __restrict__ gu, uint16_t* 
 // division: ~25 instructions per element) makes the pass above instruction bound at ~0.75 of the HBM
 // rate.  g_silu_table holds bf16(silu(g)) for every g, written by arcq_silu_table_kernel with the very
 // function above (so the results cannot differ); each CTA of the main kernel copies the 128 KB into
-// shared memory and looks SiLU up.  The table is rewritten by every call on the call's own stream:
-// calls on other streams can only ever see the same values.
+// shared memory and looks SiLU up.
 __device__ uint16_t g_silu_table[65536];
 
 __global__ void arcq_silu_table_kernel() {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   g_silu_table[i] = (uint16_t)(__float_as_uint(silu_bf16(__uint_as_float(i << 16))) >> 16);
+}
+
+// The table is written once per device: the first call launches the kernel on its own stream and records
+// an event, later calls make their stream wait for that event until it has completed (after which the
+// table is never touched again, so calls on any number of streams only ever read it).
+int ensure_silu_table(int device, cudaStream_t stream) {
+  struct State { bool started = false, done = false; cudaEvent_t ev = nullptr; };
+  static std::mutex mu;
+  static State st[64];
+  if (device < 0 || device >= 64) return ARCQ_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  State& s = st[device];
+  if (s.done) return ARCQ_OK;
+  if (!s.started) {
+    ARCQ_CUDA_TRY(cudaEventCreateWithFlags(&s.ev, cudaEventDisableTiming));
+    arcq_silu_table_kernel<<<65536 / 256, 256, 0, stream>>>();
+    ARCQ_CUDA_TRY(cudaGetLastError());
+    ARCQ_CUDA_TRY(cudaEventRecord(s.ev, stream));
+    s.started = true;
+    return ARCQ_OK;
+  }
+  if (cudaEventQuery(s.ev) == cudaSuccess) {
+    s.done = true;
+    return ARCQ_OK;
+  }
+  (void)cudaGetLastError();   // (cudaErrorNotReady is not an error)
+  ARCQ_CUDA_TRY(cudaStreamWaitEvent(stream, s.ev, 0));
+  return ARCQ_OK;
 }
 
 __global__ void __launch_bounds__(1024, 1) arcq_silu_mul_table_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ out,
@@ -510,8 +539,8 @@ int launch_silu_mul_grouped(const void* gu, void* out, int64_t rows, int F, cons
   auto o = static_cast<uint16_t*>(out);
   auto am = reinterpret_cast<unsigned int*>(amax);
   if (total >= (1LL << 21) && di.max_smem_optin >= 131072) {
-    arcq_silu_table_kernel<<<65536 / 256, 256, 0, stream>>>();
-    ARCQ_CUDA_TRY(cudaGetLastError());
+    rc = ensure_silu_table(di.device, stream);
+    if (rc != ARCQ_OK) return rc;
     auto kern = arcq_silu_mul_grouped_kernel<true>;
     static thread_local int attr_dev = -1;
     if (attr_dev != di.device) {
@@ -535,10 +564,9 @@ int launch_silu_mul(const void* gu, void* out, int64_t tokens, int F, float* ama
   int rc = get_device_info(&di);
   if (rc != ARCQ_OK) return rc;
   const long long total = (long long)tokens * (F / 8);
-  static const int table_env = [] { const char* e = getenv("ARCQ_SILU_TABLE"); return e ? atoi(e) : 1; }();
-  if (table_env && total >= (1LL << 22) && di.max_smem_optin >= 131072) {   // 32 M elements and more: table lookups
-    arcq_silu_table_kernel<<<65536 / 256, 256, 0, stream>>>();
-    ARCQ_CUDA_TRY(cudaGetLastError());
+  if (total >= (1LL << 22) && di.max_smem_optin >= 131072) {   // 32 M elements and more: table lookups
+    rc = ensure_silu_table(di.device, stream);
+    if (rc != ARCQ_OK) return rc;
     auto kern = arcq_silu_mul_table_kernel;
     static thread_local int attr_dev = -1;
     if (attr_dev != di.device) {

@@ -28,7 +28,6 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#include <cstdlib>
 
 #include "arcq_internal.h"
 
@@ -1258,7 +1257,6 @@ int launch_ws(const QuantParams& p, int nct, int npt, int nteams, int npteams, s
   if (p.groups != nullptr && grid < p.ngroups) return ARCQ_ERR_BAD_SHAPE;   // every run needs a CTA
   // Programmatic dependent launch: the grid may be set up while the previous kernel of the stream is
   // still draining; the kernel itself waits (griddepcontrol.wait) before it touches global memory.
-  static const int pdl_env = [] { const char* e = getenv("ARCQ_QUANT_PDL"); return e ? atoi(e) : 1; }();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3((unsigned)threads);
@@ -1268,7 +1266,7 @@ int launch_ws(const QuantParams& p, int nct, int npt, int nteams, int npteams, s
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_env ? 1 : 0;
+  cfg.numAttrs = 1;
   ARCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p, nct, npt, nteams, npteams));
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
@@ -1335,14 +1333,8 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   }
   const bool rawidx = KQ > 16384;
 
-  // Warp-specialised kernel (ARCQ_QUANT_WS=0 falls back to the general one): rows of 1024..8192 channels
+  // Warp-specialised kernel: rows of 512..8192 channels
   // in full, rows of up to 16384 channels for the plain operator.
-  static const int ws_env = [] { const char* e = getenv("ARCQ_QUANT_WS"); return e ? atoi(e) : 1; }();
-  static const int raw_env = [] { const char* e = getenv("ARCQ_QUANT_RAW"); return e ? atoi(e) : 0; }();
-  static const int stages_env = [] { const char* e = getenv("ARCQ_QUANT_STAGES"); return e ? atoi(e) : 0; }();
-  static const int teams_env = [] { const char* e = getenv("ARCQ_QUANT_TEAMS"); return e ? atoi(e) : 0; }();
-  static const int pteams_env = [] { const char* e = getenv("ARCQ_QUANT_PTEAMS"); return e ? atoi(e) : 0; }();
-  static const int nct_env = [] { const char* e = getenv("ARCQ_QUANT_NCT"); return e ? atoi(e) : 0; }();
   const bool gamma_ok = !rms || (reinterpret_cast<uintptr_t>(gamma) & 15u) == 0;   // read with 128-bit loads
   const bool wide = p.G > 512;
   // (RMSNorm: one producer per 16-channel group, in whole warps - the reference's summation order)
@@ -1359,7 +1351,6 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
       int R = 0;
       if (fixed + 2 * stage <= (size_t)di.max_smem_optin) R = (int)(((size_t)di.max_smem_optin - fixed - 2 * stage) / (stage / 2));
       if (R > 4) R = 4;
-      if (raw_env >= 2 && raw_env <= 4 && raw_env <= R) R = raw_env;
       const size_t smem = fixed + 2 * stage + (size_t)R * (stage / 2);
       if (R >= 2) {
         if (p.scale) {
@@ -1376,7 +1367,6 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
       // teams of 256: more row pairs in flight for the same number of warps.
       const int g32 = (p.G + 31) / 32 * 32;   // threads of a role are whole warps
       int nct = g32 < 128 ? g32 : 128;
-      if (nct_env >= 32 && nct_env % 32 == 0 && nct_env <= g32 && nct_env <= 256) nct = nct_env;
       // producers: two 16-byte chunks of each row per thread (the RMSNorm summation order needs exactly
       // that); with the division by the tensor's scale, at least 512 of them share the arithmetic
       const int npt = (p.scale && p.G < 512) ? 512 : g32;
@@ -1384,14 +1374,11 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
       // producer teams, each with three helper warps.  The rest, up to three teams, are consumers.
       const int ptt = npt + (rms ? 96 : 0);   // threads of a producer team
       int npteams = (rms && 2 * ptt + nct <= 1024) ? 2 : 1;
-      if (rms && (pteams_env == 1 || pteams_env == 2) && pteams_env * ptt + nct <= 1024) npteams = pteams_env;
       int nteams = (1024 - npteams * ptt) / nct;
       if (nteams > 3) nteams = 3;
-      if (teams_env >= 1 && teams_env <= 3 && teams_env * nct + npteams * ptt <= 1024) nteams = teams_env;
       // gather stages: 2 for a single consumer team, else 4.  Raw stages: a multiple of the number of
       // producer teams (a stage always serves pairs of the same team), at least two per team.
       int S = nteams > 1 ? 4 : 2;
-      if (stages_env == 2 || stages_env == 4) S = stages_env;
       size_t fixed = 384 + (size_t)KQ * 4 + (rms ? ((size_t)4 * npt * sizeof(float) + 16) * npteams : 0);
       if (fixed + (S + 2 * npteams) * stage > (size_t)di.max_smem_optin && S == 4) S = 2;
       if (rms && npteams == 2 && fixed + (S + 4) * stage > (size_t)di.max_smem_optin) {
@@ -1404,7 +1391,6 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
       const int r_floor = 2 * npteams;
       int R = 8;
       while (R > r_floor && fixed + (S + R) * stage > (size_t)di.max_smem_optin) R -= 2;
-      if ((raw_env == 2 || raw_env == 4 || raw_env == 6 || raw_env == 8) && raw_env >= r_floor) R = raw_env;
       const size_t smem = fixed + (S + R) * stage;
       if (nteams >= 1 && smem <= (size_t)di.max_smem_optin) {
         const int kind = rms ? 0 : (p.scale ? 2 : 1);   // RMSNorm / plain / plain with the division
@@ -1439,16 +1425,8 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
                   : launch_variant<8, 1, 1, false, false, 512, 1>(p, nt, smem, di, stream);
   }
   if (nt <= 256 && cpt == 2) {
-    // Narrow rows (the common case).  Default: one row pair per iteration, three resident CTAs per
-    // SM.  ARCQ_QUANT_PAIRS=2 selects two pairs per iteration with two resident CTAs and a
-    // 128-register budget (tuning knob; measured slower on B200: fewer warps to hide latency).
-    static const int pairs_env = [] { const char* e = getenv("ARCQ_QUANT_PAIRS"); return e ? atoi(e) : 1; }();
-    const bool two = pairs_env == 2 && p.npairs >= 4LL * di.num_sms;
-    if (two) {
-      smem = smem_for(2, 2);
-      if (rms) return launch_variant<2, 2, 2, true, false, 256, 2>(p, nt, smem, di, stream);
-      return launch_variant<2, 2, 2, false, false, 256, 2>(p, nt, smem, di, stream);
-    }
+    // Narrow rows: one row pair per iteration, three resident CTAs per SM (two pairs per iteration with
+    // two resident CTAs were measured slower on B200: fewer warps to hide latency).
     if (rms) return launch_variant<2, 2, 1, true, false, 256, 3>(p, nt, smem, di, stream);
     return launch_variant<2, 2, 1, false, false, 256, 3>(p, nt, smem, di, stream);
   }

@@ -193,7 +193,11 @@ int arcq_absmax_bf16(const void* x, int64_t n, float* out, int accumulate, void*
 
 /* Layer glue between the quantized linears.  No counterpart in the reference's bindings: its layers
  * call torch for these (Hugging Face apply_rotary_pos_emb and act_fn(gate) * up in
- * model/qLlamaLayer.py).  Results equal eager torch bit for bit.
+ * model/qLlamaLayer.py).  Results equal eager torch bit for bit FOR THE FORMULAS WRITTEN BELOW.  For the
+ * rotary embedding that formula keeps cos and sin in fp32 and rounds once; Hugging Face's
+ * apply_rotary_pos_emb, which the reference layer calls, multiplies by bf16 cos / sin and rounds each
+ * product and the sum to bf16, so a layer output agrees with the reference layer's within bf16 rounding
+ * at this step, not bit for bit.
  *
  * arcq_rope_bf16: rotate-half rotary embedding, in place, on the first `heads` heads of `head_dim`
  *   elements of every row of x [tokens, row_elems] (bf16; e.g. the q and k columns of a fused qkv
