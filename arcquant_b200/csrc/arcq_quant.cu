@@ -1388,6 +1388,10 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
       // A consumer team that is more than one lap of the gather ring ahead would pass its "full" wait
       // on the previous lap's phase: never more consumer teams than gather stages.
       if (nteams > S) nteams = S;
+      // With two producer teams the pairs are not filled in order, and a consumer team that comes back to a
+      // stage only every third lap would take the parity of an older lap for its own: the number of
+      // consumer teams must divide the number of gather stages.
+      if (npteams == 2 && nteams == 3) nteams = 2;
       const int r_floor = 2 * npteams;
       int R = 8;
       while (R > r_floor && fixed + (S + R) * stage > (size_t)di.max_smem_optin) R -= 2;

@@ -220,7 +220,7 @@ def test_rmsnorm_quantize_x_steady_state(tokens, ke):
     sampled_rows_match_oracle(q, sf, rows, qo, sfo, kq + ke)
 
 
-@pytest.mark.parametrize("kq", [2048, 8192])
+@pytest.mark.parametrize("kq", [2048, 3072, 3584, 5120, 8192])
 def test_rmsnorm_quantize_x_steady_state_other_widths(kq):
     ops, O = _ops(), _oracle()
     tokens, ke = 16384, 128
