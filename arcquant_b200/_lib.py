@@ -55,6 +55,8 @@ SIGNATURES = {
     "arcq_absmax_grouped_bf16": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp]),
     "arcq_reorder_quantize_x_grouped": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
     "arcq_matmul_nvfp4_grouped": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _vp, _vp, _vp, _vp]),
+    "arcq_matmul_nvfp4_swiglu": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "arcq_matmul_nvfp4_grouped_swiglu": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp]),
     "arcq_moe_combine_bf16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
 }
 

@@ -293,6 +293,30 @@ int arcq_matmul_nvfp4_grouped(const uint8_t* A, const uint8_t* B, const uint8_t*
                              (cudaStream_t)stream);
 }
 
+int arcq_matmul_nvfp4_swiglu(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                             int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b, void* C,
+                             float* amax, void* stream) {
+  int rc = check_gemm(A, B, SFA, SFB, M, N, K_eff, C);
+  if (rc != ARCQ_OK) return rc;
+  if (N % 256) return ARCQ_ERR_BAD_SHAPE;
+  if (!alpha_a || !amax) return ARCQ_ERR_NULL_POINTER;
+  if (M == 0) return ARCQ_OK;
+  return launch_gemm_grouped(A, B, SFA, SFB, M, N, K_eff, nullptr, 1, alpha_a, alpha_b, C, (cudaStream_t)stream, amax,
+                             nullptr);
+}
+
+int arcq_matmul_nvfp4_grouped_swiglu(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                                     int64_t M_bound, int64_t N, int64_t K_eff, const int32_t* tile_group,
+                                     const int32_t* groups, int ngroups, const float* alpha_a, const float* alpha_b,
+                                     void* C, float* amax, void* stream) {
+  int rc = check_gemm(A, B, SFA, SFB, M_bound, N, K_eff, C);
+  if (rc != ARCQ_OK || M_bound == 0) return rc;
+  if (ngroups < 1 || ngroups > 64 || N % 256 || N * (int64_t)ngroups > ((int64_t)1 << 30)) return ARCQ_ERR_BAD_SHAPE;
+  if (!tile_group || !groups || !alpha_a || !amax) return ARCQ_ERR_NULL_POINTER;
+  return launch_gemm_grouped(A, B, SFA, SFB, M_bound, N, K_eff, tile_group, ngroups, alpha_a, alpha_b, C,
+                             (cudaStream_t)stream, amax, groups);
+}
+
 int arcq_absmax_bf16(const void* x, int64_t n, float* out, int accumulate, void* stream) {
   if (n < 0) return ARCQ_ERR_BAD_SHAPE;
   if (!out || (n > 0 && !x)) return ARCQ_ERR_NULL_POINTER;

@@ -466,7 +466,21 @@ struct Gemm2Params {
   // (device memory: the host never learns the split).  Matrix g owns rows [g*N, (g+1)*N) of B and of
   // its scales, and alpha_a[g] * alpha_b[g].
   const int* tile_group;
+  // SwiGLU epilogue (template flag of the kernel): B holds gate and up columns interleaved in blocks of 128
+  // (tile column tn = gate columns [128 tn, 128 tn + 128) then the same up columns), C is [M, N/2] and
+  // receives bf16(bf16(silu(gate)) * up) of the bf16-rounded GEMM outputs; amax[g] (bit pattern of a
+  // non-negative float) takes max|.| over the valid rows - rows below M, and for grouped problems below the
+  // end of their run, groups[g] + groups[ngroups + g].
+  unsigned int* amax;
+  const int* groups;
+  int ngroups;
 };
+
+// SiLU of a bf16 value, rounded to bf16, exactly as arcq_silu_mul_bf16 (and eager torch) compute it.
+__device__ __forceinline__ float silu_bf16_exact(float g) {
+  const float s = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+  return __uint_as_float(pack_bf16x2(s, 0.f) << 16);
+}
 
 // Tile order of the persistent pairs: bands of group_m tile rows, and inside a band column by column.
 // The ~74 tiles in flight at any time then cover about group_m x (74 / group_m) tiles, so every strip of
@@ -481,6 +495,7 @@ __device__ __forceinline__ void pair_tile_coords(int tile, const Gemm2Params& p,
   tm = first + (in_band - tn * rows);
 }
 
+template <bool SWIGLU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C2_THREADS, 1)
 arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
@@ -617,8 +632,9 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
       pair_tile_coords(tile, p, tm, tn);
+      int grp = 0;
       if (p.tile_group != nullptr) {
-        const int grp = __ldg(p.tile_group + tm);
+        grp = __ldg(p.tile_group + tm);
         if (grp < 0) continue;
         alpha = p.alpha;
         if (p.alpha_a) alpha *= __ldg(p.alpha_a + grp);
@@ -648,7 +664,27 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(tmem_empty_bar);
-      const int col0 = tn * 256;
+      if (SWIGLU) {
+        // columns 0..127 of the tile are gate, 128..255 the matching up columns: out = silu(gate) * up in
+        // the gate registers, and its maximum over the rows that hold data
+        int row_end = p.M;
+        if (p.groups != nullptr) row_end = __ldg(p.groups + grp) + __ldg(p.groups + p.ngroups + grp);
+        uint32_t m = 0;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const uint32_t g = o[j], u = o[64 + j];
+          const float a = silu_bf16_exact(__uint_as_float(g << 16)) * __uint_as_float(u << 16);
+          const float b = silu_bf16_exact(__uint_as_float(g & 0xffff0000u)) * __uint_as_float(u & 0xffff0000u);
+          o[j] = pack_bf16x2(a, b);
+          asm("max.u16x2 %0, %0, %1;" : "+r"(m) : "r"(o[j] & 0x7fff7fffu));
+        }
+        uint32_t v = row < row_end ? max(m & 0xffffu, m >> 16) : 0u;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, d));
+        if (lane == 0 && v) atomicMax(p.amax + grp, v << 16);
+      }
+      const int col0 = SWIGLU ? tn * 128 : tn * 256;
+      const int ncols = SWIGLU ? (p.N >> 1) : p.N;
       if (p.tma_store) {
         // Through shared memory: the warp's 32 rows x 256 columns leave as four boxes of 64 columns
         // (32 rows x 128 bytes, 128-byte swizzle: lane = row, 16-byte chunk c of row r sits at chunk
@@ -659,7 +695,7 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const uint32_t cst = cstage_base + (uint32_t)quad * 8192u;
         if (row0 < p.M) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < (SWIGLU ? 1 : 2); ++h) {
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging is free again
             __syncwarp();
 #pragma unroll
@@ -679,7 +715,7 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 #pragma unroll
               for (int bs = 0; bs < 2; ++bs) {
                 const int col = col0 + 64 * (2 * h + bs);
-                if (col < p.N)
+                if (col < ncols)
                   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_c),
                                "r"(cst + (uint32_t)bs * 4096u), "r"(col), "r"(row0)
                                : "memory");
@@ -688,7 +724,7 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
           }
         }
-      } else if (row < p.M) {
+      } else if (!SWIGLU && row < p.M) {
 #pragma unroll
         for (int v = 0; v < 32; ++v) {          // 32 x 16 bytes = this row's 256 columns
           if (col0 + v * 8 < p.N)
@@ -857,10 +893,15 @@ int make_c_map(CUtensorMap* map, const void* ptr, int64_t M, int64_t N) {
 
 // ngroups > 1: B and SFB hold `ngroups` matrices of N rows each, tile_group says which one every
 // 256-row tile of A multiplies (see Gemm2Params).
+// swiglu_amax != nullptr: SwiGLU epilogue (see Gemm2Params), C is [M, N/2]; groups: the run table of a grouped
+// problem (for the maxima).
 int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M, int64_t N,
                 int64_t K_eff, const GemmParams& gp, int num_sms, cudaStream_t stream, const int* tile_group = nullptr,
-                int ngroups = 1) {
+                int ngroups = 1, float* swiglu_amax = nullptr, const int* groups = nullptr) {
   Gemm2Params p;
+  p.amax = reinterpret_cast<unsigned int*>(swiglu_amax);
+  p.groups = groups;
+  p.ngroups = ngroups;
   p.c = gp.c;
   p.alpha_a = gp.alpha_a;
   p.alpha_b = gp.alpha_b;
@@ -882,7 +923,8 @@ int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
   p.tile_group = tile_group;
   CUtensorMap ma, mb, msa, msb, mc;
-  int rc = make_c_map(&mc, gp.c, M, N);
+  if (swiglu_amax != nullptr) ARCQ_CUDA_TRY(cudaMemsetAsync(swiglu_amax, 0, sizeof(float) * ngroups, stream));
+  int rc = make_c_map(&mc, gp.c, M, swiglu_amax != nullptr ? N / 2 : N);
   if (rc != ARCQ_OK) return rc;
   rc = make_operand_map(&ma, A, M, K_eff / 2, 128);
   if (rc != ARCQ_OK) return rc;
@@ -892,7 +934,7 @@ int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   if (rc != ARCQ_OK) return rc;
   rc = make_sf_map(&msb, SFB, ((N * ngroups + 127) / 128) * (int64_t)gp.natoms);
   if (rc != ARCQ_OK) return rc;
-  auto kern = arcq_gemm2_kernel;
+  auto kern = swiglu_amax != nullptr ? arcq_gemm2_kernel<true> : arcq_gemm2_kernel<false>;
   ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C2_SMEM_BYTES));
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   long long clusters = num_sms / 2;
@@ -965,7 +1007,7 @@ static void plan_splitk(int64_t M, int64_t N, int64_t K_eff, int num_sms, int* b
 
 int launch_gemm_grouped(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                         int64_t N, int64_t K_eff, const int* tile_group, int ngroups, const float* alpha_a,
-                        const float* alpha_b, void* Cout, cudaStream_t stream) {
+                        const float* alpha_b, void* Cout, cudaStream_t stream, float* swiglu_amax, const int* groups) {
   DeviceInfo di;
   int rc = get_device_info(&di);
   if (rc != ARCQ_OK) return rc;
@@ -979,7 +1021,7 @@ int launch_gemm_grouped(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, 
   p.ksteps_total = (int)(K_eff / 64);
   p.natoms = (int)((K_eff / 16 + 3) / 4);
   p.splits = 1;
-  return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream, tile_group, ngroups);
+  return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream, tile_group, ngroups, swiglu_amax, groups);
 }
 
 size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K_eff) {

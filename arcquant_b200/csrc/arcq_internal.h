@@ -53,7 +53,10 @@ int launch_moe_combine(const void* y, const int* pos, const void* w, void* out, 
 // matrix of every 256-row tile of A, alpha_a / alpha_b are per-matrix arrays.
 int launch_gemm_grouped(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                         int64_t N, int64_t K_eff, const int* tile_group, int ngroups, const float* alpha_a,
-                        const float* alpha_b, void* C, cudaStream_t stream);
+                        const float* alpha_b, void* C, cudaStream_t stream,
+                        // SwiGLU epilogue: C is [M, N/2], swiglu_amax[ngroups] takes max|C| per matrix; tile_group
+                        // may be null with ngroups 1 (one matrix); groups: run table of a grouped problem
+                        float* swiglu_amax = nullptr, const int* groups = nullptr);
 int launch_absmax_grouped(const void* x, const int* row_map, const int* groups, int ngroups, int K, float* out,
                           cudaStream_t stream);
 int launch_moe_layout(const long long* slot_group, int n, int ngroups, int tile, int rows_bound, int div, int* dest,

@@ -179,9 +179,14 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         return self.timer.phase(name) if self.timer is not None else contextlib.nullcontext()
 
     def __init__(self, cfg: LlamaLayerConfig, weights: dict, indices: dict, tp_rank: int = 0, tp_size: int = 1,
-                 group=None, device="cuda"):
+                 group=None, device="cuda", fuse_swiglu: bool = True):
+        """fuse_swiglu: pack gate and up interleaved in blocks of 128 channels so that SiLU(gate) * up (and its
+        max|.|) is computed in the gate_up GEMM's epilogue instead of a pass of its own over [tokens, 2 * ffn];
+        same bits either way.  Needs ffn / tp_size to be a multiple of 128; meant for prefill-sized batches
+        (the fused GEMM always runs the CTA-pair kernel)."""
         super().__init__()
         self.cfg, self.rank, self.tp, self.group = cfg, tp_rank, tp_size, group
+        self.fuse_swiglu = bool(fuse_swiglu) and (cfg.ffn // tp_size) % 128 == 0
         if cfg.n_heads % tp_size or cfg.n_kv_heads % tp_size or cfg.ffn % tp_size:
             raise ValueError("heads / kv heads / ffn must split over the tensor-parallel group")
         dev = torch.device(device)
@@ -195,8 +200,12 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         # column-parallel: rows of this rank's heads / ffn slice, global channel order
         wqkv = torch.cat([to(weights["wq"][q0:q1]), to(weights["wk"][k0:k1]), to(weights["wv"][k0:k1])], dim=0)
         self.qkv = PackedLinear(wqkv, indices["q"], cfg.select_num)
-        wgu = torch.cat([to(weights["w_gate"][f0:f1]), to(weights["w_up"][f0:f1])], dim=0)
+        if self.fuse_swiglu:
+            wgu = ops.interleave_gate_up(to(weights["w_gate"][f0:f1]), to(weights["w_up"][f0:f1]))
+        else:
+            wgu = torch.cat([to(weights["w_gate"][f0:f1]), to(weights["w_up"][f0:f1])], dim=0)
         self.gate_up = PackedLinear(wgu, indices["up"], cfg.select_num)
+        self.register_buffer("fuse_swiglu_t", torch.tensor(int(self.fuse_swiglu), dtype=torch.int32))
         # row-parallel: K slice with its local order and local KE
         self.o = PackedLinear(to(weights["wo"][:, q0:q1]).contiguous(), tp.local_reorder_index(indices["o"], q0, q1),
                               tp.shard_select_num(cfg.select_num, tp_size, q1 - q0))
@@ -230,7 +239,15 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
                 raise ValueError(f"{name}: {getattr(self, name).W.shape[0]} output rows, expected {rows} for tp_size {tp_size}")
         self.register_buffer("ln1", state["ln1"].to(dev).contiguous())
         self.register_buffer("ln2", state["ln2"].to(dev).contiguous())
+        self.fuse_swiglu = bool(int(state["fuse_swiglu_t"])) if "fuse_swiglu_t" in state else False
+        self.register_buffer("fuse_swiglu_t", torch.tensor(int(self.fuse_swiglu), dtype=torch.int32))
         return self
+
+    def _gate_up_act(self, a: torch.Tensor, sfa: torch.Tensor):
+        """(silu(gate) * up [tokens, ffn / tp], its max|.|) from the quantized input of the gate/up projection."""
+        if self.fuse_swiglu:
+            return ops.matmul_swiglu(a, self.gate_up.W, sfa, self.gate_up.SFW, self.gate_up.scale, None)
+        return ops.silu_mul(self.gate_up.gemm(a, sfa))
 
     # ---- halves of the layer up to (and excluding) the all-reduce: usable for in-process emulation
     @torch.no_grad()
@@ -263,9 +280,7 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         with self._ph("quantize"):
             a, sfa = ops.rmsnorm_quantize_x(h2d, self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
         with self._ph("gemm"):
-            gu = self.gate_up.gemm(a, sfa)
-        with self._ph("glue"):
-            act, amax = ops.silu_mul(gu)      # silu(gate) * up and its max|.| in one pass
+            act, amax = self._gate_up_act(a, sfa)      # silu(gate) * up and its max|.| with the GEMM
         with self._ph("quantize"):
             qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16, amax=amax)
         with self._ph("gemm"):
@@ -355,9 +370,7 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         with self._ph("collective"):
             a, sfa = self._gather_quantized(a_s, sfa_s, rows_s, k_eff)
         with self._ph("gemm"):
-            gu = self.gate_up.gemm(a, sfa)
-        with self._ph("glue"):
-            act, amax = ops.silu_mul(gu)
+            act, amax = self._gate_up_act(a, sfa)
         with self._ph("quantize"):
             qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16, amax=amax)
         with self._ph("gemm"):
@@ -452,7 +465,7 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
             a, sfa, works = gathers[c]
             for w in works:
                 w.wait()
-            act, am = ops.silu_mul(self.gate_up.gemm(a, sfa))
+            act, am = self._gate_up_act(a, sfa)
             acts.append(act)
             amax.append(am)
         scale_d = torch.stack(amax).max() / (448.0 * 6.0)
@@ -512,7 +525,7 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
             w.wait()
             torch.add(x2d[r0:r1], y, out=h[r0:r1])
             a, sfa = ops.rmsnorm_quantize_x(h[r0:r1], self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
-            act, amax = ops.silu_mul(self.gate_up.gemm(a, sfa))
+            act, amax = self._gate_up_act(a, sfa)
             acts.append(act)
             amaxes.append(amax)
         scale_d = torch.stack(amaxes).max() / (448.0 * 6.0)

@@ -272,9 +272,13 @@ class QMixtralMoEBlockEP(torch.nn.Module):
         self.router = weights["router"].to(dev)
         self.experts = []
         e0 = ep_rank * self.dispatcher.e_local
+        # gate (w1) and up (w3) interleaved in blocks of 128 channels: SiLU(gate) * up and its maximum come out of
+        # the GEMM's epilogue (same bits as the GEMM followed by a SiLU pass over [rows, 2 * ffn])
+        self.fuse_swiglu = cfg.ffn % 128 == 0
         for e in range(e0, e0 + self.dispatcher.e_local):
             ew = weights["experts"][e]
-            gu = PackedLinear(torch.cat([ew["w1"], ew["w3"]], 0).to(dev), ew["w1_index"], cfg.select_num)
+            wgu = ops.interleave_gate_up(ew["w1"], ew["w3"]) if self.fuse_swiglu else torch.cat([ew["w1"], ew["w3"]], 0)
+            gu = PackedLinear(wgu.to(dev), ew["w1_index"], cfg.select_num)
             dn = PackedLinear(ew["w2"].to(dev).contiguous(), ew["w2_index"], cfg.select_num)
             self.experts.append((gu, dn))
         # one launch per projection for all local experts needs whole scale tiles per expert (N % 128)
@@ -287,18 +291,22 @@ class QMixtralMoEBlockEP(torch.nn.Module):
 
     @torch.no_grad()
     def expert_forward_grouped(self, batch: RoutedBatch) -> torch.Tensor:
-        """All local experts in six launches: [rows_bound, hidden] in the padded layout of `batch`."""
+        """All local experts in five launches: [rows_bound, hidden] in the padded layout of `batch`."""
         cfg, E = self.cfg, self.dispatcher.e_local
         ke = cfg.select_num
         s1 = ops.absmax_grouped(batch.src, batch.row_map, batch.groups, E) / (448.0 * 6.0)   # per-expert scales
         a, sfa = ops.reorder_quantize_x_grouped(batch.src, batch.row_map, s1, self.gu_index, batch.groups,
                                                 batch.rows_bound, ke)
-        h = ops.matmul_grouped(a, self.gu_W, sfa, self.gu_SF, batch.tile_group, E, 2 * cfg.ffn, s1, self.gu_scale)
-        if cfg.ffn % 256 == 0:      # SiLU * up and the per-expert maxima in one pass, empty tiles skipped
-            act, amax2 = ops.silu_mul_grouped(h, batch.tile_group, batch.groups, E)
+        if self.fuse_swiglu:        # SiLU * up and the per-expert maxima in the GEMM's epilogue
+            act, amax2 = ops.matmul_grouped_swiglu(a, self.gu_W, sfa, self.gu_SF, batch.tile_group, batch.groups, E,
+                                                   2 * cfg.ffn, s1, self.gu_scale)
         else:
-            act, _ = ops.silu_mul(h, with_amax=False)
-            amax2 = ops.absmax_grouped(act, None, batch.groups, E)
+            h = ops.matmul_grouped(a, self.gu_W, sfa, self.gu_SF, batch.tile_group, E, 2 * cfg.ffn, s1, self.gu_scale)
+            if cfg.ffn % 256 == 0:  # SiLU * up and the per-expert maxima in one pass, empty tiles skipped
+                act, amax2 = ops.silu_mul_grouped(h, batch.tile_group, batch.groups, E)
+            else:
+                act, _ = ops.silu_mul(h, with_amax=False)
+                amax2 = ops.absmax_grouped(act, None, batch.groups, E)
         s2 = amax2 / (448.0 * 6.0)
         b, sfb = ops.reorder_quantize_x_grouped(act, None, s2, self.dn_index, batch.groups, batch.rows_bound, ke)
         return ops.matmul_grouped(b, self.dn_W, sfb, self.dn_SF, batch.tile_group, E, cfg.hidden, s2, self.dn_scale)
@@ -325,8 +333,10 @@ class QMixtralMoEBlockEP(torch.nn.Module):
             with ctx:
                 xb = rows[start:start + n]
                 a, sfa, sx = NVFP4_reorder_quantize_x(xb, gu.index, gu.select_num, mode=16)
-                h = gu.gemm(a, sfa, sx)
-                act, amax = ops.silu_mul(h)
+                if self.fuse_swiglu:
+                    act, amax = ops.matmul_swiglu(a, gu.W, sfa, gu.SFW, sx, gu.scale)
+                else:
+                    act, amax = ops.silu_mul(gu.gemm(a, sfa, sx))
                 b, sfb, sa = NVFP4_reorder_quantize_x(act, dn.index, dn.select_num, mode=16, amax=amax)
                 out[start:start + n] = dn.gemm(b, sfb, sa)
             start += n

@@ -357,6 +357,69 @@ def matmul_grouped(a, b, sfa, sfb, tile_group: torch.Tensor, ngroups: int, n: in
     return c
 
 
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """[2F, K] weight whose rows alternate blocks of `block` gate channels and the same up channels: the row
+    order `matmul_swiglu` expects of its B operand."""
+    f, k = w_gate.shape
+    if w_up.shape != (f, k) or f % block:
+        raise RuntimeError("gate and up must have the same shape, with a multiple of 128 output channels")
+    return torch.stack([w_gate.reshape(f // block, block, k), w_up.reshape(f // block, block, k)], dim=1).reshape(2 * f, k)
+
+
+def matmul_swiglu(a, b, sfa, sfb, alpha_a: torch.Tensor, alpha_b: torch.Tensor | None = None):
+    """(act bf16 [M, N/2], amax 0-dim fp32): gate/up GEMM over an interleaved weight (`interleave_gate_up`) with
+    silu(gate) * up and its max|.| taken in the epilogue."""
+    lib = _lib.load()
+    for t, name in ((a, "A"), (b, "B"), (sfa, "SFA"), (sfb, "SFB")):
+        _require(t, torch.uint8, name)
+    _require(alpha_a, torch.float32, "alpha_a")
+    if alpha_b is not None:
+        _require(alpha_b, torch.float32, "alpha_b")
+    m, kb = a.shape
+    n = b.shape[0]
+    if b.shape[1] != kb or n % 256:
+        raise RuntimeError("A and B disagree on K, or N is not a multiple of 256")
+    atoms = (kb * 2 // 16 + 3) // 4
+    if sfa.numel() < ((m + 127) // 128) * atoms * 512 or sfb.numel() < (n // 128) * atoms * 512:
+        raise RuntimeError("scale buffers are smaller than the scale layout of their operands")
+    c = torch.empty((m, n // 2), dtype=torch.bfloat16, device=a.device)
+    amax = torch.empty((), dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        rc = lib.arcq_matmul_nvfp4_swiglu(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, kb * 2,
+                                          alpha_a.data_ptr(), None if alpha_b is None else alpha_b.data_ptr(),
+                                          c.data_ptr(), amax.data_ptr(), _stream())
+    _lib.check(rc, f"swiglu matmul M={m} N={n} K={kb * 2}")
+    return c, amax
+
+
+def matmul_grouped_swiglu(a, b, sfa, sfb, tile_group: torch.Tensor, groups: torch.Tensor, ngroups: int, n: int,
+                          alpha_a: torch.Tensor, alpha_b: torch.Tensor | None = None):
+    """`matmul_grouped` with the SwiGLU epilogue: (act bf16 [rows, n/2], amax fp32 [ngroups])."""
+    lib = _lib.load()
+    for t, name in ((a, "A"), (b, "B"), (sfa, "SFA"), (sfb, "SFB")):
+        _require(t, torch.uint8, name)
+    _require(tile_group, torch.int32, "tile_group")
+    _require(groups, torch.int32, "groups")
+    _require(alpha_a, torch.float32, "alpha_a")
+    if alpha_b is not None:
+        _require(alpha_b, torch.float32, "alpha_b")
+    m, kb = a.shape
+    if b.shape != (ngroups * n, kb) or tile_group.numel() < (m + 255) // 256 or alpha_a.numel() != ngroups or n % 256:
+        raise RuntimeError("operand shapes disagree")
+    atoms = (kb * 2 // 16 + 3) // 4
+    if sfa.numel() < ((m + 127) // 128) * atoms * 512 or sfb.numel() < ((ngroups * n + 127) // 128) * atoms * 512:
+        raise RuntimeError("scale buffers are smaller than the scale layout of their operands")
+    c = torch.empty((m, n // 2), dtype=torch.bfloat16, device=a.device)
+    amax = torch.empty((ngroups,), dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        rc = lib.arcq_matmul_nvfp4_grouped_swiglu(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, kb * 2,
+                                                  tile_group.data_ptr(), groups.data_ptr(), ngroups, alpha_a.data_ptr(),
+                                                  None if alpha_b is None else alpha_b.data_ptr(), c.data_ptr(),
+                                                  amax.data_ptr(), _stream())
+    _lib.check(rc, f"grouped swiglu matmul M={m} N={n} K={kb * 2} groups={ngroups}")
+    return c, amax
+
+
 def moe_combine(y: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
     """out [T, H] = sum_j bf16(y[pos[t, j]] * weights[t, j]) in bf16: the routed copies of every token,
     weighted and added (pos int32 [T, k], weights bf16 [T, k])."""

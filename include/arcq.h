@@ -276,6 +276,26 @@ int arcq_matmul_nvfp4_grouped(const uint8_t* A, const uint8_t* B, const uint8_t*
                               int64_t M_bound, int64_t N, int64_t K_eff, const int32_t* tile_group, int ngroups,
                               const float* alpha_a, const float* alpha_b, void* C, void* stream);
 
+/* ---- Gate/up projection with the SwiGLU fused into the GEMM's epilogue -------------------------------
+ * The reference runs gate_proj and up_proj as two GEMMs and then `act_fn(gate) * up` in torch
+ * (model/qLlamaLayer.py:432-436, model/qMixtralLayer.py:536-539).  Here B holds both weights, interleaved
+ * in blocks of 128 output channels - rows [256 t, 256 t + 128) of B are gate channels [128 t, 128 t + 128),
+ * rows [256 t + 128, 256 t + 256) the same up channels - so one output tile holds matching gate and up
+ * columns and the epilogue writes C [M, N/2] = bf16(bf16(silu(g)) * u) directly, g and u being the
+ * bf16-rounded GEMM results: the same bits as arcq_matmul_nvfp4 followed by arcq_silu_mul_bf16, without the
+ * [M, N] round trip through memory.  amax (fp32, device) receives max|C| over the valid rows - the
+ * per-tensor maximum the down projection's quantizer needs.  N % 256 == 0.  Always runs the CTA-pair
+ * kernel (meant for prefill-sized M).
+ * arcq_matmul_nvfp4_grouped_swiglu: the same over the runs of a grouped problem (see above); amax has one
+ * entry per run and `groups` says where each run's valid rows end. */
+int arcq_matmul_nvfp4_swiglu(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                             int64_t M, int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b,
+                             void* C, float* amax, void* stream);
+int arcq_matmul_nvfp4_grouped_swiglu(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                                     int64_t M_bound, int64_t N, int64_t K_eff, const int32_t* tile_group,
+                                     const int32_t* groups, int ngroups, const float* alpha_a, const float* alpha_b,
+                                     void* C, float* amax, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

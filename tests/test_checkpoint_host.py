@@ -54,7 +54,8 @@ def test_layer_is_rebuilt_from_packed_buffers_and_round_trips(tmp_path):
     layer = QLlamaDecoderLayerTP.from_packed(cfg, state, device="cpu")
     assert layer.down.select_num == 64 and layer.qkv.W.shape == (512, 160)
     sd = layer.state_dict()
-    assert set(sd) == set(state)
+    assert set(sd) == set(state) | {"fuse_swiglu_t"}           # a state without the flag: [gate | up] halves
+    assert int(sd["fuse_swiglu_t"]) == 0 and not layer.fuse_swiglu
     path = str(tmp_path / "layer.pt")
     checkpoint.save_packed_layer(layer, path)
     again = checkpoint.load_packed_layer(cfg, path, device="cpu")

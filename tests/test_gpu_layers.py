@@ -305,7 +305,7 @@ def test_llama_3_8b_width_layer_stage_by_stage():
 
     cfg = LlamaLayerConfig()                      # hidden 4096, 32 / 8 heads, FFN 14336, select_num 128
     W, I = random_layer_weights(cfg, 0), random_reorder_indices(cfg, 1)
-    layer = QLlamaDecoderLayerTP(cfg, W, I)
+    layer = QLlamaDecoderLayerTP(cfg, W, I, fuse_swiglu=False)      # (gate | up halves: every stage has its own output)
     bsz, seq, D = 2, 160, cfg.head_dim
     T = bsz * seq
     x = synth.activations(T, cfg.hidden, 4, synth.outlier_channels(cfg.hidden, 41, 3)).cuda()
@@ -351,6 +351,13 @@ def test_llama_3_8b_width_layer_stage_by_stage():
     out = (h + yd).reshape(bsz, seq, cfg.hidden)
     # ... and the chain above is what the layer itself computes
     assert torch.equal(layer(x.reshape(bsz, seq, cfg.hidden), pos), out)
+    # ... with SiLU(gate) * up fused into the gate/up GEMM's epilogue as well: same activation, same maximum,
+    # same layer output, bit for bit
+    fused = QLlamaDecoderLayerTP(cfg, W, I)
+    assert fused.fuse_swiglu
+    act_f, amax_f = fused._gate_up_act(a, sfa)
+    assert torch.equal(act_f, act) and float(amax_f) == float(amax)
+    assert torch.equal(fused(x.reshape(bsz, seq, cfg.hidden), pos), out)
     assert ops.gemm_poll_error() == 0
 
 
@@ -478,3 +485,26 @@ def test_calibration_statistics_in_one_pass(k, rows):
     for b in batches:
         eager.update(b.float())
     assert torch.equal(eager.value, want) and eager.select_num() == stat.select_num()
+
+
+@pytest.mark.parametrize("m,f,kq", [(300, 256, 512), (1000, 2048, 1024), (4100, 7168, 4096), (257, 14336, 4096)])
+def test_swiglu_epilogue_equals_gemm_then_silu(m, f, kq):
+    """`matmul_swiglu` over the interleaved gate/up weight against `matmul` over [gate; up] followed by
+    `silu_mul`: identical activation bits and maximum, ragged M included."""
+    from arcquant_b200 import ops
+
+    ke = 64
+    x = synth.activations(m, kq, 3, synth.outlier_channels(kq, max(1, kq // 100), 4), device="cuda")
+    wg, wu = synth.weights(f, kq, 5, device="cuda"), synth.weights(f, kq, 6, device="cuda")
+    idx = torch.randperm(kq, generator=torch.Generator().manual_seed(1)).to(torch.int16).cuda()
+    sx = ops.absmax(x) / 2688.0
+    a, sfa = ops.reorder_quantize_x(x, idx, ke, scale=sx)
+    wcat = torch.cat([wg, wu], 0)
+    sw = torch.max(wcat).float() / 2688.0
+    b1, sfb1 = ops.reorder_quantize_w((wcat / sw).contiguous(), idx, ke)
+    b2, sfb2 = ops.reorder_quantize_w((ops.interleave_gate_up(wg, wu) / sw).contiguous(), idx, ke)
+    want, amax_w = ops.silu_mul(ops.matmul_dev_alpha(a, b1, sfa, sfb1, sx, sw))
+    got, amax_g = ops.matmul_swiglu(a, b2, sfa, sfb2, sx, sw)
+    assert torch.equal(got, want)
+    assert float(amax_g) == float(amax_w)
+    assert ops.gemm_poll_error() == 0
