@@ -474,13 +474,8 @@ struct Gemm2Params {
   unsigned int* amax;
   const int* groups;
   int ngroups;
+  const uint16_t* silu_table;   // bf16(silu(g)) for all 65536 bf16 patterns g (device memory, see silu_table_ptr)
 };
-
-// SiLU of a bf16 value, rounded to bf16, exactly as arcq_silu_mul_bf16 (and eager torch) compute it.
-__device__ __forceinline__ float silu_bf16_exact(float g) {
-  const float s = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
-  return __uint_as_float(pack_bf16x2(s, 0.f) << 16);
-}
 
 // Tile order of the persistent pairs: bands of group_m tile rows, and inside a band column by column.
 // The ~74 tiles in flight at any time then cover about group_m x (74 / group_m) tiles, so every strip of
@@ -672,10 +667,12 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         uint32_t m = 0;
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
+          // SiLU of a bf16 value is one of 65536 results: looked up (the table stays in L2; evaluating
+          // expf and a division 128 times per row made the epilogue slower than the tile's MMAs)
           const uint32_t g = o[j], u = o[64 + j];
-          const float a = silu_bf16_exact(__uint_as_float(g << 16)) * __uint_as_float(u << 16);
-          const float b = silu_bf16_exact(__uint_as_float(g & 0xffff0000u)) * __uint_as_float(u & 0xffff0000u);
-          o[j] = pack_bf16x2(a, b);
+          const float sa = __uint_as_float((uint32_t)__ldg(p.silu_table + (g & 0xffffu)) << 16);
+          const float sb = __uint_as_float((uint32_t)__ldg(p.silu_table + (g >> 16)) << 16);
+          o[j] = pack_bf16x2(sa * __uint_as_float(u << 16), sb * __uint_as_float(u & 0xffff0000u));
           asm("max.u16x2 %0, %0, %1;" : "+r"(m) : "r"(o[j] & 0x7fff7fffu));
         }
         uint32_t v = row < row_end ? max(m & 0xffffu, m >> 16) : 0u;
@@ -923,7 +920,12 @@ int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
   p.tile_group = tile_group;
   CUtensorMap ma, mb, msa, msb, mc;
-  if (swiglu_amax != nullptr) ARCQ_CUDA_TRY(cudaMemsetAsync(swiglu_amax, 0, sizeof(float) * ngroups, stream));
+  p.silu_table = nullptr;
+  if (swiglu_amax != nullptr) {
+    ARCQ_CUDA_TRY(cudaMemsetAsync(swiglu_amax, 0, sizeof(float) * ngroups, stream));
+    int rc_t = silu_table_ptr(stream, &p.silu_table);
+    if (rc_t != ARCQ_OK) return rc_t;
+  }
   int rc = make_c_map(&mc, gp.c, M, swiglu_amax != nullptr ? N / 2 : N);
   if (rc != ARCQ_OK) return rc;
   rc = make_operand_map(&ma, A, M, K_eff / 2, 128);

@@ -65,6 +65,9 @@ int launch_calib_stats(const void* x, int64_t rows, int K, float* chan_absmax, u
                        cudaStream_t stream);
 int launch_silu_mul_grouped(const void* gu, void* out, int64_t rows, int F, const int* tile_group, const int* groups,
                             int ngroups, float* amax, cudaStream_t stream);
+// Device address of the 65536-entry table bf16(silu(g)) on the current device; the first call per device
+// builds it on `stream`, later calls on other streams wait for that (arcq_layer.cu).
+int silu_table_ptr(cudaStream_t stream, const uint16_t** out);
 int gemm_poll_error();
 // Same for the bounded waits of the warp-specialised quantizer.
 int quant_poll_error();

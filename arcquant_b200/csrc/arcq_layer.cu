@@ -527,6 +527,24 @@ int launch_rope(void* x, const float* cos_t, const float* sin_t, int64_t tokens,
   return ARCQ_OK;
 }
 
+int silu_table_ptr(cudaStream_t stream, const uint16_t** out) {
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  rc = ensure_silu_table(di.device, stream);
+  if (rc != ARCQ_OK) return rc;
+  static std::mutex mu;
+  static const uint16_t* addr[64] = {};
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[di.device] == nullptr) {
+    void* ptr = nullptr;
+    ARCQ_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_silu_table));   // with that device current
+    addr[di.device] = static_cast<const uint16_t*>(ptr);
+  }
+  *out = addr[di.device];
+  return ARCQ_OK;
+}
+
 int launch_silu_mul_grouped(const void* gu, void* out, int64_t rows, int F, const int* tile_group, const int* groups,
                             int ngroups, float* amax, cudaStream_t stream) {
   if (amax) ARCQ_CUDA_TRY(cudaMemsetAsync(amax, 0, sizeof(float) * ngroups, stream));
