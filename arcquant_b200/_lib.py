@@ -58,7 +58,15 @@ SIGNATURES = {
     "arcq_matmul_nvfp4_swiglu": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "arcq_matmul_nvfp4_grouped_swiglu": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp]),
     "arcq_moe_combine_bf16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
+    "arcq_matmul_nvfp4_scatter": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _vp]),
+    "arcq_sum_partials_bf16": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp]),
+    "arcq_peer_alloc": (_i32, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "arcq_peer_free": (_i32, [_vp]),
+    "arcq_peer_export": (_i32, [_vp, C.c_char_p]),
+    "arcq_peer_open": (_i32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "arcq_peer_close": (_i32, [_vp]),
 }
+PEER_HANDLE_BYTES = 64
 
 _lib = None
 

@@ -1,5 +1,6 @@
 // C-ABI entry points of libarcq.so: argument validation, then the kernel launchers.
 #include <cuda_runtime.h>
+#include <string.h>
 #include <stdint.h>
 
 #include <atomic>
@@ -315,6 +316,70 @@ int arcq_matmul_nvfp4_grouped_swiglu(const uint8_t* A, const uint8_t* B, const u
   if (!tile_group || !groups || !alpha_a || !amax) return ARCQ_ERR_NULL_POINTER;
   return launch_gemm_grouped(A, B, SFA, SFB, M_bound, N, K_eff, tile_group, ngroups, alpha_a, alpha_b, C,
                              (cudaStream_t)stream, amax, groups);
+}
+
+int arcq_matmul_nvfp4_scatter(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                              int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b,
+                              void* const* dests, int ndests, void* stream) {
+  if (!dests || ndests < 1 || ndests > 8) return dests ? ARCQ_ERR_BAD_SHAPE : ARCQ_ERR_NULL_POINTER;
+  int rc = check_gemm(A, B, SFA, SFB, M, N, K_eff, dests[0]);
+  if (rc != ARCQ_OK || M == 0) return rc;
+  if (M % ndests || (M / ndests) % 32) return ARCQ_ERR_BAD_SHAPE;
+  for (int d = 0; d < ndests; ++d) {
+    if (!dests[d]) return ARCQ_ERR_NULL_POINTER;
+    if (!aligned16(dests[d])) return ARCQ_ERR_ALIGNMENT;
+  }
+  if (!alpha_a) return ARCQ_ERR_NULL_POINTER;
+  return launch_gemm_scatter(A, B, SFA, SFB, M, N, K_eff, alpha_a, alpha_b, dests, ndests, (cudaStream_t)stream);
+}
+
+int arcq_sum_partials_bf16(const void* const* srcs, int n, int64_t elems, const void* residual, void* out,
+                           void* stream) {
+  if (elems < 0 || elems % 8 || n < 1 || n > 8) return ARCQ_ERR_BAD_SHAPE;
+  if (elems == 0) return ARCQ_OK;
+  if (!srcs || !out) return ARCQ_ERR_NULL_POINTER;
+  for (int s = 0; s < n; ++s) {
+    if (!srcs[s]) return ARCQ_ERR_NULL_POINTER;
+    if (!aligned16(srcs[s])) return ARCQ_ERR_ALIGNMENT;
+  }
+  if (!aligned16(out) || (residual && !aligned16(residual))) return ARCQ_ERR_ALIGNMENT;
+  return launch_sum_partials(srcs, n, elems, residual, out, (cudaStream_t)stream);
+}
+
+int arcq_peer_alloc(size_t bytes, void** ptr) {
+  if (!ptr) return ARCQ_ERR_NULL_POINTER;
+  if (bytes == 0) return ARCQ_ERR_BAD_SHAPE;
+  *ptr = nullptr;
+  ARCQ_CUDA_TRY(cudaMalloc(ptr, bytes));
+  return ARCQ_OK;
+}
+
+int arcq_peer_free(void* ptr) {
+  if (ptr) ARCQ_CUDA_TRY(cudaFree(ptr));
+  return ARCQ_OK;
+}
+
+int arcq_peer_export(void* ptr, unsigned char* handle) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == ARCQ_PEER_HANDLE_BYTES, "handle size");
+  if (!ptr || !handle) return ARCQ_ERR_NULL_POINTER;
+  cudaIpcMemHandle_t h;
+  ARCQ_CUDA_TRY(cudaIpcGetMemHandle(&h, ptr));
+  memcpy(handle, &h, sizeof(h));
+  return ARCQ_OK;
+}
+
+int arcq_peer_open(const unsigned char* handle, void** ptr) {
+  if (!handle || !ptr) return ARCQ_ERR_NULL_POINTER;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  *ptr = nullptr;
+  ARCQ_CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return ARCQ_OK;
+}
+
+int arcq_peer_close(void* ptr) {
+  if (ptr) ARCQ_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return ARCQ_OK;
 }
 
 int arcq_absmax_bf16(const void* x, int64_t n, float* out, int accumulate, void* stream) {

@@ -475,6 +475,17 @@ struct Gemm2Params {
   const int* groups;
   int ngroups;
   const uint16_t* silu_table;   // bf16(silu(g)) for all 65536 bf16 patterns g (device memory, see silu_table_ptr)
+  // Scattered output (0 = off): rows [d * rows_per_dest, (d + 1) * rows_per_dest) of the result go to output
+  // map d, a [rows_per_dest, N] buffer of its own - in a tensor-parallel group, this rank's slot in the memory
+  // of the rank that owns those rows (a peer's memory over NVLink, or local memory).  A multiple of 32: one
+  // bulk store carries 32 rows.
+  int rows_per_dest;
+};
+
+// Output maps of the CTA-pair kernel: one, or one per destination of a scattered output.
+constexpr int MAX_DESTS = 8;
+struct OutputMaps {
+  CUtensorMap m[MAX_DESTS];
 };
 
 // Tile order of the persistent pairs: bands of group_m tile rows, and inside a band column by column.
@@ -494,7 +505,7 @@ template <bool SWIGLU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C2_THREADS, 1)
 arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                  const __grid_constant__ CUtensorMap map_c, const Gemm2Params p) {
+                  const __grid_constant__ OutputMaps maps_c, const Gemm2Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -690,6 +701,13 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // columns >= N themselves, and keep the load/store pipe free for the scale warps.
         const int row0 = tm * 256 + (int)rank * 128 + quad * 32;
         const uint32_t cst = cstage_base + (uint32_t)quad * 8192u;
+        const CUtensorMap* map_c = &maps_c.m[0];
+        int row_st = row0;
+        if (p.rows_per_dest) {       // these 32 rows belong to one destination
+          const int d = row0 / p.rows_per_dest;
+          map_c = &maps_c.m[d];
+          row_st = row0 - d * p.rows_per_dest;
+        }
         if (row0 < p.M) {
 #pragma unroll
           for (int h = 0; h < (SWIGLU ? 1 : 2); ++h) {
@@ -713,8 +731,8 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               for (int bs = 0; bs < 2; ++bs) {
                 const int col = col0 + 64 * (2 * h + bs);
                 if (col < ncols)
-                  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_c),
-                               "r"(cst + (uint32_t)bs * 4096u), "r"(col), "r"(row0)
+                  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map_c),
+                               "r"(cst + (uint32_t)bs * 4096u), "r"(col), "r"(row_st)
                                : "memory");
               }
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -894,8 +912,10 @@ int make_c_map(CUtensorMap* map, const void* ptr, int64_t M, int64_t N) {
 // problem (for the maxima).
 int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M, int64_t N,
                 int64_t K_eff, const GemmParams& gp, int num_sms, cudaStream_t stream, const int* tile_group = nullptr,
-                int ngroups = 1, float* swiglu_amax = nullptr, const int* groups = nullptr) {
+                int ngroups = 1, float* swiglu_amax = nullptr, const int* groups = nullptr,
+                void* const* dests = nullptr, int ndests = 0) {
   Gemm2Params p;
+  p.rows_per_dest = ndests > 0 ? (int)(M / ndests) : 0;
   p.amax = reinterpret_cast<unsigned int*>(swiglu_amax);
   p.groups = groups;
   p.ngroups = ngroups;
@@ -919,14 +939,22 @@ int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   if (tile_group != nullptr) p.group_m = 4;
   if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
   p.tile_group = tile_group;
-  CUtensorMap ma, mb, msa, msb, mc;
+  CUtensorMap ma, mb, msa, msb;
+  OutputMaps mc;
   p.silu_table = nullptr;
   if (swiglu_amax != nullptr) {
     ARCQ_CUDA_TRY(cudaMemsetAsync(swiglu_amax, 0, sizeof(float) * ngroups, stream));
     int rc_t = silu_table_ptr(stream, &p.silu_table);
     if (rc_t != ARCQ_OK) return rc_t;
   }
-  int rc = make_c_map(&mc, gp.c, M, swiglu_amax != nullptr ? N / 2 : N);
+  int rc = ARCQ_OK;
+  if (ndests > 0) {
+    for (int d = 0; d < ndests && rc == ARCQ_OK; ++d) rc = make_c_map(&mc.m[d], dests[d], M / ndests, N);
+    for (int d = ndests; d < MAX_DESTS; ++d) mc.m[d] = mc.m[0];
+  } else {
+    rc = make_c_map(&mc.m[0], gp.c, M, swiglu_amax != nullptr ? N / 2 : N);
+    for (int d = 1; d < MAX_DESTS; ++d) mc.m[d] = mc.m[0];
+  }
   if (rc != ARCQ_OK) return rc;
   rc = make_operand_map(&ma, A, M, K_eff / 2, 128);
   if (rc != ARCQ_OK) return rc;
@@ -1024,6 +1052,28 @@ int launch_gemm_grouped(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, 
   p.natoms = (int)((K_eff / 16 + 3) / 4);
   p.splits = 1;
   return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream, tile_group, ngroups, swiglu_amax, groups);
+}
+
+// The GEMM whose result rows are scattered over `ndests` buffers of M / ndests rows each (see
+// Gemm2Params::rows_per_dest): always the CTA-pair kernel, whose epilogue stores through tensor maps.
+int launch_gemm_scatter(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                        int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b, void* const* dests,
+                        int ndests, cudaStream_t stream) {
+  if (ndests < 1 || ndests > MAX_DESTS || M % ndests || (M / ndests) % 32) return ARCQ_ERR_BAD_SHAPE;
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  GemmParams p = {};
+  p.c = nullptr;
+  p.alpha_a = alpha_a;
+  p.alpha_b = alpha_b;
+  p.alpha = 1.0f;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.ksteps_total = (int)(K_eff / 64);
+  p.natoms = (int)((K_eff / 16 + 3) / 4);
+  p.splits = 1;
+  return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream, nullptr, 1, nullptr, nullptr, dests, ndests);
 }
 
 size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K_eff) {

@@ -65,6 +65,13 @@ int launch_calib_stats(const void* x, int64_t rows, int K, float* chan_absmax, u
                        cudaStream_t stream);
 int launch_silu_mul_grouped(const void* gu, void* out, int64_t rows, int F, const int* tile_group, const int* groups,
                             int ngroups, float* amax, cudaStream_t stream);
+// GEMM whose result rows go to `ndests` buffers of M / ndests rows each (host array of device addresses; peers'
+// memory allowed), and the sum of `n` partial results plus an optional residual (arcq_layer.cu).
+int launch_gemm_scatter(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                        int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b, void* const* dests,
+                        int ndests, cudaStream_t stream);
+int launch_sum_partials(const void* const* srcs, int n, int64_t elems, const void* residual, void* out,
+                        cudaStream_t stream);
 // Device address of the 65536-entry table bf16(silu(g)) on the current device; the first call per device
 // builds it on `stream`, later calls on other streams wait for that (arcq_layer.cu).
 int silu_table_ptr(cudaStream_t stream, const uint16_t** out);

@@ -280,6 +280,40 @@ __global__ void arcq_moe_combine_kernel(const uint16_t* __restrict__ y, const in
   }
 }
 
+// out = residual + bf16(src[0] + src[1] + ... + src[n-1]): the partial results of a row-parallel projection
+// added in fp32 in the order of the sources (the same on every rank), rounded to the output type once, then
+// the bf16 addition of the residual stream.  The sources are this rank's receive slots (local memory that the
+// peers' GEMMs wrote) or, for a caller that pulls, addresses in the peers' memory.  One thread = 8 elements.
+struct SumSources {
+  const uint4* p[8];
+};
+__global__ void arcq_sum_partials_kernel(const SumSources src, int n, long long nvec, const uint4* __restrict__ residual,
+                                         uint4* __restrict__ out) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int s = 0; s < n; ++s) {
+      const uint4 a = __ldcs(src.p[s] + i);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        acc[2 * q] = __fadd_rn(acc[2 * q], lo_f(aw[q]));
+        acc[2 * q + 1] = __fadd_rn(acc[2 * q + 1], hi_f(aw[q]));
+      }
+    }
+    uint32_t y[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) y[q] = pack2(acc[2 * q], acc[2 * q + 1]);
+    if (residual != nullptr) {
+      const uint4 r = __ldcs(residual + i);
+      const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) y[q] = pack2(__fadd_rn(lo_f(rw[q]), lo_f(y[q])), __fadd_rn(hi_f(rw[q]), hi_f(y[q])));
+    }
+    out[i] = make_uint4(y[0], y[1], y[2], y[3]);
+  }
+}
+
 // Per-run max|x| of grouped rows: run e holds rows [groups[e], groups[e] + groups[ngroups + e]) of the
 // (padded) row numbering; row r of that numbering is input row row_map[r] (or r).  One warp per row.
 __global__ void arcq_absmax_grouped_kernel(const uint16_t* __restrict__ x, const int* __restrict__ row_map,
@@ -507,6 +541,24 @@ int launch_moe_combine(const void* y, const int* pos, const void* w, void* out, 
   arcq_moe_combine_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(y), pos,
                                                                 static_cast<const uint16_t*>(w),
                                                                 static_cast<uint16_t*>(out), tokens, hidden, k);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
+
+int launch_sum_partials(const void* const* srcs, int n, int64_t elems, const void* residual, void* out,
+                        cudaStream_t stream) {
+  if (elems == 0) return ARCQ_OK;
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  SumSources src = {};
+  for (int s = 0; s < n; ++s) src.p[s] = static_cast<const uint4*>(srcs[s]);
+  const long long nvec = elems / 8;
+  long long blocks = (nvec + 255) / 256;
+  const long long cap = (long long)di.num_sms * 16;
+  if (blocks > cap) blocks = cap;
+  arcq_sum_partials_kernel<<<(unsigned)blocks, 256, 0, stream>>>(src, n, nvec, static_cast<const uint4*>(residual),
+                                                                static_cast<uint4*>(out));
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
 }

@@ -358,13 +358,7 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
             attn = attn.transpose(1, 2).reshape(T, nq).contiguous()
         with self._ph("quantize"):
             qa, sfo, so = NVFP4_reorder_quantize_x(attn, self.o.index, self.o.select_num, mode=16)
-        with self._ph("gemm"):
-            y = self.o.gemm(qa, sfo, so)
-        y_s = torch.empty_like(x_shard)
-        with self._ph("collective"):
-            dist.reduce_scatter_tensor(y_s, y, op=dist.ReduceOp.SUM, group=self.group)
-        with self._ph("glue"):
-            h_s = x_shard + y_s
+        h_s = self._reduce_rows(self.o, qa, sfo, so, x_shard, self.peer_o)
         with self._ph("quantize"):
             a_s, sfa_s = ops.rmsnorm_quantize_x(h_s, self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
         with self._ph("collective"):
@@ -373,13 +367,59 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
             act, amax = self._gate_up_act(a, sfa)
         with self._ph("quantize"):
             qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16, amax=amax)
+        return self._reduce_rows(self.down, qd, sfd, sd, h_s, self.peer_down)
+
+    # ---- row-parallel projection + reduce-scatter + residual
+    peer_o = None       # peer.PeerSlots of the o / down projections once `enable_peer_scatter` has run
+    peer_down = None
+
+    def enable_peer_scatter(self, total_rows: int) -> None:
+        """Sequence-parallel steps over `total_rows` tokens from now on send the partial results of the o and down
+        projections straight from the GEMM's epilogue into the owning rank's memory (`ops.matmul_scatter`) and
+        finish the reduce-scatter with a barrier and one local pass that also adds the residual
+        (`ops.sum_partials`), instead of a GEMM into local memory followed by NCCL's reduce-scatter and an
+        addition.  Collective call: every rank of the group, same arguments.  The ranks must share one machine."""
+        from .peer import PeerSlots
+
+        rows_s = total_rows // self.tp
+        if rows_s * self.tp != total_rows or rows_s % 128:
+            raise ValueError("token shards must be equal and multiples of 128 rows")
+        dev = self.ln1.device
+        # (two blocks: the barrier of one projection and the all-gather that follows it separate a block's
+        # readers from its next writers)
+        self.peer_o = PeerSlots(rows_s, self.cfg.hidden, self.rank, self.tp, self.group, dev)
+        self.peer_down = PeerSlots(rows_s, self.cfg.hidden, self.rank, self.tp, self.group, dev)
+        self._peer_flag = torch.zeros(1, dtype=torch.float32, device=dev)
+
+    def disable_peer_scatter(self) -> None:
+        for name in ("peer_o", "peer_down"):
+            slots = getattr(self, name)
+            if slots is not None:
+                slots.close()
+            setattr(self, name, None)
+
+    def _reduce_rows(self, lin: PackedLinear, q, sf, scale_x, residual_s: torch.Tensor, slots) -> torch.Tensor:
+        """residual_s + (this rank's token rows of the sum over ranks of x_r W_r^T)."""
+        import torch.distributed as dist
+
+        if slots is not None and slots.rows == residual_s.shape[0]:
+            with self._ph("gemm"):
+                ops.matmul_scatter(q, lin.W, sf, lin.SFW, scale_x, lin.scale, slots.dests)
+            with self._ph("collective"):
+                # every rank's GEMM (and with it every store into this rank's slots) is complete once this small
+                # all-reduce, which follows the GEMM in each rank's stream, has finished here
+                if self.tp > 1:
+                    dist.all_reduce(self._peer_flag, group=self.group)
+            with self._ph("glue"):
+                out = torch.empty_like(residual_s)
+                return ops.sum_partials(slots.sources, residual_s.numel(), out, residual_s)
         with self._ph("gemm"):
-            y = self.down.gemm(qd, sfd, sd)
+            y = lin.gemm(q, sf, scale_x)
+        y_s = torch.empty_like(residual_s)
         with self._ph("collective"):
             dist.reduce_scatter_tensor(y_s, y, op=dist.ReduceOp.SUM, group=self.group)
         with self._ph("glue"):
-            out = h_s + y_s
-        return out
+            return residual_s + y_s
 
     # ---- the same with communication hidden behind compute
     @staticmethod

@@ -6,6 +6,8 @@ These are thin: shape bookkeeping in Python, every byte of work in libarcq.so.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
 from . import _lib
@@ -438,3 +440,50 @@ def moe_combine(y: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor) -> to
 
 def gemm_poll_error() -> int:
     return int(_lib.load().arcq_gemm_poll_error())
+
+
+def matmul_scatter(a, b, sfa, sfb, alpha_a: torch.Tensor, alpha_b: torch.Tensor | None, dests) -> None:
+    """GEMM of `matmul_dev_alpha` whose result rows leave for len(dests) buffers of M / len(dests) rows each:
+    dests are device addresses (ints) of bf16 [M / len(dests), N] blocks - receive slots in the peers' memory
+    (see `peer.PeerSlots`) or local memory."""
+    lib = _lib.load()
+    for t, name in ((a, "A"), (b, "B"), (sfa, "SFA"), (sfb, "SFB")):
+        _require(t, torch.uint8, name)
+    _require(alpha_a, torch.float32, "alpha_a")
+    if alpha_b is not None:
+        _require(alpha_b, torch.float32, "alpha_b")
+    m, kb = a.shape
+    n = b.shape[0]
+    nd = len(dests)
+    if b.shape[1] != kb:
+        raise RuntimeError("A and B disagree on K")
+    if nd < 1 or nd > 8 or m % nd or (m // nd) % 32:
+        raise RuntimeError("rows must split evenly over 1..8 destinations, in multiples of 32")
+    atoms = (kb * 2 // 16 + 3) // 4
+    if sfa.numel() < ((m + 127) // 128) * atoms * 512 or sfb.numel() < ((n + 127) // 128) * atoms * 512:
+        raise RuntimeError("scale buffers are smaller than the scale layout of their operands")
+    arr = (C.c_void_p * nd)(*[int(d) for d in dests])
+    with torch.cuda.device(a.device):
+        rc = lib.arcq_matmul_nvfp4_scatter(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, kb * 2,
+                                           alpha_a.data_ptr(), None if alpha_b is None else alpha_b.data_ptr(),
+                                           arr, nd, _stream())
+    _lib.check(rc, f"scatter matmul M={m} N={n} K={kb * 2} dests={nd}")
+
+
+def sum_partials(srcs, elems: int, out: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """out = residual + bf16(sum of the bf16 blocks at the device addresses `srcs`, fp32, in that order)."""
+    lib = _lib.load()
+    _require(out, torch.bfloat16, "out")
+    if residual is not None:
+        _require(residual, torch.bfloat16, "residual")
+        if residual.numel() != elems:
+            raise RuntimeError("residual and sources disagree on the element count")
+    if out.numel() != elems or elems % 8:
+        raise RuntimeError("out must hold `elems` elements, a multiple of 8")
+    n = len(srcs)
+    arr = (C.c_void_p * n)(*[int(p) for p in srcs])
+    with torch.cuda.device(out.device):
+        rc = lib.arcq_sum_partials_bf16(arr, n, elems, None if residual is None else residual.data_ptr(),
+                                        out.data_ptr(), _stream())
+    _lib.check(rc, f"sum of {n} partials, {elems} elements")
+    return out

@@ -562,6 +562,22 @@ def layer_measure(dev, world, rank, steps, hbm_peak, tf_peak):
     if sp:
         res["form"] = ("sequence-parallel: residual stream sharded by tokens, RMSNorm + quantize on the shard, all-gather "
                        "of packed codes and block scales, reduce-scatter after the row-parallel GEMMs")
+    if sp:
+        # first with NCCL's reduce-scatter behind the row-parallel GEMMs, then - the form reported - with the GEMMs'
+        # epilogues storing into the owners' memory (falls back to the NCCL form, and says so, if the peers'
+        # memory cannot be mapped)
+        ms_e = max_over_ranks(time_ms(step, steps), dev)
+        g_nccl = GraphedStep(step)
+        ms_g = max_over_ranks(time_ms(g_nccl, steps), dev)
+        res["nccl_reduce_scatter_form"] = {"eager_ms": ms_e, "ms": ms_g, "tokens_per_s": T / (ms_g * 1e-3)}
+        del g_nccl
+        try:
+            layer.enable_peer_scatter(T)
+            res["form"] += ("; row-parallel GEMMs store their tiles straight into the owning rank's memory over NVLink "
+                            "(arcq_matmul_nvfp4_scatter), the reduce-scatter ends with a barrier and one local pass that "
+                            "also adds the residual (arcq_sum_partials_bf16)")
+        except Exception as exc:
+            res["peer_scatter_error"] = repr(exc)[:300]
     res["eager_ms"] = max_over_ranks(time_ms(step, steps), dev)
     graphed = GraphedStep(step)
     res["ms"] = max_over_ranks(time_ms(graphed, steps), dev)
@@ -578,10 +594,16 @@ def layer_measure(dev, world, rank, steps, hbm_peak, tf_peak):
     res["eager_phase_ms"] = {k: v / 3 for k, v in tot.items()}
     if sp:
         ph = res["eager_phase_ms"]
-        res["limiter"] = ("collectives: two reduce-scatters of the bf16 partial sums [16384, 4096] (134 MB each) and two "
-                          "all-gathers of packed codes (39 MB each), %.2f ms of the %.2f ms eager step, not overlapped with "
-                          "compute (the per-tensor scales of the o and down inputs order the phases)" %
-                          (ph.get("collective", 0.0), sum(ph.values())))
+        if layer.peer_o is not None:
+            res["limiter"] = ("NVLink: each rank's o and down GEMMs send (N-1)/N of their bf16 result [16384, 4096] (134 MB) "
+                              "to the owners while they run (their time is in the gemm phase: %.2f ms); collective = two "
+                              "barriers and two all-gathers of packed codes (39 MB each): %.2f ms of the %.2f ms eager step" %
+                              (ph.get("gemm", 0.0), ph.get("collective", 0.0), sum(ph.values())))
+        else:
+            res["limiter"] = ("collectives: two reduce-scatters of the bf16 partial sums [16384, 4096] (134 MB each) and two "
+                              "all-gathers of packed codes (39 MB each), %.2f ms of the %.2f ms eager step, not overlapped "
+                              "with compute (the per-tensor scales of the o and down inputs order the phases)" %
+                              (ph.get("collective", 0.0), sum(ph.values())))
         ms_ar = max_over_ranks(time_ms(lambda: layer(x3, pos), max(3, steps // 2)), dev)
         res["all_reduce_form"] = {"eager_ms": ms_ar, "tokens_per_s": T / (ms_ar * 1e-3)}
         if SP_CHUNKS > 1 and LAYER_BATCH % SP_CHUNKS == 0 and (T // SP_CHUNKS // world) % 128 == 0:
@@ -615,6 +637,24 @@ def layer_measure(dev, world, rank, steps, hbm_peak, tf_peak):
     res["e2e"] = {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                   "h2d_bytes_per_step": int(hin.numel() * 2) * world, "d2h_bytes_per_step": int(hout.numel() * 2) * world}
     return res
+
+
+def tp1_reference(dev, steps):
+    """The unsharded decoder layer on this GPU alone (no collectives, nothing that involves other ranks)."""
+    import torch
+
+    from arcquant_b200 import synth
+    from arcquant_b200.graphs import GraphedStep
+
+    cfg, layer = build_layer(dev, 1, 0)
+    T = LAYER_BATCH * LAYER_SEQ
+    x3 = synth.activations(T, cfg.hidden, 7, synth.outlier_channels(cfg.hidden, 41, 1), device=dev).reshape(
+        LAYER_BATCH, LAYER_SEQ, cfg.hidden)
+    pos = torch.arange(LAYER_SEQ, device=dev)
+    graphed = GraphedStep(lambda: layer(x3, pos))
+    ms = time_ms(graphed, steps)
+    return {"ms": ms, "tokens_per_s": T / (ms * 1e-3), "parallelism": "tp1", "tokens": T,
+            "note": "rank 0 alone while the other ranks wait; same shapes, same CUDA-graph launch"}
 
 
 def moe_roofline(world: int, hbm_peak: float, tf_peak: float):
@@ -698,6 +738,17 @@ def multi_gpu_parity(dev, world, rank):
     own = mine.pipelined_shard_rows(T, world, rank, 4).to(dev)
     y_pp = mine.forward_sequence_parallel_pipelined(x2[own].contiguous(), B, S, pos, 4)
     out["sp"] = max(rel(y_sp, ref[rank * rows:(rank + 1) * rows]), rel(y_pp, ref[own]))
+    try:
+        mine.enable_peer_scatter(T)
+        y_ps = mine.forward_sequence_parallel(x2[rank * rows:(rank + 1) * rows].contiguous(), B, S, pos)
+        out["sp"] = max(out["sp"], rel(y_ps, ref[rank * rows:(rank + 1) * rows]))
+        torch.cuda.synchronize()
+    except RuntimeError as exc:
+        if "peer slots unavailable" not in str(exc):
+            raise
+    import torch.distributed as dist
+    dist.barrier()
+    mine.disable_peer_scatter()
     del ranks
     mcfg = MoEConfig(hidden=1024, ffn=2048, n_experts=8, top_k=2, select_num=64)
     MW = random_moe_weights(mcfg, 0)
@@ -709,7 +760,6 @@ def multi_gpu_parity(dev, world, rank):
         xt[lo:hi].contiguous(), routing=(ids[lo:hi].contiguous(), w[lo:hi].contiguous()))
     out["ep"] = rel(part, full[lo:hi])
     worst = torch.tensor([out["tp"], out["sp"], out["ep"]], device=dev)
-    import torch.distributed as dist
     dist.all_reduce(worst, op=dist.ReduceOp.MAX)
     out = {k: float(v) for k, v in zip(("tp", "sp", "ep"), worst.tolist())}
     if max(out.values()) > 1e-2:
@@ -946,6 +996,13 @@ def run_ours(args):
     lres = layer_measure(dev, world, rank, max(args.steps, 10), hbm_peak, tf_peak)
     clocks = sampler.stop() if rank == 0 else None
     extra = {"parity": parity, "llama_layer": lres}
+    if rank == 0:
+        # the same layer unsharded on rank 0 alone, the other ranks idle: the one-GPU point of the same quantity
+        try:
+            extra["tp1_same_run"] = tp1_reference(dev, 10)
+        except Exception as exc:
+            extra["tp1_same_run_error"] = repr(exc)[:300]
+    dist.barrier()
     try:
         extra["moe_block"] = moe_measure(dev, world, rank, 10, hbm_peak, tf_peak)
     except Exception as exc:

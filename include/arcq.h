@@ -296,6 +296,39 @@ int arcq_matmul_nvfp4_grouped_swiglu(const uint8_t* A, const uint8_t* B, const u
                                      const int32_t* groups, int ngroups, const float* alpha_a, const float* alpha_b,
                                      void* C, float* amax, void* stream);
 
+/* ---- Row-parallel projection fused with its reduce-scatter over peer memory -----------------------------
+ * No counterpart in the reference (it runs on one GPU, model/qLlamaLayer.py:364, 442); these serve the
+ * tensor-parallel form of its decoder layer, where the o and down projections are sharded by K and their
+ * partial results must be added over the ranks, each rank keeping the token rows it owns.
+ *
+ * arcq_matmul_nvfp4_scatter: the GEMM of arcq_matmul_nvfp4_dev_alpha whose epilogue stores rows
+ *   [d * M / ndests, (d + 1) * M / ndests) of the result into dests[d], a bf16 [M / ndests, N] buffer of its
+ *   own (host array of ndests <= 8 device addresses).  In a tensor-parallel group dests[d] is this rank's
+ *   receive slot in the memory of rank d (an address obtained with arcq_peer_open, or local memory for
+ *   d == this rank): every output tile leaves for its owner over NVLink as soon as it is computed, while the
+ *   tensor cores work on the next tile.  M % ndests == 0, (M / ndests) % 32 == 0.  Always the CTA-pair kernel.
+ * arcq_sum_partials_bf16: out = residual + bf16(srcs[0] + ... + srcs[n-1]) over `elems` bf16 elements
+ *   (fp32 accumulation in the order given, one rounding, then the bf16 residual addition; residual may be
+ *   NULL): what a rank runs over its n receive slots once every peer's GEMM has finished (the caller orders
+ *   that, e.g. with a barrier of its communication library on the same stream).  srcs: host array of n <= 8
+ *   device addresses; elems % 8 == 0.
+ * arcq_peer_alloc / _free: device memory from cudaMalloc (not from a framework's pool), which is what
+ *   arcq_peer_export can describe; _export writes the 64-byte handle another process on the same machine
+ *   passes to arcq_peer_open, which maps the block into the calling process and enables peer access from the
+ *   current device; _close unmaps it.  Handles travel by any host channel (the Python layer uses its process
+ *   group's all_gather_object). */
+#define ARCQ_PEER_HANDLE_BYTES 64
+int arcq_matmul_nvfp4_scatter(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                              int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b,
+                              void* const* dests, int ndests, void* stream);
+int arcq_sum_partials_bf16(const void* const* srcs, int n, int64_t elems, const void* residual, void* out,
+                           void* stream);
+int arcq_peer_alloc(size_t bytes, void** ptr);
+int arcq_peer_free(void* ptr);
+int arcq_peer_export(void* ptr, unsigned char* handle);
+int arcq_peer_open(const unsigned char* handle, void** ptr);
+int arcq_peer_close(void* ptr);
+
 #ifdef __cplusplus
 }
 #endif

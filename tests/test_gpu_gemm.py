@@ -276,3 +276,67 @@ def test_cta_pair_kernel_on_ragged_tiles(m, n):
                       sf_take_rows(sfb, cols, k_eff), alpha)
     got = c[rt][:, ct].float().cpu().numpy()
     _assert_close(got, ref)
+
+
+@pytest.mark.parametrize("m,n,nd", [(1024, 2048, 4), (2048, 4096, 8), (768, 2056, 8), (1024, 1024, 1), (4096, 4096, 2)])
+def test_scattered_output_rows_land_in_their_destinations(m, n, nd):
+    """`matmul_scatter`: rows [d M/nd, (d+1) M/nd) of the result go to destination d (here: separate local
+    buffers standing for the peers' receive slots).  The bytes are those of the plain GEMM on the CTA-pair
+    kernel (same tiles, same accumulation order - only the address of each bulk store changes), which the
+    other tests of this file hold to the oracle; rows_per_dest 96 makes destinations change inside a 256-row
+    tile, and memory around every destination must stay untouched."""
+    ops = _ops()
+    kq, ke = 1024, 64
+    dev = "cuda:0"
+    out = synth.outlier_channels(kq, kq // 100, 1)
+    x = synth.activations(m, kq, m + 2, out, device=dev)
+    w = synth.weights(n, kq, n + 3, device=dev)
+    idx = synth.reorder_index_from_stats(x[:512].abs().amax(0)).to(dev)
+    sx, sw = ops.absmax(x) / 2688.0, ops.absmax(w) / 2688.0
+    a, sfa = ops.reorder_quantize_x((x / sx).to(torch.bfloat16), idx, ke)
+    b, sfb = ops.reorder_quantize_w((w / sw).to(torch.bfloat16), idx, ke)
+    rows = m // nd
+    guard = torch.full((nd, rows + 16, n), 7.0, dtype=torch.bfloat16, device=dev)
+    dests = [guard[d, 8:].data_ptr() for d in range(nd)]
+    ops.matmul_scatter(a, b, sfa, sfb, sx, sw, dests)
+    torch.cuda.synchronize()
+    assert ops.gemm_poll_error() == 0
+    # the reference bytes: the same kernel with one destination (the plain launcher may pick the single-CTA
+    # kernel for the small shapes, whose accumulation order differs in the last bit)
+    whole = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    ops.matmul_scatter(a, b, sfa, sfb, sx, sw, [whole.data_ptr()])
+    plain = ops.matmul_dev_alpha(a, b, sfa, sfb, sx, sw)
+    torch.cuda.synchronize()
+    assert torch.equal(guard[:, 8:8 + rows].reshape(m, n), whole)
+    assert bool((guard[:, :8] == 7.0).all()) and bool((guard[:, 8 + rows:] == 7.0).all())
+    err = float((whole.float() - plain.float()).norm() / plain.float().norm())
+    assert err < TOL, err
+    assert float((whole == plain).float().mean()) > 0.99
+
+
+def test_scattered_output_against_the_oracle():
+    """One scattered launch held to the oracle directly (sampled rows of every destination)."""
+    from tests.helpers import sf_take_rows
+
+    ops, O = _ops(), _oracle()
+    m, n, kq, ke, nd = 2048, 2304, 2048, 128, 8
+    k_eff = kq + ke
+    dev = "cuda:0"
+    out = synth.outlier_channels(kq, kq // 100, 5)
+    x = synth.activations(m, kq, 11, out, device=dev)
+    w = synth.weights(n, kq, 12, device=dev)
+    idx = synth.reorder_index_from_stats(x[:512].abs().amax(0)).to(dev)
+    sx, sw = ops.absmax(x) / 2688.0, ops.absmax(w) / 2688.0
+    a, sfa = ops.reorder_quantize_x((x / sx).to(torch.bfloat16), idx, ke)
+    b, sfb = ops.reorder_quantize_w((w / sw).to(torch.bfloat16), idx, ke)
+    slots = torch.zeros((nd, m // nd, n), dtype=torch.bfloat16, device=dev)
+    ops.matmul_scatter(a, b, sfa, sfb, sx, sw, [slots[d].data_ptr() for d in range(nd)])
+    torch.cuda.synchronize()
+    assert ops.gemm_poll_error() == 0
+    g = torch.Generator().manual_seed(3)
+    rows = np.asarray(sorted(set([0, 255, 256, 257, m - 1] + torch.randint(0, m, (40,), generator=g).tolist())), dtype=np.int64)
+    rt = torch.from_numpy(rows).to(dev)
+    ref = O.gemm_fast(a[rt].cpu().numpy(), sf_take_rows(sfa, rows, k_eff), b.cpu().numpy(), sfb.cpu().numpy(),
+                      float(sx * sw))
+    got = slots.reshape(m, n)[rt].float().cpu().numpy()
+    _assert_close(got, ref)

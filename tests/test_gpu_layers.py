@@ -508,3 +508,88 @@ def test_swiglu_epilogue_equals_gemm_then_silu(m, f, kq):
     assert torch.equal(got, want)
     assert float(amax_g) == float(amax_w)
     assert ops.gemm_poll_error() == 0
+
+
+@pytest.mark.parametrize("n,elems", [(1, 4096), (2, 1 << 20), (4, 3 * 4096 * 8), (8, 2048 * 4096)])
+def test_sum_of_partials_equals_fp32_sum_in_order(n, elems):
+    """`sum_partials`: fp32 sum of the sources in the order given, one rounding to bf16, then the bf16 residual
+    addition - bit for bit what torch computes with the same steps."""
+    from arcquant_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(n)
+    parts = torch.randn((n, elems), generator=g, device="cuda").to(torch.bfloat16)
+    res = torch.randn((elems,), generator=g, device="cuda").to(torch.bfloat16)
+    acc = torch.zeros(elems, dtype=torch.float32, device="cuda")
+    for s in range(n):
+        acc = acc + parts[s].float()
+    want_plain = acc.to(torch.bfloat16)
+    want = res + want_plain
+    out = torch.empty(elems, dtype=torch.bfloat16, device="cuda")
+    srcs = [parts[s].data_ptr() for s in range(n)]
+    assert torch.equal(ops.sum_partials(srcs, elems, out), want_plain)
+    assert torch.equal(ops.sum_partials(srcs, elems, out, res), want)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_projection_with_scattered_output_and_local_sum_equals_reduce_scatter(world):
+    """The reduce-scatter of a row-parallel projection as the tensor-parallel layer runs it over peer memory,
+    with all ranks' receive blocks on one GPU: every rank's GEMM stores its rows for owner d into slot
+    [d][rank], every owner adds its slots and the residual.  Must equal residual + bf16(sum over ranks of the
+    plain GEMM's rows) computed with torch."""
+    from arcquant_b200 import ops
+
+    dev = "cuda:0"
+    tokens, hidden, k_local, ke = 1024, 1024, 512, 64
+    rows = tokens // world
+    blocks = torch.zeros((world, world, rows, hidden), dtype=torch.bfloat16, device=dev)   # [owner][source]
+    partial = []
+    for r in range(world):
+        out = synth.outlier_channels(k_local, 5, r)
+        x = synth.activations(tokens, k_local, 20 + r, out, device=dev)
+        w = synth.weights(hidden, k_local, 40 + r, device=dev)
+        idx = synth.reorder_index_from_stats(x[:256].abs().amax(0)).to(dev)
+        sx, sw = ops.absmax(x) / 2688.0, ops.absmax(w) / 2688.0
+        a, sfa = ops.reorder_quantize_x((x / sx).to(torch.bfloat16), idx, ke)
+        b, sfb = ops.reorder_quantize_w((w / sw).to(torch.bfloat16), idx, ke)
+        ops.matmul_scatter(a, b, sfa, sfb, sx, sw, [blocks[d, r].data_ptr() for d in range(world)])
+        whole = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
+        ops.matmul_scatter(a, b, sfa, sfb, sx, sw, [whole.data_ptr()])
+        partial.append(whole)
+    torch.cuda.synchronize()
+    assert ops.gemm_poll_error() == 0
+    residual = synth.activations(tokens, hidden, 7, synth.outlier_channels(hidden, 10, 3), device=dev)
+    acc = torch.zeros((tokens, hidden), dtype=torch.float32, device=dev)
+    for r in range(world):
+        acc = acc + partial[r].float()
+    want = residual + acc.to(torch.bfloat16)
+    for d in range(world):
+        out = torch.empty((rows, hidden), dtype=torch.bfloat16, device=dev)
+        ops.sum_partials([blocks[d, s].data_ptr() for s in range(world)], rows * hidden, out,
+                         residual[d * rows:(d + 1) * rows].contiguous())
+        assert torch.equal(out, want[d * rows:(d + 1) * rows]), d
+
+
+def test_peer_slots_on_one_rank_and_the_layers_reduce_step():
+    """`PeerSlots` with a group of one (allocation, export, the tensor view) and the layer's `_reduce_rows` over
+    it: residual + the projection, the same bytes as the plain GEMM followed by an addition."""
+    from arcquant_b200 import ops
+    from arcquant_b200.llama_layer import QLlamaDecoderLayerTP, random_layer_weights, random_reorder_indices
+    from arcquant_b200.qlinear import NVFP4_reorder_quantize_x
+
+    cfg = _small_cfg()
+    W, I = random_layer_weights(cfg, 0), random_reorder_indices(cfg, 1)
+    layer = QLlamaDecoderLayerTP(cfg, W, I)
+    tokens = 256
+    layer.enable_peer_scatter(tokens)
+    try:
+        x = synth.activations(tokens, cfg.n_heads * cfg.head_dim, 4, synth.outlier_channels(cfg.hidden, 10, 3)).cuda()
+        res = synth.activations(tokens, cfg.hidden, 5, synth.outlier_channels(cfg.hidden, 10, 3)).cuda()
+        qa, sfo, so = NVFP4_reorder_quantize_x(x, layer.o.index, layer.o.select_num, mode=16)
+        got = layer._reduce_rows(layer.o, qa, sfo, so, res, layer.peer_o)
+        whole = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16, device="cuda")
+        ops.matmul_scatter(qa, layer.o.W, sfo, layer.o.SFW, so, layer.o.scale, [whole.data_ptr()])
+        torch.cuda.synchronize()
+        assert torch.equal(got, res + whole)
+        assert torch.equal(layer.peer_o.local()[0], whole)
+    finally:
+        layer.disable_peer_scatter()

@@ -69,6 +69,15 @@ def _worker(rank, world, port, q):
         err_pp = float((y_pp.float() - y_ref[own].float()).norm() / y_ref[own].float().norm())
         if err_pp > 2e-3:
             err_tp = max(err_tp, 2.0 + err_pp)
+        # the same with the row-parallel projections storing straight into the owners' memory
+        layer.enable_peer_scatter(512)
+        y_ps = layer.forward_sequence_parallel(x8.reshape(512, -1)[rank * rows_s:(rank + 1) * rows_s].contiguous(), 1, 512, pos8)
+        y_ps2 = layer.forward_sequence_parallel(x8.reshape(512, -1)[rank * rows_s:(rank + 1) * rows_s].contiguous(), 1, 512, pos8)
+        err_ps = float((y_ps.float() - ref_sp.float()).norm() / ref_sp.float().norm())
+        if err_ps > 2e-3 or not torch.equal(y_ps, y_ps2):
+            err_tp = max(err_tp, 3.0 + err_ps)
+        dist.barrier()
+        layer.disable_peer_scatter()
         # --- expert-parallel MoE block: same per-expert batches as one rank owning every expert
         mcfg = MoEConfig(hidden=1024, ffn=2048, n_experts=4, top_k=2, select_num=64)
         MW = random_moe_weights(mcfg, 0)
