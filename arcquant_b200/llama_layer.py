@@ -295,13 +295,15 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         if self.tp > 1 and x2d.shape[0] >= 2 * self.overlap_rows and self._dist_ready():
             return self._forward_overlapped(x2d, bsz, seq, positions).reshape(bsz, seq, hidden)
         y = self.attn_partial(x2d, bsz, seq, positions)
-        with self._ph("collective"):
-            y = tp.all_reduce_sum(y, self.group)
+        if self.tp > 1:      # (an unsharded layer inside a multi-rank process talks to nobody)
+            with self._ph("collective"):
+                y = tp.all_reduce_sum(y, self.group)
         with self._ph("glue"):
             h = x2d + y
         y = self.mlp_partial(h)
-        with self._ph("collective"):
-            y = tp.all_reduce_sum(y, self.group)
+        if self.tp > 1:
+            with self._ph("collective"):
+                y = tp.all_reduce_sum(y, self.group)
         with self._ph("glue"):
             out = h + y
         return out.reshape(bsz, seq, hidden)

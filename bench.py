@@ -519,10 +519,14 @@ def init_nccl(dist, dev):
             opts.config.min_ctas = min(NCCL_CTAS, 4)
         except Exception:
             opts = None
+    import datetime
+
+    # a collective that a peer never joins ends this run after three minutes, not after NCCL's default ten
+    limit = datetime.timedelta(seconds=180)
     if opts is not None:
-        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts, timeout=limit)
     else:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=limit)
     if SM_RESERVE > 0:
         import torch
 
