@@ -60,6 +60,9 @@ SIGNATURES = {
     "arcq_moe_combine_bf16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
     "arcq_matmul_nvfp4_scatter": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _vp]),
     "arcq_sum_partials_bf16": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp]),
+    "arcq_rmsnorm_quantize_x_multi": (_i32, [_vp, _vp, _f32, _vp, _i64, _i32, _i32, _vp, _vp, _i32, _vp]),
+    "arcq_peer_barrier": (_i32, [_vp, _i32, _i32, _vp, _vp]),
+    "arcq_peer_poll_error": (_i32, []),
     "arcq_peer_alloc": (_i32, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "arcq_peer_free": (_i32, [_vp]),
     "arcq_peer_export": (_i32, [_vp, C.c_char_p]),

@@ -130,6 +130,36 @@ int arcq_rmsnorm_quantize_x(const void* x, const void* gamma, float eps, const i
                          (cudaStream_t)stream);
 }
 
+int arcq_rmsnorm_quantize_x_multi(const void* x, const void* gamma, float eps, const int16_t* reorder_index,
+                                  int64_t M, int KQ, int KE, uint8_t* const* qx, uint8_t* const* sfx, int ndests,
+                                  void* stream) {
+  int rc = check_quant_shape(M, KQ, KE, ARCQ_MODE_16);
+  if (rc != ARCQ_OK) return rc;
+  int g = KQ / 16;
+  if (g % 32 || g < 64 || g > 512) return ARCQ_ERR_UNSUPPORTED_K;
+  if (ndests < 1 || ndests > 8) return ARCQ_ERR_BAD_SHAPE;
+  if (!qx || !sfx) return ARCQ_ERR_NULL_POINTER;
+  if (M == 0) return ARCQ_OK;
+  if (!x || !gamma) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(x)) return ARCQ_ERR_ALIGNMENT;
+  for (int d = 0; d < ndests; ++d) {
+    if (!qx[d] || !sfx[d]) return ARCQ_ERR_NULL_POINTER;
+    if (!aligned16(qx[d]) || !aligned16(sfx[d])) return ARCQ_ERR_ALIGNMENT;
+  }
+  return launch_quantize(x, gamma, eps, reorder_index, M, KQ, KE, ARCQ_MODE_16, 0, qx[0], sfx[0],
+                         (cudaStream_t)stream, nullptr, nullptr, 0, nullptr, qx + 1, sfx + 1, ndests - 1);
+}
+
+int arcq_peer_barrier(void* const* flags, int rank, int world, uint32_t* counter, void* stream) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return ARCQ_ERR_BAD_SHAPE;
+  if (!flags || !counter) return ARCQ_ERR_NULL_POINTER;
+  for (int d = 0; d < world; ++d)
+    if (!flags[d]) return ARCQ_ERR_NULL_POINTER;
+  return launch_peer_barrier(flags, rank, world, counter, (cudaStream_t)stream);
+}
+
+int arcq_peer_poll_error(void) { return peer_poll_error(); }
+
 int arcq_reorder_quantize_w(const void* w, const int16_t* reorder_index, int64_t N, int KQ, int KE, int mode,
                             uint8_t* qw, uint8_t* sfw, void* stream) {
   int rc = check_quant_shape(N, KQ, KE, mode);

@@ -30,7 +30,9 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
                     int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream,
                     const float* scale = nullptr,    // scale (device): x is divided by it first; plain x only
                     const int* groups = nullptr, int ngroups = 0,   // runs of rows with their own order and scale
-                    const int* row_map = nullptr);                  // input row of every output row
+                    const int* row_map = nullptr,                   // input row of every output row
+                    // further copies of the output (e.g. the peers' gathered buffers), see QuantParams
+                    uint8_t* const* q_extra = nullptr, uint8_t* const* sf_extra = nullptr, int nextra = 0);
 int launch_absmax(const void* x, int64_t n, float* out, int accumulate, cudaStream_t stream);
 // workspace (may be null): scratch for split-K partial sums, see gemm_workspace_bytes().
 int launch_gemm(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
@@ -70,6 +72,8 @@ int launch_silu_mul_grouped(const void* gu, void* out, int64_t rows, int F, cons
 int launch_gemm_scatter(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                         int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b, void* const* dests,
                         int ndests, cudaStream_t stream);
+int launch_peer_barrier(void* const* flags, int rank, int world, unsigned int* counter, cudaStream_t stream);
+int peer_poll_error();
 int launch_sum_partials(const void* const* srcs, int n, int64_t elems, const void* residual, void* out,
                         cudaStream_t stream);
 // Device address of the 65536-entry table bf16(silu(g)) on the current device; the first call per device

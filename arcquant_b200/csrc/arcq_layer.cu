@@ -314,6 +314,48 @@ __global__ void arcq_sum_partials_kernel(const SumSources src, int n, long long 
   }
 }
 
+// Barrier over the ranks of a tensor-parallel group through flags in peer memory.  Rank r owns a block of
+// `world` 32-bit flags; arriving at barrier number e, it writes e into flag [r] of every rank's block and
+// waits until all flags of its own block have reached e.  One CTA, thread d talks to rank d.  Everything this
+// rank's earlier kernels of the stream wrote (into its own or a peer's memory) is visible to a peer's kernels
+// that follow the peer's barrier: the kernel boundary orders those writes before this thread's system-scope
+// fence and flag store, the peer's flag load and fence order its later reads after them.
+// The wait is bounded: after `limit_ns` the kernel records ARCQ_ERR_TIMEOUT and returns.
+struct PeerFlags {
+  unsigned int* p[8];
+};
+__device__ int g_peer_error = 0;   // sticky until polled
+
+__global__ void arcq_peer_barrier_kernel(const PeerFlags f, int rank, int world, unsigned int* counter,
+                                         unsigned long long limit_ns) {
+  __shared__ unsigned int epoch_s;
+  if (threadIdx.x == 0) {
+    epoch_s = *counter + 1u;
+    *counter = epoch_s;
+  }
+  __syncthreads();
+  const unsigned int epoch = epoch_s;
+  const int d = threadIdx.x;
+  if (d < world) {
+    __threadfence_system();
+    *reinterpret_cast<volatile unsigned int*>(f.p[d] + rank) = epoch;
+    const volatile unsigned int* in = f.p[rank] + d;
+    unsigned long long t0 = 0;
+    for (unsigned int it = 0; (int)(*in - epoch) < 0; ++it) {
+      if ((it & 255u) == 255u) {
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+        if (t0 == 0) t0 = t1;
+        if (t1 - t0 > limit_ns) {
+          atomicExch(&g_peer_error, ARCQ_ERR_TIMEOUT);
+          break;
+        }
+      }
+    }
+    __threadfence_system();
+  }
+}
+
 // Per-run max|x| of grouped rows: run e holds rows [groups[e], groups[e] + groups[ngroups + e]) of the
 // (padded) row numbering; row r of that numbering is input row row_map[r] (or r).  One warp per row.
 __global__ void arcq_absmax_grouped_kernel(const uint16_t* __restrict__ x, const int* __restrict__ row_map,
@@ -543,6 +585,22 @@ int launch_moe_combine(const void* y, const int* pos, const void* w, void* out, 
                                                                 static_cast<uint16_t*>(out), tokens, hidden, k);
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
+}
+
+int launch_peer_barrier(void* const* flags, int rank, int world, unsigned int* counter, cudaStream_t stream) {
+  PeerFlags f = {};
+  for (int d = 0; d < world; ++d) f.p[d] = static_cast<unsigned int*>(flags[d]);
+  arcq_peer_barrier_kernel<<<1, 32, 0, stream>>>(f, rank, world, counter, 10000000000ull);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
+
+int peer_poll_error() {
+  int v = 0, zero = 0;
+  ARCQ_CUDA_TRY(cudaDeviceSynchronize());
+  ARCQ_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_peer_error, sizeof(int)));
+  if (v) ARCQ_CUDA_TRY(cudaMemcpyToSymbol(g_peer_error, &zero, sizeof(int)));
+  return v;
 }
 
 int launch_sum_partials(const void* const* srcs, int n, int64_t elems, const void* residual, void* out,

@@ -59,6 +59,15 @@ struct QuantParams {
   const int* row_map;
 };
 
+// Further copies of the output (warp-specialised fused RMSNorm kernel, MULTI variant): every code and scale
+// byte is also stored at its address plus dq[d] / dsf[d], d < n - the same rows of the gathered buffers of
+// the other ranks of a tensor-parallel group (peer memory), so that the all-gather happens while the rows are
+// made.
+struct ExtraDests {
+  long long dq[7], dsf[7];
+  int n;
+};
+
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
@@ -647,8 +656,10 @@ __device__ __forceinline__ void scale_of_pair_fma(uint32_t m, uint32_t& codes, f
 // for the odd last row: row 1 is stored first and row 0 overwrites it).  In every layout the codes of
 // scale column c start at byte 8 c of the row, and a critical group's residual sits 1 (mode 16) or 2
 // (mode 32) columns after its main part.
+template <bool MULTI>
 __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g, int G0, bool mode32, bool is_weight,
-                                                       uint8_t* q0, uint8_t* q1, uint8_t* sf0, uint8_t* sf1) {
+                                                       uint8_t* q0, uint8_t* q1, uint8_t* sf0, uint8_t* sf1,
+                                                       const ExtraDests& ex) {
   const uint32_t m = amax_pair_h(w);
   uint32_t codes;
   float2 dec, rcp;
@@ -664,6 +675,14 @@ __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g,
   sf1[cm] = (uint8_t)(codes >> 8);
   *reinterpret_cast<uint2*>(q0 + 8u * col) = c0;
   sf0[cm] = (uint8_t)codes;
+#pragma unroll 1
+  for (int d = 0; MULTI && d < ex.n; ++d) {
+    const long long oq = ex.dq[d], os = ex.dsf[d];
+    *reinterpret_cast<uint2*>(q1 + oq + 8u * col) = c1;
+    (sf1 + os)[cm] = (uint8_t)(codes >> 8);
+    *reinterpret_cast<uint2*>(q0 + oq + 8u * col) = c0;
+    (sf0 + os)[cm] = (uint8_t)codes;
+  }
   if (!critical) return;
 
   uint2 e0 = c0, e1 = c1;
@@ -686,6 +705,14 @@ __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g,
   sf1[cr] = (uint8_t)(rcodes >> 8);
   *reinterpret_cast<uint2*>(q0 + 8u * rcol) = e0;
   sf0[cr] = (uint8_t)rcodes;
+#pragma unroll 1
+  for (int d = 0; MULTI && d < ex.n; ++d) {
+    const long long oq = ex.dq[d], os = ex.dsf[d];
+    *reinterpret_cast<uint2*>(q1 + oq + 8u * rcol) = e1;
+    (sf1 + os)[cr] = (uint8_t)(rcodes >> 8);
+    *reinterpret_cast<uint2*>(q0 + oq + 8u * rcol) = e0;
+    (sf0 + os)[cr] = (uint8_t)rcodes;
+  }
 }
 
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
@@ -728,9 +755,10 @@ __device__ __forceinline__ float div_guard(float s) {
 // npteams producer teams of npt = KQ/16 threads (more than one only with RMSNorm, whose producers carry
 // real arithmetic), sharing the pairs the same way; producer t of a team owns the 16-byte chunks t and
 // t + KQ/16 of each row, the reference's assignment and summation order for RMSNorm.
-template <bool RMS, bool WIDE, bool SCALED, int S, int R>
+template <bool RMS, bool WIDE, bool SCALED, int S, int R, bool MULTI = false>
 __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantParams p, const int nct, const int npt, const int nteams,
-                                                                        const int npteams) {
+                                                                        const int npteams,
+                                                                        const __grid_constant__ ExtraDests ex) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x;
   const int KQ = p.KQ, G = p.G;
@@ -1208,7 +1236,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
           if (lane == 0) mbar_arrive(empty0 + 8 * s);
           released = true;
         }
-        if (live) quantize_group_pair_ws(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1);
+        if (live) quantize_group_pair_ws<MULTI>(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1, ex);
       }
       if (!released && lane == 0) mbar_arrive(empty0 + 8 * s);
       slot = slot + 1 == ncw ? 0 : slot + 1;
@@ -1235,10 +1263,10 @@ __global__ void arcq_absmax_kernel(const uint4* __restrict__ x, long long nvec, 
   if ((threadIdx.x & 31) == 0) atomicMax(out, r << 16);
 }
 
-template <bool RMS, bool WIDE, bool SCALED, int S, int R>
+template <bool RMS, bool WIDE, bool SCALED, int S, int R, bool MULTI = false>
 int launch_ws(const QuantParams& p, int nct, int npt, int nteams, int npteams, size_t smem, const DeviceInfo& di,
-              cudaStream_t stream) {
-  auto kern = arcq_quantize_ws_kernel<RMS, WIDE, SCALED, S, R>;
+              cudaStream_t stream, const ExtraDests& ex = ExtraDests()) {
+  auto kern = arcq_quantize_ws_kernel<RMS, WIDE, SCALED, S, R, MULTI>;
   const int threads = nteams * nct + npteams * (npt + (RMS ? 96 : 0));
   // the attribute and the occupancy query cost host time: once per (device, block size, shared memory)
   static thread_local int c_dev = -1, c_threads = 0, c_occ = 0;
@@ -1267,7 +1295,7 @@ int launch_ws(const QuantParams& p, int nct, int npt, int nteams, int npteams, s
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  ARCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p, nct, npt, nteams, npteams));
+  ARCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p, nct, npt, nteams, npteams, ex));
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
 }
@@ -1291,7 +1319,8 @@ int launch_variant(const QuantParams& p, int nt, size_t smem, const DeviceInfo& 
 
 int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* idx, int64_t rows, int KQ,
                     int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream, const float* scale,
-                    const int* groups, int ngroups, const int* row_map) {
+                    const int* groups, int ngroups, const int* row_map, uint8_t* const* q_extra,
+                    uint8_t* const* sf_extra, int nextra) {
   if (rows == 0) return ARCQ_OK;
   DeviceInfo di;
   int rc = get_device_info(&di);
@@ -1318,6 +1347,12 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   p.groups = groups;
   p.ngroups = ngroups;
   p.row_map = row_map;
+  ExtraDests ex = {};
+  ex.n = nextra;
+  for (int d = 0; d < nextra && d < 7; ++d) {
+    ex.dq[d] = (long long)(q_extra[d] - q);
+    ex.dsf[d] = (long long)(sf_extra[d] - sf);
+  }
 
   const bool rms = gamma != nullptr;
   int nt, cpt;
@@ -1398,6 +1433,15 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
       const size_t smem = fixed + (S + R) * stage;
       if (nteams >= 1 && smem <= (size_t)di.max_smem_optin) {
         const int kind = rms ? 0 : (p.scale ? 2 : 1);   // RMSNorm / plain / plain with the division
+        if (ex.n > 0) {   // output stored several times: the fused RMSNorm operator only
+          if (kind != 0) return ARCQ_ERR_UNSUPPORTED_K;
+#define ARCQ_WS_MULTI(S_, R_) \
+  if (S == S_ && R == R_) return launch_ws<true, false, false, S_, R_, true>(p, nct, npt, nteams, npteams, smem, di, stream, ex);
+          ARCQ_WS_MULTI(2, 2) ARCQ_WS_MULTI(2, 4) ARCQ_WS_MULTI(2, 6) ARCQ_WS_MULTI(2, 8)
+          ARCQ_WS_MULTI(4, 2) ARCQ_WS_MULTI(4, 4) ARCQ_WS_MULTI(4, 6) ARCQ_WS_MULTI(4, 8)
+#undef ARCQ_WS_MULTI
+          return ARCQ_ERR_UNSUPPORTED_K;
+        }
 #define ARCQ_WS_CASE(KIND_, RMS_, SCALED_, S_, R_) \
   if (kind == KIND_ && S == S_ && R == R_) \
     return launch_ws<RMS_, false, SCALED_, S_, R_>(p, nct, npt, nteams, npteams, smem, di, stream);
@@ -1413,7 +1457,7 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
     }
   }
   // only the warp-specialised kernel divides by the scale, walks grouped rows or follows a row map
-  if (p.scale || p.groups || p.row_map) return ARCQ_ERR_UNSUPPORTED_K;
+  if (p.scale || p.groups || p.row_map || ex.n) return ARCQ_ERR_UNSUPPORTED_K;
 
   const size_t table = 160 + (((size_t)KQ * (rawidx ? 2 : 4) + 15) & ~(size_t)15);
   auto smem_for = [&](int nbuf, int pairs) {

@@ -342,10 +342,7 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         if positions is None:
             positions = torch.arange(seq, device=x_shard.device)
         k_eff = cfg.hidden + self.qkv.select_num
-        with self._ph("quantize"):
-            a_s, sfa_s = ops.rmsnorm_quantize_x(x_shard, self.ln1, cfg.eps, self.qkv.index, self.qkv.select_num)
-        with self._ph("collective"):
-            a, sfa = self._gather_quantized(a_s, sfa_s, rows_s, k_eff)
+        a, sfa = self._quantize_gathered(x_shard, self.ln1, self.qkv, rows_s, k_eff, self.peer_g1)
         with self._ph("gemm"):
             qkv = self.qkv.gemm(a, sfa)
         nq, nk = self.h_local * D, self.kv_local * D
@@ -361,10 +358,7 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         with self._ph("quantize"):
             qa, sfo, so = NVFP4_reorder_quantize_x(attn, self.o.index, self.o.select_num, mode=16)
         h_s = self._reduce_rows(self.o, qa, sfo, so, x_shard, self.peer_o)
-        with self._ph("quantize"):
-            a_s, sfa_s = ops.rmsnorm_quantize_x(h_s, self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
-        with self._ph("collective"):
-            a, sfa = self._gather_quantized(a_s, sfa_s, rows_s, k_eff)
+        a, sfa = self._quantize_gathered(h_s, self.ln2, self.gate_up, rows_s, k_eff, self.peer_g2)
         with self._ph("gemm"):
             act, amax = self._gate_up_act(a, sfa)
         with self._ph("quantize"):
@@ -374,14 +368,20 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
     # ---- row-parallel projection + reduce-scatter + residual
     peer_o = None       # peer.PeerSlots of the o / down projections once `enable_peer_scatter` has run
     peer_down = None
+    peer_g1 = None      # peer.PeerGathered: quantized input of the qkv / gate_up projections
+    peer_g2 = None
+    peer_barrier = None
 
     def enable_peer_scatter(self, total_rows: int) -> None:
         """Sequence-parallel steps over `total_rows` tokens from now on send the partial results of the o and down
         projections straight from the GEMM's epilogue into the owning rank's memory (`ops.matmul_scatter`) and
         finish the reduce-scatter with a barrier and one local pass that also adds the residual
         (`ops.sum_partials`), instead of a GEMM into local memory followed by NCCL's reduce-scatter and an
-        addition.  Collective call: every rank of the group, same arguments.  The ranks must share one machine."""
-        from .peer import PeerSlots
+        addition; the fused RMSNorm quantizers store their rows into every rank's gathered buffers
+        (`ops.rmsnorm_quantize_x_multi`) instead of an all-gather behind them; and the ranks meet at barriers
+        through flags in peer memory (`ops.peer_barrier`).  No NCCL call is left in the step.
+        Collective call: every rank of the group, same arguments.  The ranks must share one machine."""
+        from .peer import PeerBarrier, PeerGathered, PeerSlots
 
         rows_s = total_rows // self.tp
         if rows_s * self.tp != total_rows or rows_s % 128:
@@ -391,10 +391,13 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         # readers from its next writers)
         self.peer_o = PeerSlots(rows_s, self.cfg.hidden, self.rank, self.tp, self.group, dev)
         self.peer_down = PeerSlots(rows_s, self.cfg.hidden, self.rank, self.tp, self.group, dev)
-        self._peer_flag = torch.zeros(1, dtype=torch.float32, device=dev)
+        k_eff = self.cfg.hidden + self.qkv.select_num
+        self.peer_g1 = PeerGathered(rows_s, k_eff, self.rank, self.tp, self.group, dev)
+        self.peer_g2 = PeerGathered(rows_s, k_eff, self.rank, self.tp, self.group, dev)
+        self.peer_barrier = PeerBarrier(self.rank, self.tp, self.group, dev)
 
     def disable_peer_scatter(self) -> None:
-        for name in ("peer_o", "peer_down"):
+        for name in ("peer_o", "peer_down", "peer_g1", "peer_g2", "peer_barrier"):
             slots = getattr(self, name)
             if slots is not None:
                 slots.close()
@@ -408,10 +411,7 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
             with self._ph("gemm"):
                 ops.matmul_scatter(q, lin.W, sf, lin.SFW, scale_x, lin.scale, slots.dests)
             with self._ph("collective"):
-                # every rank's GEMM (and with it every store into this rank's slots) is complete once this small
-                # all-reduce, which follows the GEMM in each rank's stream, has finished here
-                if self.tp > 1:
-                    dist.all_reduce(self._peer_flag, group=self.group)
+                self.peer_barrier()      # every rank's GEMM, and with it every store into this rank's slots, is complete
             with self._ph("glue"):
                 out = torch.empty_like(residual_s)
                 return ops.sum_partials(slots.sources, residual_s.numel(), out, residual_s)
@@ -422,6 +422,21 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
             dist.reduce_scatter_tensor(y_s, y, op=dist.ReduceOp.SUM, group=self.group)
         with self._ph("glue"):
             return residual_s + y_s
+
+    def _quantize_gathered(self, x_s: torch.Tensor, gain: torch.Tensor, lin: PackedLinear, rows_s: int, k_eff: int,
+                           gathered):
+        """(codes [rows_s * tp, k_eff / 2], scales) of RMSNorm(x) over all ranks' token shards."""
+        if gathered is not None and gathered.q.shape[0] == rows_s * self.tp:
+            with self._ph("quantize"):
+                ops.rmsnorm_quantize_x_multi(x_s, gain, self.cfg.eps, lin.index, lin.select_num, gathered.q_dests,
+                                             gathered.sf_dests)
+            with self._ph("collective"):
+                self.peer_barrier()      # every rank's rows have arrived in this rank's copy
+            return gathered.q, gathered.sf
+        with self._ph("quantize"):
+            a_s, sfa_s = ops.rmsnorm_quantize_x(x_s, gain, self.cfg.eps, lin.index, lin.select_num)
+        with self._ph("collective"):
+            return self._gather_quantized(a_s, sfa_s, rows_s, k_eff)
 
     # ---- the same with communication hidden behind compute
     @staticmethod

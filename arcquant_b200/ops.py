@@ -487,3 +487,37 @@ def sum_partials(srcs, elems: int, out: torch.Tensor, residual: torch.Tensor | N
                                         out.data_ptr(), _stream())
     _lib.check(rc, f"sum of {n} partials, {elems} elements")
     return out
+
+
+def rmsnorm_quantize_x_multi(x, weight, eps: float, reorder_index, ke: int, q_dests, sf_dests) -> None:
+    """`rmsnorm_quantize_x` storing its output len(q_dests) times: q_dests[d] / sf_dests[d] are device addresses
+    (ints) of where these rows' codes and scale tiles start in destination d (this rank's or a peer's memory)."""
+    lib = _lib.load()
+    _require(x, torch.bfloat16, "input")
+    _require(weight, torch.bfloat16, "weight")
+    _require(reorder_index, torch.int16, "reorder_index")
+    rows, kq = x.shape
+    n = len(q_dests)
+    if weight.numel() != kq or reorder_index.numel() != kq or len(sf_dests) != n:
+        raise RuntimeError("gain / channel order must have one entry per channel; one scale address per code address")
+    qa = (C.c_void_p * n)(*[int(p) for p in q_dests])
+    sa = (C.c_void_p * n)(*[int(p) for p in sf_dests])
+    with torch.cuda.device(x.device):
+        rc = lib.arcq_rmsnorm_quantize_x_multi(x.data_ptr(), weight.data_ptr(), float(eps), reorder_index.data_ptr(),
+                                               rows, kq, ke, qa, sa, n, _stream())
+    _lib.check(rc, f"rmsnorm_quantize_x to {n} destinations, rows={rows} KQ={kq} KE={ke}")
+
+
+def peer_barrier(flag_blocks, rank: int, counter: torch.Tensor) -> None:
+    """Device-side barrier of a tensor-parallel group on the current stream (see `peer.PeerBarrier`)."""
+    lib = _lib.load()
+    n = len(flag_blocks)
+    arr = (C.c_void_p * n)(*[int(p) for p in flag_blocks])
+    with torch.cuda.device(counter.device):
+        rc = lib.arcq_peer_barrier(arr, int(rank), n, counter.data_ptr(), _stream())
+    _lib.check(rc, "peer barrier")
+
+
+def peer_poll_error() -> int:
+    """ARCQ_ERR_TIMEOUT if a peer barrier gave up waiting since the last poll (synchronises the device)."""
+    return int(_lib.load().arcq_peer_poll_error())

@@ -577,9 +577,11 @@ def layer_measure(dev, world, rank, steps, hbm_peak, tf_peak):
         del g_nccl
         try:
             layer.enable_peer_scatter(T)
-            res["form"] += ("; row-parallel GEMMs store their tiles straight into the owning rank's memory over NVLink "
-                            "(arcq_matmul_nvfp4_scatter), the reduce-scatter ends with a barrier and one local pass that "
-                            "also adds the residual (arcq_sum_partials_bf16)")
+            res["form"] += ("; no NCCL call in the step: the row-parallel GEMMs store their tiles straight into the owning "
+                            "rank's memory over NVLink (arcq_matmul_nvfp4_scatter) and the reduce-scatter ends with one local "
+                            "pass that also adds the residual (arcq_sum_partials_bf16); the RMSNorm quantizers store their rows "
+                            "into every rank's gathered buffers (arcq_rmsnorm_quantize_x_multi); four barriers through flags "
+                            "in peer memory (arcq_peer_barrier)")
         except Exception as exc:
             res["peer_scatter_error"] = repr(exc)[:300]
     res["eager_ms"] = max_over_ranks(time_ms(step, steps), dev)
@@ -596,12 +598,16 @@ def layer_measure(dev, world, rank, steps, hbm_peak, tf_peak):
     tot = layer.timer.totals()
     layer.timer = None
     res["eager_phase_ms"] = {k: v / 3 for k, v in tot.items()}
+    if layer.peer_barrier is not None:
+        from arcquant_b200 import ops
+        if ops.peer_poll_error() != 0:
+            raise RuntimeError("a peer barrier timed out: the ranks did not issue the same sequence of steps")
     if sp:
         ph = res["eager_phase_ms"]
         if layer.peer_o is not None:
             res["limiter"] = ("NVLink: each rank's o and down GEMMs send (N-1)/N of their bf16 result [16384, 4096] (134 MB) "
-                              "to the owners while they run (their time is in the gemm phase: %.2f ms); collective = two "
-                              "barriers and two all-gathers of packed codes (39 MB each): %.2f ms of the %.2f ms eager step" %
+                              "to the owners while they run (their time is in the gemm phase: %.2f ms); collective = the four "
+                              "barriers (waiting for the slowest rank included): %.2f ms of the %.2f ms eager step" %
                               (ph.get("gemm", 0.0), ph.get("collective", 0.0), sum(ph.values())))
         else:
             res["limiter"] = ("collectives: two reduce-scatters of the bf16 partial sums [16384, 4096] (134 MB each) and two "

@@ -316,8 +316,25 @@ int arcq_matmul_nvfp4_grouped_swiglu(const uint8_t* A, const uint8_t* B, const u
  *   arcq_peer_export can describe; _export writes the 64-byte handle another process on the same machine
  *   passes to arcq_peer_open, which maps the block into the calling process and enables peer access from the
  *   current device; _close unmaps it.  Handles travel by any host channel (the Python layer uses its process
- *   group's all_gather_object). */
+ *   group's all_gather_object).
+ * arcq_rmsnorm_quantize_x_multi: arcq_rmsnorm_quantize_x whose output bytes are stored ndests <= 8 times, at
+ *   (qx[d], sfx[d]) - host arrays of device addresses; in a sequence-parallel group the places of this
+ *   rank's token rows in every rank's gathered code and scale buffers (M a multiple of 128, so that the
+ *   rows' scale tiles are whole): the all-gather in front of a column-parallel projection happens while the
+ *   rows are quantized.
+ * arcq_peer_barrier: all ranks of the group have finished the work that precedes the call in their streams
+ *   before work that follows it in any rank's stream starts.  flags: host array of `world` device addresses,
+ *   flags[d] = rank d's block of `world` 32-bit words (zeroed once, before the handles are exchanged; peers'
+ *   blocks opened with arcq_peer_open); counter: a zero-initialised 32-bit word in this rank's memory that
+ *   counts its barriers (every rank must issue the same sequence of barriers).  One small kernel; its wait is
+ *   bounded (10 s), after which arcq_peer_poll_error() returns ARCQ_ERR_TIMEOUT (it synchronises the device
+ *   and clears the record). */
 #define ARCQ_PEER_HANDLE_BYTES 64
+int arcq_rmsnorm_quantize_x_multi(const void* x, const void* gamma, float eps, const int16_t* reorder_index,
+                                  int64_t M, int KQ, int KE, uint8_t* const* qx, uint8_t* const* sfx, int ndests,
+                                  void* stream);
+int arcq_peer_barrier(void* const* flags, int rank, int world, uint32_t* counter, void* stream);
+int arcq_peer_poll_error(void);
 int arcq_matmul_nvfp4_scatter(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                               int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b,
                               void* const* dests, int ndests, void* stream);

@@ -593,3 +593,32 @@ def test_peer_slots_on_one_rank_and_the_layers_reduce_step():
         assert torch.equal(layer.peer_o.local()[0], whole)
     finally:
         layer.disable_peer_scatter()
+
+
+def test_peer_barrier_and_gathered_buffers_on_one_rank():
+    """A group of one: the barrier kernel signals and waits on its own flag (its counter advances, nothing
+    times out), and `PeerGathered` hands the quantizer the start of this rank's rows."""
+    from arcquant_b200 import ops
+    from arcquant_b200.peer import PeerBarrier, PeerGathered
+
+    bar = PeerBarrier(0, 1)
+    for _ in range(5):
+        bar()
+    torch.cuda.synchronize()
+    assert int(bar.counter.item()) == 5
+    assert ops.peer_poll_error() == 0
+    assert int(bar.local_bytes()[:4].view(torch.int32).item()) == 5
+    bar.close()
+    rows, kq, ke = 256, 1024, 64
+    g = PeerGathered(rows, kq + ke, 0, 1)
+    x = synth.activations(rows, kq, 3, synth.outlier_channels(kq, 10, 2), device="cuda")
+    gain = torch.ones(kq, dtype=torch.bfloat16, device="cuda")
+    idx = synth.reorder_index_from_stats(x.abs().amax(0)).cuda()
+    ops.rmsnorm_quantize_x_multi(x, gain, 1e-5, idx, ke, g.q_dests, g.sf_dests)
+    q_ref, sf_ref = ops.rmsnorm_quantize_x(x, gain, 1e-5, idx, ke)
+    torch.cuda.synchronize()
+    assert torch.equal(g.q, q_ref)
+    n = min(g.sf.numel(), sf_ref.numel())
+    span = (rows // 128) * (((kq + ke) // 16 + 3) // 4) * 512
+    assert torch.equal(g.sf[:span], sf_ref[:span]) and n >= span
+    g.close()

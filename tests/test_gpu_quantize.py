@@ -312,3 +312,31 @@ def test_runs_on_the_current_stream_and_device_memory_only():
     O = _oracle()
     qo, _ = O.quantize_x(xs, idx.numpy(), 128)
     assert np.array_equal(q.cpu().numpy(), qo)
+
+
+@pytest.mark.parametrize("rows,kq,ke,nd", [(4096, 4096, 128, 4), (256, 4096, 128, 8), (2048, 2048, 64, 2), (1024, 8192, 256, 3)])
+def test_fused_operator_storing_its_output_several_times(rows, kq, ke, nd):
+    """`rmsnorm_quantize_x_multi`: the same bytes at every destination (here local buffers standing for the
+    peers' gathered buffers, each at its own offset inside a larger guarded allocation), equal to the
+    single-destination operator, which the other tests hold to the oracle."""
+    from arcquant_b200 import ops
+
+    dev = "cuda:0"
+    x = synth.activations(rows, kq, rows + 1, synth.outlier_channels(kq, kq // 100, 2), device=dev)
+    gain = (1.0 + 0.1 * torch.randn(kq, generator=torch.Generator().manual_seed(5))).to(torch.bfloat16).to(dev)
+    idx = synth.reorder_index_from_stats(x[:256].abs().amax(0)).to(dev)
+    q_ref, sf_ref = ops.rmsnorm_quantize_x(x, gain, 1e-5, idx, ke)
+    k_eff = kq + ke
+    tile = ((k_eff // 16 + 3) // 4) * 512
+    span = (rows // 128) * tile
+    qbuf = torch.full((nd, 3 * rows, k_eff // 2), 0x5A, dtype=torch.uint8, device=dev)
+    sfbuf = torch.full((nd, 3 * span), 0x5A, dtype=torch.uint8, device=dev)
+    ops.rmsnorm_quantize_x_multi(x, gain, 1e-5, idx, ke, [qbuf[d, rows:].data_ptr() for d in range(nd)],
+                                 [sfbuf[d, span:].data_ptr() for d in range(nd)])
+    torch.cuda.synchronize()
+    assert ops.gemm_poll_error() == 0
+    for d in range(nd):
+        assert torch.equal(qbuf[d, rows:2 * rows], q_ref), d
+        assert torch.equal(sfbuf[d, span:2 * span], sf_ref[:span]), d
+        assert bool((qbuf[d, :rows] == 0x5A).all()) and bool((qbuf[d, 2 * rows:] == 0x5A).all())
+        assert bool((sfbuf[d, :span] == 0x5A).all()) and bool((sfbuf[d, 2 * span:] == 0x5A).all())
