@@ -59,12 +59,13 @@ struct QuantParams {
   const int* row_map;
 };
 
-// Further copies of the output (warp-specialised fused RMSNorm kernel, MULTI variant): every code and scale
-// byte is also stored at its address plus dq[d] / dsf[d], d < n - the same rows of the gathered buffers of
-// the other ranks of a tensor-parallel group (peer memory), so that the all-gather happens while the rows are
-// made.
+// Further copies of the output (warp-specialised fused RMSNorm kernel, MULTI variant): every 8 bytes of codes
+// are also stored at their address plus dq[d], d < n - the same rows of the gathered buffers of the other
+// ranks of a tensor-parallel group (peer memory), so that the all-gather happens while the rows are made.
+// The scale bytes (single-byte stores here: a packet each on NVLink) follow in one copy of the rows' whole
+// scale tiles, arcq_broadcast_kernel.
 struct ExtraDests {
-  long long dq[7], dsf[7];
+  long long dq[7];
   int n;
 };
 
@@ -677,11 +678,9 @@ __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g,
   sf0[cm] = (uint8_t)codes;
 #pragma unroll 1
   for (int d = 0; MULTI && d < ex.n; ++d) {
-    const long long oq = ex.dq[d], os = ex.dsf[d];
+    const long long oq = ex.dq[d];
     *reinterpret_cast<uint2*>(q1 + oq + 8u * col) = c1;
-    (sf1 + os)[cm] = (uint8_t)(codes >> 8);
     *reinterpret_cast<uint2*>(q0 + oq + 8u * col) = c0;
-    (sf0 + os)[cm] = (uint8_t)codes;
   }
   if (!critical) return;
 
@@ -707,11 +706,9 @@ __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g,
   sf0[cr] = (uint8_t)rcodes;
 #pragma unroll 1
   for (int d = 0; MULTI && d < ex.n; ++d) {
-    const long long oq = ex.dq[d], os = ex.dsf[d];
+    const long long oq = ex.dq[d];
     *reinterpret_cast<uint2*>(q1 + oq + 8u * rcol) = e1;
-    (sf1 + os)[cr] = (uint8_t)(rcodes >> 8);
     *reinterpret_cast<uint2*>(q0 + oq + 8u * rcol) = e0;
-    (sf0 + os)[cr] = (uint8_t)rcodes;
   }
 }
 
@@ -1244,6 +1241,17 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   }
 }
 
+// `nvec` 16-byte words from src to each of n destinations (the scale tiles of a rank's rows to its peers).
+struct BroadcastDests {
+  uint4* p[7];
+};
+__global__ void arcq_broadcast_kernel(const uint4* __restrict__ src, const BroadcastDests dst, int n, long long nvec) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 v = src[i];
+    for (int d = 0; d < n; ++d) dst.p[d][i] = v;
+  }
+}
+
 __global__ void arcq_absmax_kernel(const uint4* __restrict__ x, long long nvec, const uint16_t* tail,
                                    int ntail, unsigned int* out) {
   uint32_t m = 0;
@@ -1349,10 +1357,12 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   p.row_map = row_map;
   ExtraDests ex = {};
   ex.n = nextra;
+  BroadcastDests bd = {};
   for (int d = 0; d < nextra && d < 7; ++d) {
     ex.dq[d] = (long long)(q_extra[d] - q);
-    ex.dsf[d] = (long long)(sf_extra[d] - sf);
+    bd.p[d] = reinterpret_cast<uint4*>(sf_extra[d]);
   }
+  if (nextra > 0 && rows % 128) return ARCQ_ERR_BAD_SHAPE;   // whole scale tiles travel
 
   const bool rms = gamma != nullptr;
   int nt, cpt;
@@ -1435,12 +1445,20 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
         const int kind = rms ? 0 : (p.scale ? 2 : 1);   // RMSNorm / plain / plain with the division
         if (ex.n > 0) {   // output stored several times: the fused RMSNorm operator only
           if (kind != 0) return ARCQ_ERR_UNSUPPORTED_K;
+          int rc_m = ARCQ_ERR_UNSUPPORTED_K;
 #define ARCQ_WS_MULTI(S_, R_) \
-  if (S == S_ && R == R_) return launch_ws<true, false, false, S_, R_, true>(p, nct, npt, nteams, npteams, smem, di, stream, ex);
+  if (S == S_ && R == R_) rc_m = launch_ws<true, false, false, S_, R_, true>(p, nct, npt, nteams, npteams, smem, di, stream, ex);
           ARCQ_WS_MULTI(2, 2) ARCQ_WS_MULTI(2, 4) ARCQ_WS_MULTI(2, 6) ARCQ_WS_MULTI(2, 8)
           ARCQ_WS_MULTI(4, 2) ARCQ_WS_MULTI(4, 4) ARCQ_WS_MULTI(4, 6) ARCQ_WS_MULTI(4, 8)
 #undef ARCQ_WS_MULTI
-          return ARCQ_ERR_UNSUPPORTED_K;
+          if (rc_m != ARCQ_OK) return rc_m;
+          // the rows' scale tiles, whole, to every other destination
+          const long long nvec = (rows / 128) * (long long)p.natoms * 32;
+          long long blocks = (nvec + 255) / 256;
+          if (blocks > (long long)di.num_sms * 4) blocks = (long long)di.num_sms * 4;
+          arcq_broadcast_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(sf), bd, ex.n, nvec);
+          ARCQ_CUDA_TRY(cudaGetLastError());
+          return ARCQ_OK;
         }
 #define ARCQ_WS_CASE(KIND_, RMS_, SCALED_, S_, R_) \
   if (kind == KIND_ && S == S_ && R == R_) \
