@@ -59,16 +59,6 @@ struct QuantParams {
   const int* row_map;
 };
 
-// Further copies of the output (warp-specialised fused RMSNorm kernel, MULTI variant): every 8 bytes of codes
-// are also stored at their address plus dq[d], d < n - the same rows of the gathered buffers of the other
-// ranks of a tensor-parallel group (peer memory), so that the all-gather happens while the rows are made.
-// The scale bytes (single-byte stores here: a packet each on NVLink) follow in one copy of the rows' whole
-// scale tiles, arcq_broadcast_kernel.
-struct ExtraDests {
-  long long dq[7];
-  int n;
-};
-
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
@@ -657,10 +647,8 @@ __device__ __forceinline__ void scale_of_pair_fma(uint32_t m, uint32_t& codes, f
 // for the odd last row: row 1 is stored first and row 0 overwrites it).  In every layout the codes of
 // scale column c start at byte 8 c of the row, and a critical group's residual sits 1 (mode 16) or 2
 // (mode 32) columns after its main part.
-template <bool MULTI>
 __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g, int G0, bool mode32, bool is_weight,
-                                                       uint8_t* q0, uint8_t* q1, uint8_t* sf0, uint8_t* sf1,
-                                                       const ExtraDests& ex) {
+                                                       uint8_t* q0, uint8_t* q1, uint8_t* sf0, uint8_t* sf1) {
   const uint32_t m = amax_pair_h(w);
   uint32_t codes;
   float2 dec, rcp;
@@ -676,12 +664,6 @@ __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g,
   sf1[cm] = (uint8_t)(codes >> 8);
   *reinterpret_cast<uint2*>(q0 + 8u * col) = c0;
   sf0[cm] = (uint8_t)codes;
-#pragma unroll 1
-  for (int d = 0; MULTI && d < ex.n; ++d) {
-    const long long oq = ex.dq[d];
-    *reinterpret_cast<uint2*>(q1 + oq + 8u * col) = c1;
-    *reinterpret_cast<uint2*>(q0 + oq + 8u * col) = c0;
-  }
   if (!critical) return;
 
   uint2 e0 = c0, e1 = c1;
@@ -704,12 +686,6 @@ __device__ __forceinline__ void quantize_group_pair_ws(uint32_t (&w)[16], int g,
   sf1[cr] = (uint8_t)(rcodes >> 8);
   *reinterpret_cast<uint2*>(q0 + 8u * rcol) = e0;
   sf0[cr] = (uint8_t)rcodes;
-#pragma unroll 1
-  for (int d = 0; MULTI && d < ex.n; ++d) {
-    const long long oq = ex.dq[d];
-    *reinterpret_cast<uint2*>(q1 + oq + 8u * rcol) = e1;
-    *reinterpret_cast<uint2*>(q0 + oq + 8u * rcol) = e0;
-  }
 }
 
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
@@ -752,10 +728,9 @@ __device__ __forceinline__ float div_guard(float s) {
 // npteams producer teams of npt = KQ/16 threads (more than one only with RMSNorm, whose producers carry
 // real arithmetic), sharing the pairs the same way; producer t of a team owns the 16-byte chunks t and
 // t + KQ/16 of each row, the reference's assignment and summation order for RMSNorm.
-template <bool RMS, bool WIDE, bool SCALED, int S, int R, bool MULTI = false>
+template <bool RMS, bool WIDE, bool SCALED, int S, int R>
 __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantParams p, const int nct, const int npt, const int nteams,
-                                                                        const int npteams,
-                                                                        const __grid_constant__ ExtraDests ex) {
+                                                                        const int npteams) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x;
   const int KQ = p.KQ, G = p.G;
@@ -1233,7 +1208,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
           if (lane == 0) mbar_arrive(empty0 + 8 * s);
           released = true;
         }
-        if (live) quantize_group_pair_ws<MULTI>(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1, ex);
+        if (live) quantize_group_pair_ws(w, g, G0, mode32, is_weight, q0, q1, sf0, sf1);
       }
       if (!released && lane == 0) mbar_arrive(empty0 + 8 * s);
       slot = slot + 1 == ncw ? 0 : slot + 1;
@@ -1241,7 +1216,10 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
   }
 }
 
-// `nvec` 16-byte words from src to each of n destinations (the scale tiles of a rank's rows to its peers).
+// `nvec` 16-byte words from src to each of n destinations: the codes and scale tiles a rank has just made of
+// its token rows, to the same place in its peers' gathered buffers (peer memory over NVLink).  Storing them from
+// inside the quantizer as they are made was measured no faster (the transfer is bound by NVLink either way) and
+// needs single-byte stores for the scales, a packet each.
 struct BroadcastDests {
   uint4* p[7];
 };
@@ -1271,10 +1249,10 @@ __global__ void arcq_absmax_kernel(const uint4* __restrict__ x, long long nvec, 
   if ((threadIdx.x & 31) == 0) atomicMax(out, r << 16);
 }
 
-template <bool RMS, bool WIDE, bool SCALED, int S, int R, bool MULTI = false>
+template <bool RMS, bool WIDE, bool SCALED, int S, int R>
 int launch_ws(const QuantParams& p, int nct, int npt, int nteams, int npteams, size_t smem, const DeviceInfo& di,
-              cudaStream_t stream, const ExtraDests& ex = ExtraDests()) {
-  auto kern = arcq_quantize_ws_kernel<RMS, WIDE, SCALED, S, R, MULTI>;
+              cudaStream_t stream) {
+  auto kern = arcq_quantize_ws_kernel<RMS, WIDE, SCALED, S, R>;
   const int threads = nteams * nct + npteams * (npt + (RMS ? 96 : 0));
   // the attribute and the occupancy query cost host time: once per (device, block size, shared memory)
   static thread_local int c_dev = -1, c_threads = 0, c_occ = 0;
@@ -1303,7 +1281,7 @@ int launch_ws(const QuantParams& p, int nct, int npt, int nteams, int npteams, s
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  ARCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p, nct, npt, nteams, npteams, ex));
+  ARCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p, nct, npt, nteams, npteams));
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
 }
@@ -1325,11 +1303,43 @@ int launch_variant(const QuantParams& p, int nt, size_t smem, const DeviceInfo& 
 
 }  // namespace
 
+static int launch_quantize_one(const void* x, const void* gamma, float eps, const int16_t* idx, int64_t rows, int KQ,
+                               int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream,
+                               const float* scale, const int* groups, int ngroups, const int* row_map);
+
 int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* idx, int64_t rows, int KQ,
                     int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream, const float* scale,
                     const int* groups, int ngroups, const int* row_map, uint8_t* const* q_extra,
                     uint8_t* const* sf_extra, int nextra) {
   if (rows == 0) return ARCQ_OK;
+  if (nextra > 0 && (rows % 128 || nextra > 7)) return ARCQ_ERR_BAD_SHAPE;   // whole scale tiles travel
+  int rc = launch_quantize_one(x, gamma, eps, idx, rows, KQ, KE, mode, is_weight, q, sf, stream, scale, groups,
+                               ngroups, row_map);
+  if (rc != ARCQ_OK || nextra == 0) return rc;
+  DeviceInfo di;
+  rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  BroadcastDests bq = {}, bs = {};
+  for (int d = 0; d < nextra; ++d) {
+    bq.p[d] = reinterpret_cast<uint4*>(q_extra[d]);
+    bs.p[d] = reinterpret_cast<uint4*>(sf_extra[d]);
+  }
+  const long long nq = rows * (long long)((KQ + KE) / 2) / 16;
+  const long long ns = (rows / 128) * (long long)(((KQ + KE) / 16 + 3) / 4) * 32;
+  const long long cap = (long long)di.num_sms * 8;
+  long long bl = (nq + 255) / 256;
+  arcq_broadcast_kernel<<<(unsigned)(bl < cap ? bl : cap), 256, 0, stream>>>(reinterpret_cast<const uint4*>(q), bq,
+                                                                            nextra, nq);
+  bl = (ns + 255) / 256;
+  arcq_broadcast_kernel<<<(unsigned)(bl < cap ? bl : cap), 256, 0, stream>>>(reinterpret_cast<const uint4*>(sf), bs,
+                                                                            nextra, ns);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
+
+static int launch_quantize_one(const void* x, const void* gamma, float eps, const int16_t* idx, int64_t rows, int KQ,
+                               int KE, int mode, int is_weight, uint8_t* q, uint8_t* sf, cudaStream_t stream,
+                               const float* scale, const int* groups, int ngroups, const int* row_map) {
   DeviceInfo di;
   int rc = get_device_info(&di);
   if (rc != ARCQ_OK) return rc;
@@ -1355,14 +1365,6 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
   p.groups = groups;
   p.ngroups = ngroups;
   p.row_map = row_map;
-  ExtraDests ex = {};
-  ex.n = nextra;
-  BroadcastDests bd = {};
-  for (int d = 0; d < nextra && d < 7; ++d) {
-    ex.dq[d] = (long long)(q_extra[d] - q);
-    bd.p[d] = reinterpret_cast<uint4*>(sf_extra[d]);
-  }
-  if (nextra > 0 && rows % 128) return ARCQ_ERR_BAD_SHAPE;   // whole scale tiles travel
 
   const bool rms = gamma != nullptr;
   int nt, cpt;
@@ -1443,23 +1445,6 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
       const size_t smem = fixed + (S + R) * stage;
       if (nteams >= 1 && smem <= (size_t)di.max_smem_optin) {
         const int kind = rms ? 0 : (p.scale ? 2 : 1);   // RMSNorm / plain / plain with the division
-        if (ex.n > 0) {   // output stored several times: the fused RMSNorm operator only
-          if (kind != 0) return ARCQ_ERR_UNSUPPORTED_K;
-          int rc_m = ARCQ_ERR_UNSUPPORTED_K;
-#define ARCQ_WS_MULTI(S_, R_) \
-  if (S == S_ && R == R_) rc_m = launch_ws<true, false, false, S_, R_, true>(p, nct, npt, nteams, npteams, smem, di, stream, ex);
-          ARCQ_WS_MULTI(2, 2) ARCQ_WS_MULTI(2, 4) ARCQ_WS_MULTI(2, 6) ARCQ_WS_MULTI(2, 8)
-          ARCQ_WS_MULTI(4, 2) ARCQ_WS_MULTI(4, 4) ARCQ_WS_MULTI(4, 6) ARCQ_WS_MULTI(4, 8)
-#undef ARCQ_WS_MULTI
-          if (rc_m != ARCQ_OK) return rc_m;
-          // the rows' scale tiles, whole, to every other destination
-          const long long nvec = (rows / 128) * (long long)p.natoms * 32;
-          long long blocks = (nvec + 255) / 256;
-          if (blocks > (long long)di.num_sms * 4) blocks = (long long)di.num_sms * 4;
-          arcq_broadcast_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(sf), bd, ex.n, nvec);
-          ARCQ_CUDA_TRY(cudaGetLastError());
-          return ARCQ_OK;
-        }
 #define ARCQ_WS_CASE(KIND_, RMS_, SCALED_, S_, R_) \
   if (kind == KIND_ && S == S_ && R == R_) \
     return launch_ws<RMS_, false, SCALED_, S_, R_>(p, nct, npt, nteams, npteams, smem, di, stream);
@@ -1475,7 +1460,7 @@ int launch_quantize(const void* x, const void* gamma, float eps, const int16_t* 
     }
   }
   // only the warp-specialised kernel divides by the scale, walks grouped rows or follows a row map
-  if (p.scale || p.groups || p.row_map || ex.n) return ARCQ_ERR_UNSUPPORTED_K;
+  if (p.scale || p.groups || p.row_map) return ARCQ_ERR_UNSUPPORTED_K;
 
   const size_t table = 160 + (((size_t)KQ * (rawidx ? 2 : 4) + 15) & ~(size_t)15);
   auto smem_for = [&](int nbuf, int pairs) {

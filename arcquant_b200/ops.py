@@ -490,8 +490,9 @@ def sum_partials(srcs, elems: int, out: torch.Tensor, residual: torch.Tensor | N
 
 
 def rmsnorm_quantize_x_multi(x, weight, eps: float, reorder_index, ke: int, q_dests, sf_dests) -> None:
-    """`rmsnorm_quantize_x` storing its output len(q_dests) times: q_dests[d] / sf_dests[d] are device addresses
-    (ints) of where these rows' codes and scale tiles start in destination d (this rank's or a peer's memory)."""
+    """`rmsnorm_quantize_x` into destination 0 and a copy of the result to the others: q_dests[d] / sf_dests[d]
+    are device addresses (ints) of where these rows' codes and scale tiles start in destination d (this rank's or
+    a peer's memory)."""
     lib = _lib.load()
     _require(x, torch.bfloat16, "input")
     _require(weight, torch.bfloat16, "weight")

@@ -8,9 +8,9 @@ group).  Three uses:
   GEMM stores the rows of its partial result that rank d owns (`ops.matmul_scatter`): the tiles cross NVLink
   while the GEMM is still running, and what is left of the reduce-scatter is a barrier and one pass over local
   memory (`ops.sum_partials`).
-* `PeerGathered`: the gathered packed codes and block scales of a sequence-parallel activation: every rank's
-  quantizer stores its token rows into every rank's copy (`ops.rmsnorm_quantize_x_multi`), so the all-gather
-  is over when the quantizers and a barrier are.
+* `PeerGathered`: the gathered packed codes and block scales of a sequence-parallel activation: every rank
+  quantizes its token rows into its own copy and stores them into every other rank's
+  (`ops.rmsnorm_quantize_x_multi`), so the all-gather is over when those stores and a barrier are.
 * `PeerBarrier`: that barrier - flags in peer memory, one small kernel per rank (`ops.peer_barrier`).
 
 The reference has no counterpart (its layers run on one GPU).

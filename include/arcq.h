@@ -317,11 +317,12 @@ int arcq_matmul_nvfp4_grouped_swiglu(const uint8_t* A, const uint8_t* B, const u
  *   passes to arcq_peer_open, which maps the block into the calling process and enables peer access from the
  *   current device; _close unmaps it.  Handles travel by any host channel (the Python layer uses its process
  *   group's all_gather_object).
- * arcq_rmsnorm_quantize_x_multi: arcq_rmsnorm_quantize_x whose output bytes are stored ndests <= 8 times, at
- *   (qx[d], sfx[d]) - host arrays of device addresses; in a sequence-parallel group the places of this
- *   rank's token rows in every rank's gathered code and scale buffers (M a multiple of 128, so that the
- *   rows' scale tiles are whole): the all-gather in front of a column-parallel projection happens while the
- *   rows are quantized.
+ * arcq_rmsnorm_quantize_x_multi: arcq_rmsnorm_quantize_x into (qx[0], sfx[0]), followed on the same stream by
+ *   a copy of the codes and of the rows' scale tiles to (qx[d], sfx[d]), 0 < d < ndests <= 8 - host arrays of
+ *   device addresses; in a sequence-parallel group the places of this rank's token rows in every rank's
+ *   gathered code and scale buffers (M a multiple of 128, so that the rows' scale tiles are whole).  With a
+ *   barrier behind it this is the all-gather in front of a column-parallel projection, written as stores
+ *   into the peers' memory.
  * arcq_peer_barrier: all ranks of the group have finished the work that precedes the call in their streams
  *   before work that follows it in any rank's stream starts.  flags: host array of `world` device addresses,
  *   flags[d] = rank d's block of `world` 32-bit words (zeroed once, before the handles are exchanged; peers'
