@@ -58,6 +58,7 @@ SIGNATURES = {
     "arcq_matmul_nvfp4_swiglu": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "arcq_matmul_nvfp4_grouped_swiglu": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp]),
     "arcq_moe_combine_bf16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
+    "arcq_matmul_nvfp4_residual": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),
     "arcq_matmul_nvfp4_scatter": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _vp]),
     "arcq_sum_partials_bf16": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp]),
     "arcq_rmsnorm_quantize_x_multi": (_i32, [_vp, _vp, _f32, _vp, _i64, _i32, _i32, _vp, _vp, _i32, _vp]),

@@ -348,6 +348,16 @@ int arcq_matmul_nvfp4_grouped_swiglu(const uint8_t* A, const uint8_t* B, const u
                              (cudaStream_t)stream, amax, groups);
 }
 
+int arcq_matmul_nvfp4_residual(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                               int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b,
+                               const void* residual, void* C, void* stream) {
+  int rc = check_gemm(A, B, SFA, SFB, M, N, K_eff, C);
+  if (rc != ARCQ_OK || M == 0) return rc;
+  if (!alpha_a || !residual) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(residual)) return ARCQ_ERR_ALIGNMENT;
+  return launch_gemm_residual(A, B, SFA, SFB, M, N, K_eff, alpha_a, alpha_b, residual, C, (cudaStream_t)stream);
+}
+
 int arcq_matmul_nvfp4_scatter(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                               int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b,
                               void* const* dests, int ndests, void* stream) {

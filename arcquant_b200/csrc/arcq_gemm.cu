@@ -124,6 +124,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// The same for data that is read once (an L2 evict-first policy keeps it from displacing the operands).
+__device__ __forceinline__ void tma_load_2d_once(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -402,7 +411,7 @@ constexpr int C2_STAGE_BYTES = C2_A_BYTES + C2_B_BYTES + C2_SFA_BYTES + C2_SFB_B
 constexpr int C2_SF_COLS = KSTEPS * 4 + KSTEPS * 8;  // 48 TMEM columns of scales per stage
 constexpr int C2_TMEM_COLS = 512;                    // 256 accumulator + 5 x 48 scale columns
 constexpr int C2_CSTAGE_BYTES = 4 * 8192;             // output staging: 32 rows x 128 columns of bf16 per epilogue warp
-constexpr int C2_SMEM_BYTES = 1024 + C2_STAGES * C2_STAGE_BYTES + C2_CSTAGE_BYTES + 256;
+constexpr int C2_SMEM_BYTES = 1024 + C2_STAGES * C2_STAGE_BYTES + C2_CSTAGE_BYTES + 256 + 64;   // + residual barriers
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;      // clears the pair-rank bit of a shared address
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -501,11 +510,16 @@ __device__ __forceinline__ void pair_tile_coords(int tile, const Gemm2Params& p,
   tm = first + (in_band - tn * rows);
 }
 
-template <bool SWIGLU>
+// RESID: the epilogue adds a residual tile (bf16 [M, N], map_r) to the bf16-rounded result before it stores:
+// C = bf16(R + bf16(alpha * A B^T)), what a bf16 addition after the GEMM computes.  The tile arrives by TMA in
+// the same staging memory the output leaves from (per-thread loads of 32 different rows per instruction would
+// hold up the scale warps' shared-memory loads, as per-thread stores did).
+template <bool SWIGLU, bool RESID = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C2_THREADS, 1)
 arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                  const __grid_constant__ OutputMaps maps_c, const Gemm2Params p) {
+                  const __grid_constant__ OutputMaps maps_c, const Gemm2Params p,
+                  const __grid_constant__ CUtensorMap map_r) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -520,6 +534,7 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   auto sf_ready_bar = [&](int s) { return bar_base + 8u * (3 * C2_STAGES + s); }; // scales in TMEM (leader's is used)
   const uint32_t tmem_full_bar = bar_base + 8u * (4 * C2_STAGES);
   const uint32_t tmem_empty_bar = tmem_full_bar + 8u;
+  auto resid_bar = [&](int q, int b) { return bar_base + 256u + 8u * (2 * q + b); };   // residual box landed in slot b of epilogue warp q
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();        // 0 = leader (issues the MMAs), 1 = peer
@@ -534,6 +549,7 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
     mbar_init(tmem_full_bar, 1);
     mbar_init(tmem_empty_bar, 8);                 // four epilogue warps in each of the two CTAs
+    for (int q = 0; q < 8; ++q) mbar_init(resid_bar(q >> 1, q & 1), 1);
     misc[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -633,7 +649,7 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       if (p.alpha_a) alpha *= __ldg(p.alpha_a);
       if (p.alpha_b) alpha *= __ldg(p.alpha_b);
     }
-    uint32_t tile_it = 0;
+    uint32_t tile_it = 0, resid_it = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
@@ -645,6 +661,15 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         alpha = p.alpha;
         if (p.alpha_a) alpha *= __ldg(p.alpha_a + grp);
         if (p.alpha_b) alpha *= __ldg(p.alpha_b + grp);
+      }
+      if (RESID) {
+        // the first residual box of this tile is fetched while the tile's MMAs are still running
+        const int row0r = tm * 256 + (int)rank * 128 + quad * 32;
+        if (lane == 0 && row0r < p.M) {
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // slot 0 is free again
+          mbar_expect_tx(resid_bar(quad, 0), 4096u);
+          tma_load_2d_once(cstage_base + (uint32_t)quad * 8192u, &map_r, resid_bar(quad, 0), tn * 256, row0r);
+        }
       }
       ok = mbar_wait(tmem_full_bar, tile_it & 1u, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -708,7 +733,49 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           map_c = &maps_c.m[d];
           row_st = row0 - d * p.rows_per_dest;
         }
-        if (row0 < p.M) {
+        if (RESID && row0 < p.M) {
+          // Four boxes of 64 columns, two slots: box k is added and stored from slot k & 1 while box k + 1 is
+          // on its way into the other slot (box 0 was requested before the accumulator was ready).
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int col = col0 + 64 * k;
+            if (col >= ncols) break;
+            const uint32_t slot = cst + (uint32_t)(k & 1) * 4096u;
+            if (lane == 0 && k + 1 < 4 && col + 64 < ncols) {
+              if (k >= 1) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // box k - 1 has left its slot
+              mbar_expect_tx(resid_bar(quad, (k + 1) & 1), 4096u);
+              tma_load_2d_once(cst + (uint32_t)((k + 1) & 1) * 4096u, &map_r, resid_bar(quad, (k + 1) & 1), col + 64, row0);
+            }
+            ok = mbar_wait(resid_bar(quad, k & 1), (resid_it >> (k & 1)) & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            resid_it ^= 1u << (k & 1);      // (bit b: parity of slot b's next box)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const int j = 32 * k + 4 * c;
+              const uint32_t addr = slot + (uint32_t)lane * 128u + (uint32_t)((c ^ (lane & 7)) << 4);
+              uint32_t r0, r1, r2, r3;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
+              const uint32_t rr[4] = {r0, r1, r2, r3};
+              uint32_t out4[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                out4[e] = pack_bf16x2(__uint_as_float(rr[e] << 16) + __uint_as_float(o[j + e] << 16),
+                                      __uint_as_float(rr[e] & 0xffff0000u) + __uint_as_float(o[j + e] & 0xffff0000u));
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(out4[0]), "r"(out4[1]), "r"(out4[2]),
+                           "r"(out4[3])
+                           : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map_c),
+                           "r"(slot), "r"(col), "r"(row_st)
+                           : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+        } else if (row0 < p.M) {
 #pragma unroll
           for (int h = 0; h < (SWIGLU ? 1 : 2); ++h) {
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging is free again
@@ -913,7 +980,7 @@ int make_c_map(CUtensorMap* map, const void* ptr, int64_t M, int64_t N) {
 int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M, int64_t N,
                 int64_t K_eff, const GemmParams& gp, int num_sms, cudaStream_t stream, const int* tile_group = nullptr,
                 int ngroups = 1, float* swiglu_amax = nullptr, const int* groups = nullptr,
-                void* const* dests = nullptr, int ndests = 0) {
+                void* const* dests = nullptr, int ndests = 0, const void* residual = nullptr) {
   Gemm2Params p;
   p.rows_per_dest = ndests > 0 ? (int)(M / ndests) : 0;
   p.amax = reinterpret_cast<unsigned int*>(swiglu_amax);
@@ -964,12 +1031,18 @@ int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   if (rc != ARCQ_OK) return rc;
   rc = make_sf_map(&msb, SFB, ((N * ngroups + 127) / 128) * (int64_t)gp.natoms);
   if (rc != ARCQ_OK) return rc;
-  auto kern = swiglu_amax != nullptr ? arcq_gemm2_kernel<true> : arcq_gemm2_kernel<false>;
+  CUtensorMap mr = mc.m[0];
+  if (residual != nullptr) {
+    rc = make_c_map(&mr, residual, M, N);
+    if (rc != ARCQ_OK) return rc;
+  }
+  auto kern = swiglu_amax != nullptr ? arcq_gemm2_kernel<true, false>
+                                     : (residual != nullptr ? arcq_gemm2_kernel<false, true> : arcq_gemm2_kernel<false, false>);
   ARCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C2_SMEM_BYTES));
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   long long clusters = num_sms / 2;
   if (clusters > tiles) clusters = tiles;
-  kern<<<(unsigned)(2 * clusters), C2_THREADS, C2_SMEM_BYTES, stream>>>(ma, mb, msa, msb, mc, p);
+  kern<<<(unsigned)(2 * clusters), C2_THREADS, C2_SMEM_BYTES, stream>>>(ma, mb, msa, msb, mc, p, mr);
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
 }
@@ -1074,6 +1147,28 @@ int launch_gemm_scatter(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, 
   p.natoms = (int)((K_eff / 16 + 3) / 4);
   p.splits = 1;
   return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream, nullptr, 1, nullptr, nullptr, dests, ndests);
+}
+
+// C = bf16(residual + bf16(alpha_a * alpha_b * A B^T)): always the CTA-pair kernel, whose epilogue fetches the
+// residual tile by TMA.
+int launch_gemm_residual(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                         int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b, const void* residual,
+                         void* Cout, cudaStream_t stream) {
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  GemmParams p = {};
+  p.c = static_cast<__nv_bfloat16*>(Cout);
+  p.alpha_a = alpha_a;
+  p.alpha_b = alpha_b;
+  p.alpha = 1.0f;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.ksteps_total = (int)(K_eff / 64);
+  p.natoms = (int)((K_eff / 16 + 3) / 4);
+  p.splits = 1;
+  return launch_pair(A, B, SFA, SFB, M, N, K_eff, p, di.num_sms, stream, nullptr, 1, nullptr, nullptr, nullptr, 0,
+                     residual);
 }
 
 size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K_eff) {

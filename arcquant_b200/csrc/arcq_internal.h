@@ -72,6 +72,9 @@ int launch_silu_mul_grouped(const void* gu, void* out, int64_t rows, int F, cons
 int launch_gemm_scatter(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                         int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b, void* const* dests,
                         int ndests, cudaStream_t stream);
+int launch_gemm_residual(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                         int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b, const void* residual,
+                         void* C, cudaStream_t stream);
 int launch_peer_barrier(void* const* flags, int rank, int world, unsigned int* counter, cudaStream_t stream);
 int peer_poll_error();
 int launch_sum_partials(const void* const* srcs, int n, int64_t elems, const void* residual, void* out,

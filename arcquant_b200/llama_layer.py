@@ -142,7 +142,11 @@ class PackedLinear(torch.nn.Module):
         self._set(W.contiguous(), SFW.contiguous(), get("scale"), index.contiguous(), select_num)
         return self
 
-    def gemm(self, qx, sfx, scale_x=None):
+    def gemm(self, qx, sfx, scale_x=None, residual=None):
+        """x W^T (+ residual, added in the GEMM's epilogue: for prefill-sized batches)."""
+        if residual is not None:
+            return ops.matmul_residual(qx, self.W, sfx, self.SFW, self.scale if scale_x is None else scale_x,
+                                       None if scale_x is None else self.scale, residual)
         if scale_x is None:
             return ops.matmul_dev_alpha(qx, self.W, sfx, self.SFW, self.scale, None)
         return ops.matmul_dev_alpha(qx, self.W, sfx, self.SFW, scale_x, self.scale)
@@ -251,7 +255,8 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
 
     # ---- halves of the layer up to (and excluding) the all-reduce: usable for in-process emulation
     @torch.no_grad()
-    def attn_partial(self, x2d: torch.Tensor, bsz: int, seq: int, positions: torch.Tensor) -> torch.Tensor:
+    def attn_partial(self, x2d: torch.Tensor, bsz: int, seq: int, positions: torch.Tensor,
+                     residual: torch.Tensor | None = None) -> torch.Tensor:
         cfg, D = self.cfg, self.cfg.head_dim
         with self._ph("quantize"):
             a, sfa = ops.rmsnorm_quantize_x(x2d, self.ln1, cfg.eps, self.qkv.index, self.qkv.select_num)
@@ -272,10 +277,10 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         with self._ph("quantize"):
             qa, sfo, so = NVFP4_reorder_quantize_x(attn, self.o.index, self.o.select_num, mode=16)
         with self._ph("gemm"):
-            return self.o.gemm(qa, sfo, so)
+            return self.o.gemm(qa, sfo, so, residual)
 
     @torch.no_grad()
-    def mlp_partial(self, h2d: torch.Tensor) -> torch.Tensor:
+    def mlp_partial(self, h2d: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         cfg = self.cfg
         with self._ph("quantize"):
             a, sfa = ops.rmsnorm_quantize_x(h2d, self.ln2, cfg.eps, self.gate_up.index, self.gate_up.select_num)
@@ -284,7 +289,7 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         with self._ph("quantize"):
             qd, sfd, sd = NVFP4_reorder_quantize_x(act, self.down.index, self.down.select_num, mode=16, amax=amax)
         with self._ph("gemm"):
-            return self.down.gemm(qd, sfd, sd)
+            return self.down.gemm(qd, sfd, sd, residual)
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
@@ -294,6 +299,10 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         x2d = x.reshape(bsz * seq, hidden).contiguous()
         if self.tp > 1 and x2d.shape[0] >= 2 * self.overlap_rows and self._dist_ready():
             return self._forward_overlapped(x2d, bsz, seq, positions).reshape(bsz, seq, hidden)
+        if self.tp == 1 and self.fuse_residual and x2d.shape[0] >= 1024:
+            # one rank, a prefill-sized batch: both residual additions happen in the epilogues of the o and down GEMMs
+            h = self.attn_partial(x2d, bsz, seq, positions, residual=x2d)
+            return self.mlp_partial(h, residual=h).reshape(bsz, seq, hidden)
         y = self.attn_partial(x2d, bsz, seq, positions)
         if self.tp > 1:      # (an unsharded layer inside a multi-rank process talks to nobody)
             with self._ph("collective"):
@@ -309,6 +318,7 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         return out.reshape(bsz, seq, hidden)
 
     overlap_rows = 4096   # rows per chunk of the overlapped schedule (a multiple of 128)
+    fuse_residual = True  # one rank: residual additions in the GEMM epilogues (same bits as separate additions)
 
     # ---- sequence-parallel form: the residual stream is sharded by tokens over the group
     def _gather_quantized(self, q_s: torch.Tensor, sf_s: torch.Tensor, rows_s: int, k_eff: int):

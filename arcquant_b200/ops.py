@@ -522,3 +522,31 @@ def peer_barrier(flag_blocks, rank: int, counter: torch.Tensor) -> None:
 def peer_poll_error() -> int:
     """ARCQ_ERR_TIMEOUT if a peer barrier gave up waiting since the last poll (synchronises the device)."""
     return int(_lib.load().arcq_peer_poll_error())
+
+
+def matmul_residual(a, b, sfa, sfb, alpha_a: torch.Tensor, alpha_b: torch.Tensor | None, residual: torch.Tensor,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 [M, N] = residual + bf16(alpha_a * alpha_b * (A.SFA)(B.SFB)^T), the addition done in the GEMM's epilogue
+    (same bits as `matmul_dev_alpha` followed by a bf16 addition)."""
+    lib = _lib.load()
+    for t, name in ((a, "A"), (b, "B"), (sfa, "SFA"), (sfb, "SFB")):
+        _require(t, torch.uint8, name)
+    _require(alpha_a, torch.float32, "alpha_a")
+    if alpha_b is not None:
+        _require(alpha_b, torch.float32, "alpha_b")
+    _require(residual, torch.bfloat16, "residual")
+    m, kb = a.shape
+    n = b.shape[0]
+    if b.shape[1] != kb or tuple(residual.shape) != (m, n):
+        raise RuntimeError("A and B disagree on K, or the residual is not [M, N]")
+    atoms = (kb * 2 // 16 + 3) // 4
+    if sfa.numel() < ((m + 127) // 128) * atoms * 512 or sfb.numel() < ((n + 127) // 128) * atoms * 512:
+        raise RuntimeError("scale buffers are smaller than the scale layout of their operands")
+    c = torch.empty((m, n), dtype=torch.bfloat16, device=a.device) if out is None else out
+    _require(c, torch.bfloat16, "out")
+    with torch.cuda.device(a.device):
+        rc = lib.arcq_matmul_nvfp4_residual(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), m, n, kb * 2,
+                                            alpha_a.data_ptr(), None if alpha_b is None else alpha_b.data_ptr(),
+                                            residual.data_ptr(), c.data_ptr(), _stream())
+    _lib.check(rc, f"matmul with residual M={m} N={n} K={kb * 2}")
+    return c

@@ -296,6 +296,15 @@ int arcq_matmul_nvfp4_grouped_swiglu(const uint8_t* A, const uint8_t* B, const u
                                      const int32_t* groups, int ngroups, const float* alpha_a, const float* alpha_b,
                                      void* C, float* amax, void* stream);
 
+/* ---- Projection with the residual addition in the GEMM's epilogue ---------------------------------------
+ * The reference adds the residual stream in torch after o_proj and down_proj (`residual + hidden_states`,
+ * model/qLlamaLayer.py:162, 168).  arcq_matmul_nvfp4_residual writes C = bf16(R + bf16(alpha_a * alpha_b *
+ * A B^T)) - the bits of that addition - with R (bf16 [M, N], may be C itself) fetched tile by tile in the
+ * epilogue instead of a pass of its own over [M, N].  Always the CTA-pair kernel (meant for prefill-sized M). */
+int arcq_matmul_nvfp4_residual(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
+                               int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b,
+                               const void* residual, void* C, void* stream);
+
 /* ---- Row-parallel projection fused with its reduce-scatter over peer memory -----------------------------
  * No counterpart in the reference (it runs on one GPU, model/qLlamaLayer.py:364, 442); these serve the
  * tensor-parallel form of its decoder layer, where the o and down projections are sharded by K and their

@@ -340,3 +340,32 @@ def test_scattered_output_against_the_oracle():
                       float(sx * sw))
     got = slots.reshape(m, n)[rt].float().cpu().numpy()
     _assert_close(got, ref)
+
+
+@pytest.mark.parametrize("m,n,kq", [(1024, 1024, 1024), (4100, 4104, 1024), (2048, 4096, 4096), (300, 9992, 512)])
+def test_residual_added_in_the_epilogue_equals_gemm_then_addition(m, n, kq):
+    """`matmul_residual`: bf16(R + bf16(GEMM)) from the epilogue - bit for bit the GEMM of the same kernel followed
+    by torch's bf16 addition; ragged shapes clip the residual boxes like the output boxes; rows beyond M stay
+    untouched."""
+    ops = _ops()
+    ke = 64
+    dev = "cuda:0"
+    out = synth.outlier_channels(kq, max(1, kq // 100), 1)
+    x = synth.activations(m, kq, m + 2, out, device=dev)
+    w = synth.weights(n, kq, n + 3, device=dev)
+    idx = synth.reorder_index_from_stats(x[:256].abs().amax(0)).to(dev)
+    sx, sw = ops.absmax(x) / 2688.0, ops.absmax(w) / 2688.0
+    a, sfa = ops.reorder_quantize_x((x / sx).to(torch.bfloat16), idx, ke)
+    b, sfb = ops.reorder_quantize_w((w / sw).to(torch.bfloat16), idx, ke)
+    res = (0.05 * torch.randn((m, n), generator=torch.Generator().manual_seed(9))).to(torch.bfloat16).to(dev)
+    whole = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    ops.matmul_scatter(a, b, sfa, sfb, sx, sw, [whole.data_ptr()]) if m % 32 == 0 else None
+    if m % 32:
+        # (the scattered launcher wants whole 32-row boxes; the plain launcher picks the pair kernel for these shapes)
+        whole = ops.matmul_dev_alpha(a, b, sfa, sfb, sx, sw)
+    guard = torch.full((m + 8, n), 7.0, dtype=torch.bfloat16, device=dev)
+    got = ops.matmul_residual(a, b, sfa, sfb, sx, sw, res, out=guard[:m])
+    torch.cuda.synchronize()
+    assert ops.gemm_poll_error() == 0
+    assert torch.equal(got, res + whole)
+    assert bool((guard[m:] == 7.0).all())

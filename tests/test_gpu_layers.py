@@ -622,3 +622,21 @@ def test_peer_barrier_and_gathered_buffers_on_one_rank():
     span = (rows // 128) * (((kq + ke) // 16 + 3) // 4) * 512
     assert torch.equal(g.sf[:span], sf_ref[:span]) and n >= span
     g.close()
+
+
+def test_residual_additions_in_the_gemm_epilogues_give_the_same_layer_output():
+    """One rank, a prefill-sized batch: `forward` adds both residuals in the epilogues of the o and down GEMMs;
+    the bytes must be those of the GEMMs followed by separate additions."""
+    from arcquant_b200.llama_layer import QLlamaDecoderLayerTP, random_layer_weights, random_reorder_indices
+
+    cfg = _small_cfg()
+    W, I = random_layer_weights(cfg, 0), random_reorder_indices(cfg, 1)
+    layer = QLlamaDecoderLayerTP(cfg, W, I)
+    x = synth.activations(4096, cfg.hidden, 4, synth.outlier_channels(cfg.hidden, 10, 3)).reshape(4, 1024, cfg.hidden).cuda()
+    pos = torch.arange(1024, device="cuda")
+    fused = layer(x, pos)
+    layer.fuse_residual = False
+    plain = layer(x, pos)
+    torch.cuda.synchronize()
+    # (the unfused o and down GEMMs run the same CTA-pair kernel at this size, so the sums agree bit for bit)
+    assert torch.equal(fused, plain)
