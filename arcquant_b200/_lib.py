@@ -62,6 +62,8 @@ SIGNATURES = {
     "arcq_matmul_nvfp4_scatter": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _vp]),
     "arcq_sum_partials_bf16": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp]),
     "arcq_rmsnorm_quantize_x_multi": (_i32, [_vp, _vp, _f32, _vp, _i64, _i32, _i32, _vp, _vp, _i32, _vp]),
+    "arcq_ep_send_layout": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "arcq_ep_rows": (_i32, [_vp, _vp, _i32, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "arcq_peer_barrier": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "arcq_peer_poll_error": (_i32, []),
     "arcq_peer_alloc": (_i32, [C.c_size_t, C.POINTER(C.c_void_p)]),

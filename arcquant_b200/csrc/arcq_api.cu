@@ -150,6 +150,33 @@ int arcq_rmsnorm_quantize_x_multi(const void* x, const void* gamma, float eps, c
                          (cudaStream_t)stream, nullptr, nullptr, 0, nullptr, qx + 1, sfx + 1, ndests - 1);
 }
 
+int arcq_ep_send_layout(const int64_t* ids, int n, int e_local, int ep, int cap, int rank, int32_t* slot,
+                        void* const* slot_tables, int32_t* overflow, void* stream) {
+  if (n < 0 || n > (1 << 20) || e_local < 1 || ep < 1 || ep > 8 || cap < 1 || rank < 0 || rank >= ep ||
+      (int64_t)ep * cap > (int64_t)0x3fffffff)
+    return ARCQ_ERR_BAD_SHAPE;
+  if ((n > 0 && (!ids || !slot)) || !slot_tables || !overflow) return ARCQ_ERR_NULL_POINTER;
+  for (int d = 0; d < ep; ++d)
+    if (!slot_tables[d]) return ARCQ_ERR_NULL_POINTER;
+  return launch_ep_send_layout(reinterpret_cast<const long long*>(ids), n, e_local, ep, cap, rank, slot, slot_tables,
+                               overflow, (cudaStream_t)stream);
+}
+
+int arcq_ep_rows(const void* src, const int32_t* item_src, int div, int src_limit, const int32_t* item_slot, int n,
+                 int row_bytes, int cap, int ep, int rank, void* const* dst, void* stream) {
+  if (n < 0 || div < 1 || src_limit < 0 || row_bytes <= 0 || row_bytes % 16 || cap < 1 || ep < 1 || ep > 8 || rank < 0 ||
+      rank >= ep || (int64_t)ep * cap > (int64_t)0x3fffffff)
+    return ARCQ_ERR_BAD_SHAPE;
+  if (n == 0) return ARCQ_OK;
+  if (!src || !dst) return ARCQ_ERR_NULL_POINTER;
+  if (!aligned16(src)) return ARCQ_ERR_ALIGNMENT;
+  for (int d = 0; d < ep; ++d) {
+    if (!dst[d]) return ARCQ_ERR_NULL_POINTER;
+    if (!aligned16(dst[d])) return ARCQ_ERR_ALIGNMENT;
+  }
+  return launch_ep_rows(src, item_src, div, src_limit, item_slot, n, row_bytes, cap, ep, rank, dst, (cudaStream_t)stream);
+}
+
 int arcq_peer_barrier(void* const* flags, int rank, int world, uint32_t* counter, void* stream) {
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return ARCQ_ERR_BAD_SHAPE;
   if (!flags || !counter) return ARCQ_ERR_NULL_POINTER;

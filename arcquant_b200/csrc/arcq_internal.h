@@ -75,6 +75,12 @@ int launch_gemm_scatter(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, 
 int launch_gemm_residual(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                          int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b, const void* residual,
                          void* C, cudaStream_t stream);
+// Expert-parallel dispatch through peer memory (arcq_layer.cu): places of this rank's routed copies in the peers'
+// receive buffers, and rows into the peers' buffers (both directions).
+int launch_ep_send_layout(const long long* ids, int n, int e_local, int ep, int cap, int rank, int* slot,
+                          void* const* meta, int* overflow, cudaStream_t stream);
+int launch_ep_rows(const void* src, const int* item_src, int div, int src_limit, const int* item_slot, int n, int row_bytes,
+                   int cap, int ep, int rank, void* const* dst, cudaStream_t stream);
 int launch_peer_barrier(void* const* flags, int rank, int world, unsigned int* counter, cudaStream_t stream);
 int peer_poll_error();
 int launch_sum_partials(const void* const* srcs, int n, int64_t elems, const void* residual, void* out,

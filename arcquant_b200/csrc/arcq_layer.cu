@@ -459,6 +459,90 @@ arcq_moe_layout_kernel(const long long* __restrict__ slot_group, int n, int ngro
   }
 }
 
+// Expert-parallel dispatch through peer memory, send side, one CTA: copy i of this rank goes to local expert
+// ids[i] % e_local of rank d = ids[i] / e_local and takes the next free place j of this rank's block in rank
+// d's receive buffer (places in copy order): slot[i] = d * cap + j, and the place's local expert is written
+// into rank d's slot table (meta.p[d][rank * cap + j]); places of the block that stay free are marked with
+// e_local ("nobody").  Copies beyond a block's capacity are dropped: slot[i] = ep * cap, *overflow set.
+struct PeerPtrs {
+  void* p[8];
+};
+__global__ void __launch_bounds__(1024, 1)
+arcq_ep_send_layout_kernel(const long long* __restrict__ ids, int n, int e_local, int ep, int cap, int rank,
+                           int* __restrict__ slot, const PeerPtrs meta, int* __restrict__ overflow) {
+  __shared__ int s_warp[32], s_total;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int per = (n + 1023) >> 10;
+  const int lo = min(n, tid * per), hi = min(n, lo + per);
+  for (int d = 0; d < ep; ++d) {
+    long long* table = static_cast<long long*>(meta.p[d]) + (size_t)rank * cap;
+    int mine = 0;
+    for (int i = lo; i < hi; ++i) {
+      const long long e = ids[i];
+      mine += (e >= 0 && e / e_local == d) ? 1 : 0;
+    }
+    int inc = mine;
+#pragma unroll
+    for (int k = 1; k < 32; k <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, inc, k);
+      if (lane >= k) inc += v;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane], winc = w;
+#pragma unroll
+      for (int k = 1; k < 32; k <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, winc, k);
+        if (lane >= k) winc += v;
+      }
+      s_warp[lane] = winc - w;
+      if (lane == 31) s_total = winc;
+    }
+    __syncthreads();
+    int r = s_warp[warp] + inc - mine;
+    const int total = s_total;
+    for (int i = lo; i < hi; ++i) {
+      const long long e = ids[i];
+      if (e >= 0 && e / e_local == d) {
+        if (r < cap) {
+          slot[i] = d * cap + r;
+          table[r] = e - (long long)d * e_local;
+        } else {
+          slot[i] = ep * cap;
+          *overflow = 1;
+        }
+        ++r;
+      }
+    }
+    for (int j = min(total, cap) + tid; j < cap; j += 1024) table[j] = e_local;
+    __syncthreads();                                   // s_warp / s_total are reused by the next rank
+  }
+  for (int i = lo; i < hi; ++i)
+    if (ids[i] < 0 || ids[i] >= (long long)ep * e_local) slot[i] = ep * cap;
+}
+
+// Rows into the peers' buffers, one warp per item: item i reads row (item_src ? item_src[i] : i / div) of src
+// (skipped if that is >= src_limit) and writes place rank * cap + s % cap of the buffer of rank s / cap, where
+// s = item_slot ? item_slot[i] : i (skipped if s >= ep * cap).  Dispatch: items = routed copies, s = their slot;
+// return trip: items = the places of this rank's receive buffer, read through the experts' padded layout.
+__global__ void arcq_ep_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ item_src, int div, int src_limit,
+                                    const int* __restrict__ item_slot, int n, int row_vec, int cap, int ep, int rank,
+                                    const PeerPtrs dst) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < n; i += warps) {
+    const int s = item_slot ? __ldg(item_slot + i) : i;
+    if (s < 0 || s >= ep * cap) continue;
+    const int r = item_src ? __ldg(item_src + i) : i / div;
+    if (r < 0 || r >= src_limit) continue;
+    const int d = s / cap;
+    const uint4* from = src + (size_t)r * row_vec;
+    uint4* to = static_cast<uint4*>(dst.p[d]) + ((size_t)rank * cap + (s - d * cap)) * row_vec;
+    for (int v = lane; v < row_vec; v += 32) to[v] = __ldg(from + v);
+  }
+}
+
 // Calibration statistics in one pass over the activations (utilize.py:108 and :546-547 of ARCQuant):
 // per-channel running max|x| and the number of elements larger than an eighth of their row's (signed)
 // maximum.  A CTA of 256 threads walks rows b, b + grid, ...; thread t owns the 16-byte chunks t, t + 256,
@@ -546,6 +630,32 @@ int launch_calib_stats(const void* x, int64_t rows, int K, float* chan_absmax, u
   else if (cpt <= 16) ARCQ_CALIB(16);
   else return ARCQ_ERR_UNSUPPORTED_K;
 #undef ARCQ_CALIB
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
+
+int launch_ep_send_layout(const long long* ids, int n, int e_local, int ep, int cap, int rank, int* slot,
+                          void* const* meta, int* overflow, cudaStream_t stream) {
+  PeerPtrs m = {};
+  for (int d = 0; d < ep; ++d) m.p[d] = meta[d];
+  arcq_ep_send_layout_kernel<<<1, 1024, 0, stream>>>(ids, n, e_local, ep, cap, rank, slot, m, overflow);
+  ARCQ_CUDA_TRY(cudaGetLastError());
+  return ARCQ_OK;
+}
+
+int launch_ep_rows(const void* src, const int* item_src, int div, int src_limit, const int* item_slot, int n, int row_bytes,
+                   int cap, int ep, int rank, void* const* dst, cudaStream_t stream) {
+  if (n == 0) return ARCQ_OK;
+  DeviceInfo di;
+  int rc = get_device_info(&di);
+  if (rc != ARCQ_OK) return rc;
+  PeerPtrs b = {};
+  for (int d = 0; d < ep; ++d) b.p[d] = dst[d];
+  long long blocks = ((long long)n + 7) / 8;              // eight warps (rows) per CTA
+  const long long capb = (long long)di.num_sms * 8;
+  if (blocks > capb) blocks = capb;
+  arcq_ep_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint4*>(src), item_src, div, src_limit,
+                                                           item_slot, n, row_bytes / 16, cap, ep, rank, b);
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
 }

@@ -228,6 +228,101 @@ class ExpertParallelDispatcher:
         return out
 
 
+class MoEPeerBuffers:
+    """What one rank of `PeerExpertDispatcher` needs: the addresses of every rank's receive buffer
+    [ep * cap, hidden] bf16, slot table [ep * cap] int64 and return buffer [ep * cap + 1, hidden] bf16 (its last row
+    stays zero: what dropped copies read), this rank's own three as tensors, and a barrier of the group."""
+
+    def __init__(self, cap: int, hidden: int, rank: int, ep: int, group=None, device=None):
+        from .peer import PeerBarrier, PeerBlock
+
+        self.cap, self.hidden, self.rank, self.ep = cap, hidden, rank, ep
+        self._blocks = [PeerBlock(ep * cap * hidden * 2, rank, ep, group, device),
+                        PeerBlock(ep * cap * 8, rank, ep, group, device),
+                        PeerBlock((ep * cap + 1) * hidden * 2, rank, ep, group, device)]
+        self.barrier = PeerBarrier(rank, ep, group, device)
+        self.recv_base, self.meta_base, self.ret_base = (b.base for b in self._blocks)
+        self.recv = self._blocks[0].local_bytes().view(torch.bfloat16).reshape(ep * cap, hidden)
+        self.meta = self._blocks[1].local_bytes().view(torch.int64)
+        self.ret = self._blocks[2].local_bytes().view(torch.bfloat16).reshape(ep * cap + 1, hidden)
+
+    def close(self) -> None:
+        for b in self._blocks + [self.barrier]:
+            b.close()
+
+    @staticmethod
+    def local_group(cap: int, hidden: int, ep: int, device) -> list:
+        """`ep` buffer sets in one process, each seeing the others' tensors as its peers (no barrier): all ranks
+        of a group emulated on one GPU, phase by phase."""
+        out = []
+        for r in range(ep):
+            b = MoEPeerBuffers.__new__(MoEPeerBuffers)
+            b.cap, b.hidden, b.rank, b.ep = cap, hidden, r, ep
+            b.recv = torch.zeros((ep * cap, hidden), dtype=torch.bfloat16, device=device)
+            b.meta = torch.zeros((ep * cap,), dtype=torch.int64, device=device)
+            b.ret = torch.zeros((ep * cap + 1, hidden), dtype=torch.bfloat16, device=device)
+            b.barrier = lambda: None
+            b._blocks = []
+            out.append(b)
+        for b in out:
+            b.recv_base = [o.recv.data_ptr() for o in out]
+            b.meta_base = [o.meta.data_ptr() for o in out]
+            b.ret_base = [o.ret.data_ptr() for o in out]
+        return out
+
+
+class PeerExpertDispatcher(ExpertParallelDispatcher):
+    """`ExpertParallelDispatcher` without collectives: every rank stores its routed rows (and the local expert of
+    each) straight into the memory of the ranks that own the experts, and the experts' output rows straight
+    back; a barrier through flags in peer memory follows each direction.  Three small launches and a barrier
+    replace the sort / scatter / gather / all-to-all sequence of the parent on the way out, one launch and a
+    barrier on the way back.  The capacity of a block is fixed at construction."""
+
+    def __init__(self, n_experts: int, buffers: MoEPeerBuffers):
+        super().__init__(n_experts, buffers.rank, buffers.ep, None, buffers.cap, None)
+        self.buf = buffers
+        self._overflow = torch.zeros(1, dtype=torch.int32, device=buffers.recv.device)
+
+    def overflowed(self) -> bool:
+        return bool(self._overflow.item())
+
+    # the two halves of `dispatch` (separate so that a test can run all ranks of a group in one process)
+    def send(self, x: torch.Tensor, ids: torch.Tensor) -> dict:
+        b = self.buf
+        T, k = ids.shape
+        flat = ids.reshape(-1).to(torch.int64).contiguous()
+        slot = ops.ep_send_layout(flat, self.e_local, self.ep, b.cap, self.rank, b.meta_base, self._overflow)
+        ops.ep_rows(x, None, k, T, slot, flat.numel(), b.cap, self.ep, self.rank, b.recv_base)
+        return dict(T=T, k=k, copy_row=slot)
+
+    def receive(self, state: dict) -> RoutedBatch:
+        b = self.buf
+        dest, row_slot, groups, tile_group, rows_bound = padded_layout(b.meta, self.e_local)
+        state = dict(state, slot_row=dest, rows_bound=rows_bound)
+        return RoutedBatch(b.recv, row_slot.to(torch.int32), groups, tile_group, rows_bound, self.e_local, state)
+
+    def dispatch(self, x: torch.Tensor, ids: torch.Tensor) -> RoutedBatch:
+        state = self.send(x, ids)
+        self.buf.barrier()          # every rank's rows and slot tables have arrived
+        return self.receive(state)
+
+    # and of `combine`
+    def send_back(self, y_rows: torch.Tensor, batch: RoutedBatch) -> None:
+        b, st = self.buf, batch.state
+        ops.ep_rows(y_rows, st["slot_row"].to(torch.int32), 1, st["rows_bound"], None, self.ep * b.cap, b.cap, self.ep,
+                    self.rank, b.ret_base)
+
+    def finish(self, weights: torch.Tensor, batch: RoutedBatch) -> torch.Tensor:
+        st = batch.state
+        pos = st["copy_row"].reshape(st["T"], st["k"])
+        return ops.moe_combine(self.buf.ret, pos.contiguous(), weights.to(torch.bfloat16).contiguous())
+
+    def combine(self, y_rows: torch.Tensor, weights: torch.Tensor, batch: RoutedBatch) -> torch.Tensor:
+        self.send_back(y_rows, batch)
+        self.buf.barrier()          # every expert's rows have come home
+        return self.finish(weights, batch)
+
+
 def random_moe_weights(cfg: MoEConfig, seed: int = 0, std: float = 0.02):
     g = torch.Generator().manual_seed(seed)
 
@@ -288,6 +383,32 @@ class QMixtralMoEBlockEP(torch.nn.Module):
         if self.grouped:
             self.gu_W, self.gu_SF, self.gu_scale, self.gu_index = _stack([gu for gu, _ in self.experts])
             self.dn_W, self.dn_SF, self.dn_scale, self.dn_index = _stack([dn for _, dn in self.experts])
+
+    def peer_capacity(self, tokens_per_rank: int, capacity_factor: float | None = 2.0) -> int:
+        """Rows one rank may send to one peer: all its copies (worst case), or `capacity_factor` times the even
+        share, rounded up to 128."""
+        copies = tokens_per_rank * self.cfg.top_k
+        if capacity_factor is None:
+            return copies
+        share = -(-copies // self.dispatcher.ep)
+        return min(copies, -(-int(share * capacity_factor) // 128) * 128)
+
+    def enable_peer_dispatch(self, tokens_per_rank: int, capacity_factor: float | None = 2.0) -> None:
+        """From now on rows travel to the experts' ranks and back as stores into peer memory
+        (`PeerExpertDispatcher`) instead of all-to-all collectives.  Collective call; the ranks share one machine."""
+        d = self.dispatcher
+        if d.ep == 1:
+            return
+        buf = MoEPeerBuffers(self.peer_capacity(tokens_per_rank, capacity_factor), self.cfg.hidden, d.rank, d.ep, d.group,
+                             self.router.device)
+        self.dispatcher = PeerExpertDispatcher(self.cfg.n_experts, buf)
+        self.dispatcher.group = d.group
+
+    def disable_peer_dispatch(self) -> None:
+        d = self.dispatcher
+        if isinstance(d, PeerExpertDispatcher):
+            d.buf.close()
+            self.dispatcher = ExpertParallelDispatcher(self.cfg.n_experts, d.rank, d.ep, d.group, d.capacity, None)
 
     @torch.no_grad()
     def expert_forward_grouped(self, batch: RoutedBatch) -> torch.Tensor:

@@ -550,3 +550,35 @@ def matmul_residual(a, b, sfa, sfb, alpha_a: torch.Tensor, alpha_b: torch.Tensor
                                             residual.data_ptr(), c.data_ptr(), _stream())
     _lib.check(rc, f"matmul with residual M={m} N={n} K={kb * 2}")
     return c
+
+
+def ep_send_layout(ids: torch.Tensor, e_local: int, ep: int, cap: int, rank: int, slot_tables, overflow: torch.Tensor):
+    """int32 [n]: place of every routed copy in the receive buffers of the experts' ranks (see
+    `arcq_ep_send_layout` in arcq.h); slot_tables: device addresses (ints) of every rank's slot table."""
+    lib = _lib.load()
+    _require(ids, torch.int64, "ids")
+    _require(overflow, torch.int32, "overflow")
+    n = ids.numel()
+    slot = torch.empty((n,), dtype=torch.int32, device=ids.device)
+    arr = (C.c_void_p * ep)(*[int(p) for p in slot_tables])
+    with torch.cuda.device(ids.device):
+        rc = lib.arcq_ep_send_layout(ids.data_ptr(), n, e_local, ep, cap, rank, slot.data_ptr(), arr, overflow.data_ptr(),
+                                     _stream())
+    _lib.check(rc, "ep_send_layout")
+    return slot
+
+
+def ep_rows(src: torch.Tensor, item_src, div: int, src_limit: int, item_slot, n: int, cap: int, ep: int, rank: int,
+            dsts) -> None:
+    """Rows of `src` [*, H] bf16 into the peers' buffers (see `arcq_ep_rows` in arcq.h); dsts: device addresses."""
+    lib = _lib.load()
+    _require(src, torch.bfloat16, "src")
+    for t, name in ((item_src, "item_src"), (item_slot, "item_slot")):
+        if t is not None:
+            _require(t, torch.int32, name)
+    arr = (C.c_void_p * ep)(*[int(p) for p in dsts])
+    with torch.cuda.device(src.device):
+        rc = lib.arcq_ep_rows(src.data_ptr(), None if item_src is None else item_src.data_ptr(), div, src_limit,
+                              None if item_slot is None else item_slot.data_ptr(), n, src.shape[1] * 2, cap, ep, rank,
+                              arr, _stream())
+    _lib.check(rc, "ep_rows")

@@ -699,6 +699,21 @@ def moe_measure(dev, world, rank, steps, hbm_peak, tf_peak):
     res = {"tokens": MOE_TOKENS, "parallelism": f"ep{world}", "scaling": "strong",
            "organisation": "one grouped launch per projection over all local experts; dispatch layout computed on "
                            "the device" if block.grouped else "per-expert loop"}
+    if world > 1:
+        # first over NCCL's all-to-all, then - the form reported - with the rows stored into the peers' memory
+        ms_e = max_over_ranks(time_ms(step, steps), dev)
+        g_nccl = GraphedStep(step)
+        ms_g = max_over_ranks(time_ms(g_nccl, steps), dev)
+        res["nccl_all_to_all_form"] = {"eager_ms": ms_e, "ms": ms_g, "tokens_per_s": MOE_TOKENS / (ms_g * 1e-3)}
+        del g_nccl
+        if block.dispatcher.overflowed():
+            raise RuntimeError("expert-parallel dispatch dropped copies: capacity factor too small for this routing")
+        try:
+            block.enable_peer_dispatch(hi - lo, 2.0)
+            res["organisation"] += ("; rows travel to the experts' ranks and back as stores into peer memory "
+                                    "(arcq_ep_send_layout, arcq_ep_rows, arcq_peer_barrier), no collective in the step")
+        except Exception as exc:
+            res["peer_dispatch_error"] = repr(exc)[:300]
     res["eager_ms"] = max_over_ranks(time_ms(step, steps), dev)
     try:
         graphed = GraphedStep(step)
@@ -711,7 +726,7 @@ def moe_measure(dev, world, rank, steps, hbm_peak, tf_peak):
     if block.dispatcher.overflowed():
         raise RuntimeError("expert-parallel dispatch dropped copies: capacity factor too small for this routing")
     if world > 1:
-        res["dispatch"] = f"all-to-all blocks of {block.dispatcher.capacity} rows per peer (2 x the even share)"
+        res["dispatch"] = f"blocks of {block.dispatcher.capacity} rows per peer (2 x the even share)"
     rf = moe_roofline(world, hbm_peak, tf_peak)
     res["roofline"] = dict(rf, frac=rf["sum_ms"] / res["ms"], achieved_ms=res["ms"])
     return res
@@ -754,7 +769,7 @@ def multi_gpu_parity(dev, world, rank):
         out["sp"] = max(out["sp"], rel(y_ps, ref[rank * rows:(rank + 1) * rows]))
         torch.cuda.synchronize()
     except RuntimeError as exc:
-        if "peer slots unavailable" not in str(exc):
+        if "peer memory unavailable" not in str(exc):
             raise
     import torch.distributed as dist
     dist.barrier()
@@ -769,6 +784,17 @@ def multi_gpu_parity(dev, world, rank):
     part = QMixtralMoEBlockEP(mcfg, MW, ep_rank=rank, ep_size=world, device=dev)(
         xt[lo:hi].contiguous(), routing=(ids[lo:hi].contiguous(), w[lo:hi].contiguous()))
     out["ep"] = rel(part, full[lo:hi])
+    peer_block = QMixtralMoEBlockEP(mcfg, MW, ep_rank=rank, ep_size=world, device=dev)
+    try:
+        peer_block.enable_peer_dispatch(hi - lo, None)
+        part = peer_block(xt[lo:hi].contiguous(), routing=(ids[lo:hi].contiguous(), w[lo:hi].contiguous()))
+        out["ep"] = max(out["ep"], rel(part, full[lo:hi]))
+        torch.cuda.synchronize()
+    except RuntimeError as exc:
+        if "peer memory unavailable" not in str(exc):
+            raise
+    dist.barrier()
+    peer_block.disable_peer_dispatch()
     worst = torch.tensor([out["tp"], out["sp"], out["ep"]], device=dev)
     dist.all_reduce(worst, op=dist.ReduceOp.MAX)
     out = {k: float(v) for k, v in zip(("tp", "sp", "ep"), worst.tolist())}

@@ -338,8 +338,23 @@ int arcq_matmul_nvfp4_residual(const uint8_t* A, const uint8_t* B, const uint8_t
  *   blocks opened with arcq_peer_open); counter: a zero-initialised 32-bit word in this rank's memory that
  *   counts its barriers (every rank must issue the same sequence of barriers).  One small kernel; its wait is
  *   bounded (10 s), after which arcq_peer_poll_error() returns ARCQ_ERR_TIMEOUT (it synchronises the device
- *   and clears the record). */
+ *   and clears the record).
+ * arcq_ep_send_layout / arcq_ep_rows: the dispatch of an expert-parallel MoE block (the per-expert loop of
+ *   model/qMixtralLayer.py:524-543 spread over `ep` ranks with e_local experts each) as stores into the peers'
+ *   memory instead of all-to-all collectives.  _send_layout (one small launch): copy i of this rank's n routed
+ *   copies, global expert ids[i], gets the next free place j of this rank's block of `cap` places in the receive
+ *   buffer of rank d = ids[i] / e_local: slot[i] = d * cap + j, and the place's local expert goes into rank d's
+ *   slot table, slot_tables[d][rank * cap + j] (int64; free places of the block receive e_local = nobody - the
+ *   form arcq_moe_layout reads).  Copies beyond the capacity are dropped (slot[i] = ep * cap, *overflow = 1).
+ *   _rows: one warp per item copies a row of `row_bytes` from src to place rank * cap + s % cap of the buffer
+ *   dst[s / cap], s = item_slot ? item_slot[i] : i (skipped when s >= ep * cap), reading row item_src ?
+ *   item_src[i] : i / div (skipped when >= src_limit): token rows to the experts' ranks, and the experts' output
+ *   rows back to the ranks of their tokens.  A barrier (arcq_peer_barrier) follows each. */
 #define ARCQ_PEER_HANDLE_BYTES 64
+int arcq_ep_send_layout(const int64_t* ids, int n, int e_local, int ep, int cap, int rank, int32_t* slot,
+                        void* const* slot_tables, int32_t* overflow, void* stream);
+int arcq_ep_rows(const void* src, const int32_t* item_src, int div, int src_limit, const int32_t* item_slot, int n,
+                 int row_bytes, int cap, int ep, int rank, void* const* dst, void* stream);
 int arcq_rmsnorm_quantize_x_multi(const void* x, const void* gamma, float eps, const int16_t* reorder_index,
                                   int64_t M, int KQ, int KE, uint8_t* const* qx, uint8_t* const* sfx, int ndests,
                                   void* stream);

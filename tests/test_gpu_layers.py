@@ -640,3 +640,56 @@ def test_residual_additions_in_the_gemm_epilogues_give_the_same_layer_output():
     torch.cuda.synchronize()
     # (the unfused o and down GEMMs run the same CTA-pair kernel at this size, so the sums agree bit for bit)
     assert torch.equal(fused, plain)
+
+
+@pytest.mark.parametrize("ep,cap_factor", [(2, None), (4, 2.0), (8, 2.0)])
+def test_expert_dispatch_through_peer_buffers_emulated_in_one_process(ep, cap_factor):
+    """`PeerExpertDispatcher` with all ranks of the group on one GPU (each rank's buffers are the others' "peer
+    memory", the phases of all ranks run one after another where the barriers would be): every rank's output must
+    equal its tokens' rows of the block that owns all experts - the same rows meet the same experts, only their
+    order inside an expert's run differs, and rows are independent of one another."""
+    from arcquant_b200.moe_block import (MoEConfig, MoEPeerBuffers, PeerExpertDispatcher, QMixtralMoEBlockEP,
+                                         random_moe_weights, route_top_k)
+
+    cfg = MoEConfig(hidden=1024, ffn=2048, n_experts=8, top_k=2, select_num=64)
+    MW = random_moe_weights(cfg, 0)
+    tokens = 1024
+    x = synth.activations(tokens, cfg.hidden, 5, synth.outlier_channels(cfg.hidden, 10, 3)).cuda()
+    ids, w = route_top_k(x, MW["router"].cuda(), cfg.top_k)
+    full = QMixtralMoEBlockEP(cfg, MW)(x, routing=(ids, w))
+    blocks = [QMixtralMoEBlockEP(cfg, MW, ep_rank=r, ep_size=ep) for r in range(ep)]
+    per = tokens // ep
+    cap = blocks[0].peer_capacity(per, cap_factor)
+    bufs = MoEPeerBuffers.local_group(cap, cfg.hidden, ep, x.device)
+    disp = [PeerExpertDispatcher(cfg.n_experts, b) for b in bufs]
+    sl = [slice(r * per, (r + 1) * per) for r in range(ep)]
+    for step in range(2):            # twice: the buffers are reused
+        states = [disp[r].send(x[sl[r]].contiguous(), ids[sl[r]].contiguous()) for r in range(ep)]
+        batches = [disp[r].receive(states[r]) for r in range(ep)]
+        ys = [blocks[r].expert_forward_grouped(batches[r]) for r in range(ep)]
+        for r in range(ep):
+            disp[r].send_back(ys[r], batches[r])
+        outs = [disp[r].finish(w[sl[r]].contiguous(), batches[r]) for r in range(ep)]
+        torch.cuda.synchronize()
+        assert not any(d.overflowed() for d in disp)
+        for r in range(ep):
+            assert torch.equal(outs[r], full[sl[r]]), (step, r)
+
+
+def test_expert_dispatch_drops_copies_beyond_the_capacity_and_says_so():
+    from arcquant_b200.moe_block import MoEPeerBuffers, PeerExpertDispatcher
+
+    ep, e_local, cap, hidden = 2, 2, 128, 256
+    bufs = MoEPeerBuffers.local_group(cap, hidden, ep, torch.device("cuda"))
+    disp = [PeerExpertDispatcher(ep * e_local, b) for b in bufs]
+    x = torch.randn((256, hidden), device="cuda").to(torch.bfloat16)
+    ids = torch.zeros((256, 1), dtype=torch.int64, device="cuda")            # every copy wants expert 0 of rank 0
+    st = disp[1].send(x, ids)
+    torch.cuda.synchronize()
+    assert disp[1].overflowed()
+    slot = st["copy_row"]
+    assert torch.equal(slot[:cap], torch.arange(cap, dtype=torch.int32, device="cuda"))       # block 0 = rank 0
+    assert bool((slot[cap:] == ep * cap).all())                                               # dropped
+    assert torch.equal(bufs[0].recv[cap:2 * cap], x[:cap])                                    # rank 1's block at rank 0
+    assert bool((bufs[0].meta[cap:2 * cap] == 0).all())
+    assert bool((bufs[1].meta[cap:2 * cap] == e_local).all())                                 # nothing for rank 1 itself

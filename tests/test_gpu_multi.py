@@ -88,6 +88,15 @@ def _worker(rank, world, port, q):
         part = QMixtralMoEBlockEP(mcfg, MW, ep_rank=rank, ep_size=world, device=dev)(
             xt[lo:hi].contiguous(), routing=(ids[lo:hi].contiguous(), w[lo:hi].contiguous()))
         err_ep = float((part.float() - full[lo:hi].float()).norm() / full[lo:hi].float().norm())
+        # the same with rows stored straight into the peers' memory (twice: the buffers are reused)
+        peer = QMixtralMoEBlockEP(mcfg, MW, ep_rank=rank, ep_size=world, device=dev)
+        peer.enable_peer_dispatch(hi - lo, None)
+        for _ in range(2):
+            got = peer(xt[lo:hi].contiguous(), routing=(ids[lo:hi].contiguous(), w[lo:hi].contiguous()))
+            if not torch.equal(got, full[lo:hi]) or peer.dispatcher.overflowed():
+                err_ep = max(err_ep, 1.0)
+        dist.barrier()
+        peer.disable_peer_dispatch()
         q.put((rank, err_tp, err_ep))
     finally:
         dist.destroy_process_group()
