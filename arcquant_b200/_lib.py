@@ -66,6 +66,7 @@ SIGNATURES = {
     "arcq_ep_rows": (_i32, [_vp, _vp, _i32, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "arcq_peer_barrier": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "arcq_peer_poll_error": (_i32, []),
+    "arcq_peer_set_wait_limit_ms": (_i32, [_i32]),
     "arcq_peer_alloc": (_i32, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "arcq_peer_free": (_i32, [_vp]),
     "arcq_peer_export": (_i32, [_vp, C.c_char_p]),

@@ -187,6 +187,8 @@ int arcq_peer_barrier(void* const* flags, int rank, int world, uint32_t* counter
 
 int arcq_peer_poll_error(void) { return peer_poll_error(); }
 
+int arcq_peer_set_wait_limit_ms(int ms) { return peer_set_wait_limit_ms(ms); }
+
 int arcq_reorder_quantize_w(const void* w, const int16_t* reorder_index, int64_t N, int KQ, int KE, int mode,
                             uint8_t* qw, uint8_t* sfw, void* stream) {
   int rc = check_quant_shape(N, KQ, KE, mode);

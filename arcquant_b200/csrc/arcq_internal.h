@@ -83,6 +83,7 @@ int launch_ep_rows(const void* src, const int* item_src, int div, int src_limit,
                    int cap, int ep, int rank, void* const* dst, cudaStream_t stream);
 int launch_peer_barrier(void* const* flags, int rank, int world, unsigned int* counter, cudaStream_t stream);
 int peer_poll_error();
+int peer_set_wait_limit_ms(int ms);
 int launch_sum_partials(const void* const* srcs, int n, int64_t elems, const void* residual, void* out,
                         cudaStream_t stream);
 // Device address of the 65536-entry table bf16(silu(g)) on the current device; the first call per device

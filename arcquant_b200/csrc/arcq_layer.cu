@@ -11,6 +11,7 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "arcq_internal.h"
@@ -697,10 +698,17 @@ int launch_moe_combine(const void* y, const int* pos, const void* w, void* out, 
   return ARCQ_OK;
 }
 
+static std::atomic<long long> g_peer_wait_limit_ms{10000};
+
+int peer_set_wait_limit_ms(int ms) {
+  return (int)g_peer_wait_limit_ms.exchange(ms < 1 ? 1 : ms);
+}
+
 int launch_peer_barrier(void* const* flags, int rank, int world, unsigned int* counter, cudaStream_t stream) {
   PeerFlags f = {};
   for (int d = 0; d < world; ++d) f.p[d] = static_cast<unsigned int*>(flags[d]);
-  arcq_peer_barrier_kernel<<<1, 32, 0, stream>>>(f, rank, world, counter, 10000000000ull);
+  arcq_peer_barrier_kernel<<<1, 32, 0, stream>>>(f, rank, world, counter,
+                                                 (unsigned long long)g_peer_wait_limit_ms.load() * 1000000ull);
   ARCQ_CUDA_TRY(cudaGetLastError());
   return ARCQ_OK;
 }

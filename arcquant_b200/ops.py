@@ -582,3 +582,8 @@ def ep_rows(src: torch.Tensor, item_src, div: int, src_limit: int, item_slot, n:
                               None if item_slot is None else item_slot.data_ptr(), n, src.shape[1] * 2, cap, ep, rank,
                               arr, _stream())
     _lib.check(rc, "ep_rows")
+
+
+def peer_set_wait_limit_ms(ms: int) -> int:
+    """Bound of the wait inside later `peer_barrier` launches (default 10 000 ms); returns the previous one."""
+    return int(_lib.load().arcq_peer_set_wait_limit_ms(int(ms)))

@@ -337,8 +337,10 @@ int arcq_matmul_nvfp4_residual(const uint8_t* A, const uint8_t* B, const uint8_t
  *   flags[d] = rank d's block of `world` 32-bit words (zeroed once, before the handles are exchanged; peers'
  *   blocks opened with arcq_peer_open); counter: a zero-initialised 32-bit word in this rank's memory that
  *   counts its barriers (every rank must issue the same sequence of barriers).  One small kernel; its wait is
- *   bounded (10 s), after which arcq_peer_poll_error() returns ARCQ_ERR_TIMEOUT (it synchronises the device
- *   and clears the record).
+ *   bounded (10 s; arcq_peer_set_wait_limit_ms changes the limit for later launches of this process and
+ *   returns the previous one), after which the kernel returns and arcq_peer_poll_error() reports
+ *   ARCQ_ERR_TIMEOUT (it synchronises the device and clears the record): a rank that never arrives costs its
+ *   peers that wait, not the GPU.
  * arcq_ep_send_layout / arcq_ep_rows: the dispatch of an expert-parallel MoE block (the per-expert loop of
  *   model/qMixtralLayer.py:524-543 spread over `ep` ranks with e_local experts each) as stores into the peers'
  *   memory instead of all-to-all collectives.  _send_layout (one small launch): copy i of this rank's n routed
@@ -360,6 +362,7 @@ int arcq_rmsnorm_quantize_x_multi(const void* x, const void* gamma, float eps, c
                                   void* stream);
 int arcq_peer_barrier(void* const* flags, int rank, int world, uint32_t* counter, void* stream);
 int arcq_peer_poll_error(void);
+int arcq_peer_set_wait_limit_ms(int ms);
 int arcq_matmul_nvfp4_scatter(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int64_t M,
                               int64_t N, int64_t K_eff, const float* alpha_a, const float* alpha_b,
                               void* const* dests, int ndests, void* stream);

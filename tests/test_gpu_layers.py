@@ -693,3 +693,25 @@ def test_expert_dispatch_drops_copies_beyond_the_capacity_and_says_so():
     assert torch.equal(bufs[0].recv[cap:2 * cap], x[:cap])                                    # rank 1's block at rank 0
     assert bool((bufs[0].meta[cap:2 * cap] == 0).all())
     assert bool((bufs[1].meta[cap:2 * cap] == e_local).all())                                 # nothing for rank 1 itself
+
+
+def test_peer_barrier_gives_up_when_a_rank_never_arrives():
+    """A group of two in which only rank 0 ever reaches the barrier (rank 1's flag is never written): the kernel
+    must return after its time limit and the host must be able to read that, with the GPU still usable."""
+    from arcquant_b200 import _lib, ops
+
+    flags = torch.zeros((2, 64), dtype=torch.int32, device="cuda")          # the two ranks' flag blocks
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    old = ops.peer_set_wait_limit_ms(300)
+    try:
+        ops.peer_barrier([flags[0].data_ptr(), flags[1].data_ptr()], 0, counter)
+        assert ops.peer_poll_error() == _lib.ERR_TIMEOUT
+        assert ops.peer_poll_error() == 0                                    # cleared by the read
+        assert int(flags[1, 0].item()) == 1 and int(flags[0, 0].item()) == 1  # rank 0 did announce itself to both
+        # the absent rank arrives late (its flag set by hand): the next barrier of rank 0 still needs epoch 2
+        flags[0, 1] = 2
+        ops.peer_barrier([flags[0].data_ptr(), flags[1].data_ptr()], 0, counter)
+        assert ops.peer_poll_error() == 0
+        assert torch.equal(torch.ones(4, device="cuda") * 2, torch.full((4,), 2.0, device="cuda"))
+    finally:
+        ops.peer_set_wait_limit_ms(old)
