@@ -468,7 +468,6 @@ struct Gemm2Params {
   int ksteps_total;   // K_eff / 64
   int natoms;         // scale atoms per 128-row tile
   int tiles_m, tiles_n;   // 256 x 256 tiles
-  int tma_store;          // output leaves through shared memory and bulk tensor stores (else: per-thread stores)
   int group_m;            // tile rows per band of the tile order (see pair_tile_coords)
   // Grouped problems (one launch over several weight matrices stacked in B): tile_group[tm] = which
   // matrix the 256-row tile tm of A multiplies, or a negative number for a tile that holds no rows
@@ -676,7 +675,6 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       if (!ok) break;
       tc_fence_after();
       const int row = tm * 256 + (int)rank * 128 + quad * 32 + lane;
-      __nv_bfloat16* crow = p.c + (size_t)row * p.N;
       // Drain the accumulator into registers as packed bf16 (128 registers for this thread's 256
       // columns) and hand tensor memory back at once: the stores below then overlap the next tile's MMAs.
       uint32_t o[128];
@@ -718,7 +716,7 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       }
       const int col0 = SWIGLU ? tn * 128 : tn * 256;
       const int ncols = SWIGLU ? (p.N >> 1) : p.N;
-      if (p.tma_store) {
+      {
         // Through shared memory: the warp's 32 rows x 256 columns leave as four boxes of 64 columns
         // (32 rows x 128 bytes, 128-byte swizzle: lane = row, 16-byte chunk c of row r sits at chunk
         // c ^ (r & 7), so a warp's 128-bit stores are conflict free), two boxes per round in the
@@ -805,12 +803,6 @@ arcq_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
           }
-        }
-      } else if (!SWIGLU && row < p.M) {
-#pragma unroll
-        for (int v = 0; v < 32; ++v) {          // 32 x 16 bytes = this row's 256 columns
-          if (col0 + v * 8 < p.N)
-            *reinterpret_cast<uint4*>(crow + col0 + v * 8) = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
         }
       }
       ++tile_it;
@@ -996,7 +988,6 @@ int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   p.natoms = gp.natoms;
   p.tiles_m = (int)((M + 255) / 256);
   p.tiles_n = (int)((N + 255) / 256);
-  p.tma_store = 1;
   // Column by column unless A alone overflows half of L2: then bands of 32 tile rows, whose A rows
   // (plus all of B) stay resident while the band lasts.  Measured on B200, the order makes no
   // difference beyond run-to-run noise for operands that fit.

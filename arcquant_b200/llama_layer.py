@@ -399,12 +399,20 @@ class QLlamaDecoderLayerTP(torch.nn.Module):
         dev = self.ln1.device
         # (two blocks: the barrier of one projection and the all-gather that follows it separate a block's
         # readers from its next writers)
-        self.peer_o = PeerSlots(rows_s, self.cfg.hidden, self.rank, self.tp, self.group, dev)
-        self.peer_down = PeerSlots(rows_s, self.cfg.hidden, self.rank, self.tp, self.group, dev)
         k_eff = self.cfg.hidden + self.qkv.select_num
-        self.peer_g1 = PeerGathered(rows_s, k_eff, self.rank, self.tp, self.group, dev)
-        self.peer_g2 = PeerGathered(rows_s, k_eff, self.rank, self.tp, self.group, dev)
-        self.peer_barrier = PeerBarrier(self.rank, self.tp, self.group, dev)
+        made = {}
+        try:     # all five blocks or none (a failure is raised on every rank together, see peer.PeerBlock)
+            made["peer_o"] = PeerSlots(rows_s, self.cfg.hidden, self.rank, self.tp, self.group, dev)
+            made["peer_down"] = PeerSlots(rows_s, self.cfg.hidden, self.rank, self.tp, self.group, dev)
+            made["peer_g1"] = PeerGathered(rows_s, k_eff, self.rank, self.tp, self.group, dev)
+            made["peer_g2"] = PeerGathered(rows_s, k_eff, self.rank, self.tp, self.group, dev)
+            made["peer_barrier"] = PeerBarrier(self.rank, self.tp, self.group, dev)
+        except Exception:
+            for block in made.values():
+                block.close()
+            raise
+        for name, block in made.items():
+            setattr(self, name, block)
 
     def disable_peer_scatter(self) -> None:
         for name in ("peer_o", "peer_down", "peer_g1", "peer_g2", "peer_barrier"):

@@ -237,10 +237,15 @@ class MoEPeerBuffers:
         from .peer import PeerBarrier, PeerBlock
 
         self.cap, self.hidden, self.rank, self.ep = cap, hidden, rank, ep
-        self._blocks = [PeerBlock(ep * cap * hidden * 2, rank, ep, group, device),
-                        PeerBlock(ep * cap * 8, rank, ep, group, device),
-                        PeerBlock((ep * cap + 1) * hidden * 2, rank, ep, group, device)]
-        self.barrier = PeerBarrier(rank, ep, group, device)
+        self._blocks = []
+        try:     # all four blocks or none (a failure is raised on every rank together, see peer.PeerBlock)
+            for nbytes in (ep * cap * hidden * 2, ep * cap * 8, (ep * cap + 1) * hidden * 2):
+                self._blocks.append(PeerBlock(nbytes, rank, ep, group, device))
+            self.barrier = PeerBarrier(rank, ep, group, device)
+        except Exception:
+            for b in self._blocks:
+                b.close()
+            raise
         self.recv_base, self.meta_base, self.ret_base = (b.base for b in self._blocks)
         self.recv = self._blocks[0].local_bytes().view(torch.bfloat16).reshape(ep * cap, hidden)
         self.meta = self._blocks[1].local_bytes().view(torch.int64)

@@ -42,48 +42,55 @@ class PeerBlock:
             raise ValueError("at most 8 ranks (one NVLink domain)")
         self.rank, self.world, self.nbytes = rank, world, int(nbytes)
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-        self._lib = _lib.load()
+        self._lib = None
         self._own = C.c_void_p()
         self._opened: list[int] = []
         self.base: list[int] = []
         # Every rank takes part in every exchange below whatever happened to it before, and all ranks raise
         # together: a rank that failed alone would leave the others waiting in a collective.
-        with torch.cuda.device(self.device):
-            err, mine = None, None
+        err, mine = None, None
+        try:
+            mine = self._make_own()
+        except Exception as exc:       # reported to the group below
+            err = repr(exc)
+        handles = [mine]
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, mine, group=group)
+        if err is None and all(h is not None for h in handles):
             try:
-                _lib.check(self._lib.arcq_peer_alloc(self.nbytes, C.byref(self._own)), "peer block: allocation")
-                self.local_bytes().zero_()
-                torch.cuda.synchronize()        # zeroed before any peer can learn the address
-                handle = C.create_string_buffer(_lib.PEER_HANDLE_BYTES)
-                _lib.check(self._lib.arcq_peer_export(self._own, handle), "peer block: export")
-                mine = bytes(handle.raw)
-            except Exception as exc:       # reported to the group below
+                for d in range(world):
+                    self.base.append(int(self._own.value) if d == rank else self._open(handles[d], d))
+            except Exception as exc:
                 err = repr(exc)
-            handles = [mine]
-            if world > 1:
-                handles = [None] * world
-                dist.all_gather_object(handles, mine, group=group)
-            if err is None and all(h is not None for h in handles):
-                try:
-                    for d in range(world):
-                        if d == rank:
-                            self.base.append(int(self._own.value))
-                            continue
-                        ptr = C.c_void_p()
-                        _lib.check(self._lib.arcq_peer_open(handles[d], C.byref(ptr)), f"peer block: opening rank {d}'s")
-                        self._opened.append(int(ptr.value))
-                        self.base.append(int(ptr.value))
-                except Exception as exc:
-                    err = repr(exc)
-            elif err is None:
-                err = "a peer could not allocate or export its block"
-            errs = [err]
-            if world > 1:
-                errs = [None] * world
-                dist.all_gather_object(errs, err, group=group)
-            if any(e is not None for e in errs):
-                self.close()
-                raise RuntimeError("peer memory unavailable: " + "; ".join(f"rank {i}: {e}" for i, e in enumerate(errs) if e))
+        elif err is None:
+            err = "a peer could not allocate or export its block"
+        errs = [err]
+        if world > 1:
+            errs = [None] * world
+            dist.all_gather_object(errs, err, group=group)
+        if any(e is not None for e in errs):
+            self.close()
+            raise RuntimeError("peer memory unavailable: " + "; ".join(f"rank {i}: {e}" for i, e in enumerate(errs) if e))
+
+    # the two device-side steps (a test replaces them with fakes to exercise the failure paths on CPU)
+    def _make_own(self) -> bytes:
+        """Allocate and zero this rank's block; the handle the peers open it with."""
+        self._lib = _lib.load()
+        with torch.cuda.device(self.device):
+            _lib.check(self._lib.arcq_peer_alloc(self.nbytes, C.byref(self._own)), "peer block: allocation")
+            self.local_bytes().zero_()
+            torch.cuda.synchronize()        # zeroed before any peer can learn the address
+            handle = C.create_string_buffer(_lib.PEER_HANDLE_BYTES)
+            _lib.check(self._lib.arcq_peer_export(self._own, handle), "peer block: export")
+        return bytes(handle.raw)
+
+    def _open(self, handle: bytes, owner: int) -> int:
+        ptr = C.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(self._lib.arcq_peer_open(handle, C.byref(ptr)), f"peer block: opening rank {owner}'s")
+        self._opened.append(int(ptr.value))
+        return int(ptr.value)
 
     def local_bytes(self) -> torch.Tensor:
         """This rank's block as a uint8 tensor (a view)."""

@@ -136,7 +136,46 @@ def _moe_overflow_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("worker", [_row_parallel_worker, _moe_worker, _moe_overflow_worker])
+def _peer_block_failure_worker(rank, world, port, q):
+    """Setting up peer memory when one rank cannot: the device steps are replaced by fakes (an allocation that
+    fails on rank 1; a mapping that fails on rank 0), everything else - the exchanges through the process
+    group - is the real code.  Every rank must come back with the same error instead of waiting for the other
+    in a collective, and a set-up in which nothing fails must work with the same fakes."""
+    _init(rank, world, port)
+    try:
+        from arcquant_b200.peer import PeerBlock
+
+        class Fake(PeerBlock):
+            fail_alloc_on = fail_open_on = None
+
+            def _make_own(self):
+                if self.rank == self.fail_alloc_on:
+                    raise RuntimeError("out of memory (fake)")
+                self._own.value = 0x1000 * (self.rank + 1)
+                return bytes([self.rank]) * 64
+
+            def _open(self, handle, owner):
+                if self.rank == self.fail_open_on:
+                    raise RuntimeError("cannot map (fake)")
+                return 0x100000 + handle[0]
+
+        ok = True
+        good = Fake(1024, rank, world, None, "cpu")
+        ok = ok and good.base == [0x1000 if rank == 0 else 0x100000, 0x100001 if rank == 0 else 0x2000]
+        for attr, who, text in (("fail_alloc_on", 1, "out of memory"), ("fail_open_on", 0, "cannot map")):
+            setattr(Fake, attr, who)
+            try:
+                Fake(1024, rank, world, None, "cpu")
+                ok = False
+            except RuntimeError as exc:
+                ok = ok and "peer memory unavailable" in str(exc) and f"rank {who}" in str(exc) and text in str(exc)
+            setattr(Fake, attr, None)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("worker", [_row_parallel_worker, _moe_worker, _moe_overflow_worker, _peer_block_failure_worker])
 def test_two_rank_gloo(worker):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
