@@ -49,7 +49,7 @@ BYTES_PER_TOKEN = 2 * HIDDEN + (HIDDEN + KE) // 2 + (HIDDEN + KE) // 16      # 1
 # current fused kernel summarised under profiles/: (134.28 + 15.80) MB / 16384 tokens (part of the output
 # is still dirty in L2 when the kernel ends, so the write part is below the algorithmic 2376 B/token);
 # traffic is proportional to tokens
-TRAFFIC_PER_TOKEN_NCU = 9160
+TRAFFIC_PER_TOKEN_NCU = 9147
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 NVLINK_GBS = 770.0          # measured peer copy, per direction per GPU
