@@ -46,7 +46,7 @@ MOE_TOKENS = 4096
 EPS = 1e-5
 BYTES_PER_TOKEN = 2 * HIDDEN + (HIDDEN + KE) // 2 + (HIDDEN + KE) // 16      # 10568
 # dram__bytes_read + dram__bytes_write per token, from the ncu capture of a 16384-token launch of the
-# current fused kernel summarised under profiles/: (134.28 + 15.80) MB / 16384 tokens (part of the output
+# current fused kernel summarised under profiles/: (134.28 + 15.59) MB / 16384 tokens (part of the output
 # is still dirty in L2 when the kernel ends, so the write part is below the algorithmic 2376 B/token);
 # traffic is proportional to tokens
 TRAFFIC_PER_TOKEN_NCU = 9147
