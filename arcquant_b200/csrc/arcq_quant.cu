@@ -703,20 +703,33 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 // rounding of the exact quotient.  With 8-bit significands mx, ms the quotient mx/ms is never within
 // 2^-18 (relative) of the midpoint of two bf16 values unless it is a bf16 value itself (a dyadic
 // mx/ms has at most 8 significant bits), while x*r is within 2^-23 of it; the same holds for the
-// fp32 quotient an IEEE division would round first.  Products outside a comfortable range take the
-// IEEE routine: products below 2^-60 in magnitude (a zero product is exact and keeps its sign, but
-// stays on that path with them) and NaNs.  There is no upper guard: a large product is as accurate as
-// any other, and where it overflows the quotient is beyond the largest bf16 number as well.  `qlo` is
-// 2^-60, or NaN (every comparison fails: IEEE routine throughout) when the divisor is so large or
-// small that 1/s is not a well-scaled normal number.
-__device__ __forceinline__ float div_shared(float x, float s, float r, float qlo) {
-  float q = __fmul_rn(x, r);
-  if (!(fabsf(q) >= qlo)) q = __fdiv_rn(x, s);
-  return q;
-}
-__device__ __forceinline__ float div_guard(float s) {
+// fp32 quotient an IEEE division would round first.  That argument needs a product that is a normal
+// number with room to spare.  Products below 2^-60 in magnitude may round differently from the quotient,
+// but never visibly: with the smallest block scale 2^-9 and the coarsest step of the e2m1 grid such an
+// element (and its residual) quantizes to a zero of its own sign either way, and a group in which every
+// element is that small gets the smallest scale either way - the codes and scale bytes, the only outputs,
+// are the same.  So there is no per-element guard (it cost more than the multiplication: a third of the
+// time of the wide operator); what is checked once is the divisor: when it is zero, not finite, or so
+// large or small that 1/s is not a well-scaled normal number, every element takes the IEEE division.
+// A large product is as accurate as any other, and where it overflows the quotient is beyond the largest
+// bf16 number as well; NaN and infinite elements give the same NaN / infinity either way.
+__device__ __forceinline__ bool div_by_reciprocal_ok(float s) {
   const float m = fabsf(s);
-  return (m >= 7.8886091e-31f && m <= 1.2676506e30f) ? 8.6736174e-19f : __int_as_float(0x7fc00000);   // 2^-100 .. 2^100
+  return m >= 7.8886091e-31f && m <= 1.2676506e30f;   // 2^-100 .. 2^100
+}
+// Words wa, wb: two channels of row 0 and of row 1.  o0 / o1: (row 0, row 1) of the first / second channel.
+__device__ __forceinline__ void div_pair_words(uint32_t wa, uint32_t wb, float s, float r, bool fast, uint32_t& o0,
+                                               uint32_t& o1) {
+  if (fast) {
+    const float2 r2 = make_float2(r, r);
+    const float2 q0 = __fmul2_rn(make_float2(bf16lo(wa), bf16lo(wb)), r2);
+    const float2 q1 = __fmul2_rn(make_float2(bf16hi(wa), bf16hi(wb)), r2);
+    o0 = pack_bf16x2_rn(q0.x, q0.y);
+    o1 = pack_bf16x2_rn(q1.x, q1.y);
+  } else {
+    o0 = pack_bf16x2_rn(__fdiv_rn(bf16lo(wa), s), __fdiv_rn(bf16lo(wb), s));
+    o1 = pack_bf16x2_rn(__fdiv_rn(bf16hi(wa), s), __fdiv_rn(bf16hi(wb), s));
+  }
 }
 
 // S: stages of the gather ring (interleaved row pairs).  R: stages of the raw ring (row pairs as they
@@ -1002,11 +1015,12 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
     bool failed = false;
     if (!RMS && WIDE) {
       const int hc = KQ >> 4;   // 16-byte chunks of half a row
-      float sc = 1.0f, rsc = 1.0f, qlo = 0.f;
+      float sc = 1.0f, rsc = 1.0f;
+      bool fast = true;
       if (SCALED) {
         sc = __uint_as_float(pack_bf16x2_rn(__ldg(scale_g), 0.f) << 16);   // (the divisor as bf16, see below)
         rsc = __frcp_rn(sc);
-        qlo = div_guard(sc);
+        fast = div_by_reciprocal_ok(sc);
       }
       const uint32_t nu = 2 * n;
       issued = nu < (uint32_t)R ? nu : (uint32_t)R;
@@ -1027,8 +1041,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
             uint4 lo, hi;
             if (SCALED) {
               auto dv = [&](uint32_t wa, uint32_t wb, uint32_t& o0, uint32_t& o1) {
-                o0 = pack_bf16x2_rn(div_shared(bf16lo(wa), sc, rsc, qlo), div_shared(bf16lo(wb), sc, rsc, qlo));
-                o1 = pack_bf16x2_rn(div_shared(bf16hi(wa), sc, rsc, qlo), div_shared(bf16hi(wb), sc, rsc, qlo));
+                div_pair_words(wa, wb, sc, rsc, fast, o0, o1);
               };
               dv(a.x, b.x, lo.x, lo.y); dv(a.y, b.y, lo.z, lo.w);
               dv(a.z, b.z, hi.x, hi.y); dv(a.w, b.w, hi.z, hi.w);
@@ -1053,12 +1066,13 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
       }
     } else if (!RMS) {
       const int nchunks = KQ >> 3;
-      float sc = 1.0f, rsc = 1.0f, qlo = 0.f;
+      float sc = 1.0f, rsc = 1.0f;
+      bool fast = true;
       if (SCALED) {
         // torch's CUDA kernel for (bf16 tensor) / (fp32 scalar tensor) loads the divisor as bf16
         sc = __uint_as_float(pack_bf16x2_rn(__ldg(scale_g), 0.f) << 16);
         rsc = __frcp_rn(sc);
-        qlo = div_guard(sc);
+        fast = div_by_reciprocal_ok(sc);
       }
       for (uint32_t it = 0; it < n; ++it) {
         const uint32_t unit = cta + it * stride;
@@ -1076,8 +1090,7 @@ __global__ void __launch_bounds__(1024, 1) arcq_quantize_ws_kernel(const QuantPa
             uint4 lo, hi;  // words of channels 8c..8c+3 and 8c+4..8c+7: (row0[ch], row1[ch]) per word
             if (SCALED) {
               auto dv = [&](uint32_t wa, uint32_t wb, uint32_t& o0, uint32_t& o1) {
-                o0 = pack_bf16x2_rn(div_shared(bf16lo(wa), sc, rsc, qlo), div_shared(bf16lo(wb), sc, rsc, qlo));
-                o1 = pack_bf16x2_rn(div_shared(bf16hi(wa), sc, rsc, qlo), div_shared(bf16hi(wb), sc, rsc, qlo));
+                div_pair_words(wa, wb, sc, rsc, fast, o0, o1);
               };
               dv(a.x, b.x, lo.x, lo.y); dv(a.y, b.y, lo.z, lo.w);
               dv(a.z, b.z, hi.x, hi.y); dv(a.w, b.w, hi.z, hi.w);
