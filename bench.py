@@ -474,7 +474,7 @@ def sweeps(dev, hbm_peak, tf_peak):
 
 def layer_roofline(world: int, hbm_peak: float, tf_peak: float, sp: bool):
     """Sum of the rooflines of one rank's share of the layer: GEMM flops at 4 x the measured bf16 rate,
-    quantizer and SiLU bytes at the measured HBM rate, attention flops at the bf16 rate, collective bytes
+    quantizer, max|x|, SiLU-output and rotary-embedding bytes at the measured HBM rate, attention flops at the bf16 rate, collective bytes
     at the measured NVLink rate."""
     T = LAYER_BATCH * LAYER_SEQ
     ke_r = KE if world == 1 else 64
@@ -486,7 +486,7 @@ def layer_roofline(world: int, hbm_peak: float, tf_peak: float, sp: bool):
     for kq in (4096 // world, FFN // world):                                       # o and down inputs
         nbytes += T * (quant_bytes_per_token(kq, ke_r))
     nbytes += T * 2 * (4096 // world)                                              # max|.| pass over the attention output
-    nbytes += T * 2 * (2 * FFN // world + FFN // world)                            # SiLU * up: read gate|up, write
+    nbytes += T * 2 * (FFN // world)                                               # SiLU * up: written by the GEMM's epilogue
     nbytes += T * 2 * (6144 // world) * 2                                          # rotary embedding in place
     attn_flops = 4.0 * LAYER_BATCH * LAYER_SEQ * LAYER_SEQ * (32 // world) * 128 * 0.5
     comm = 0.0
@@ -680,7 +680,8 @@ def moe_roofline(world: int, hbm_peak: float, tf_peak: float):
     R = MOE_TOKENS * 2 // world                                                   # routed copies per rank
     k1 = HIDDEN + KE
     flops = 2.0 * R * (2 * FFN * k1 + HIDDEN * (FFN + KE))
-    nbytes = R * (2 * HIDDEN + quant_bytes_per_token(HIDDEN, KE)) + R * 2 * 3 * FFN + R * (2 * FFN + quant_bytes_per_token(FFN, KE))
+    # (max|x| pass and quantizer over the routed rows; SiLU * up written by the GEMM's epilogue; its quantizer)
+    nbytes = R * (2 * HIDDEN + quant_bytes_per_token(HIDDEN, KE)) + R * 2 * FFN + R * quant_bytes_per_token(FFN, KE)
     nbytes += (8 // world) * (2 * FFN * k1 + HIDDEN * (FFN + KE)) * 9 // 16        # every local expert's weights once
     comm = 0.0 if world == 1 else 2 * (world - 1) / world * R * HIDDEN * 2
     t = {"gemm_ms": flops / (4 * tf_peak * 1e12) * 1e3, "hbm_ms": nbytes / (hbm_peak * 1e9) * 1e3,
