@@ -103,6 +103,11 @@ class ArcqError(RuntimeError):
         self.status = status
 
 
+CALLS = 0   # launching calls into the library that came back through `check` (what a caller may count)
+
+
 def check(status: int, where: str) -> None:
+    global CALLS
+    CALLS += 1
     if status != OK:
         raise ArcqError(status, where)
