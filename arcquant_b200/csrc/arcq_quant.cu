@@ -1471,8 +1471,10 @@ static int launch_quantize_one(const void* x, const void* gamma, float eps, cons
         const int kind = rms ? 0 : (p.scale ? 2 : 1);   // RMSNorm / plain / plain with the division
         // Fused RMSNorm with one or two whole warpgroups of consumers: registers move from the other warps to them
         // (1024 - ncons warps' worth at 56 leave at least 88 for the consumers).
+        // (Only where one CTA per SM is the rule anyway: narrow rows, whose CTAs are small enough for two per
+        // SM, keep their own thread count.)
         const int ncons = nteams * nct;
-        if (kind == 0 && (ncons == 128 || ncons == 256)) {
+        if (kind == 0 && (ncons == 128 || ncons == 256) && ncons + npteams * ptt > 512) {
 #define ARCQ_WS_XR(S_, R_) \
   if (S == S_ && R == R_) return launch_ws<true, false, false, S_, R_, true>(p, nct, npt, nteams, npteams, smem, di, stream);
           ARCQ_WS_XR(2, 2) ARCQ_WS_XR(2, 4) ARCQ_WS_XR(2, 6) ARCQ_WS_XR(2, 8)
