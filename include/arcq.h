@@ -306,7 +306,7 @@ int arcq_matmul_nvfp4_residual(const uint8_t* A, const uint8_t* B, const uint8_t
                                const void* residual, void* C, void* stream);
 
 /* ---- Row-parallel projection fused with its reduce-scatter over peer memory -----------------------------
- * No counterpart in the reference (it runs on one GPU, model/qLlamaLayer.py:364, 442); these serve the
+ * No counterpart in the reference (it runs on one GPU: o_proj and down_proj at model/qLlamaLayer.py:363-366, 439-443); these serve the
  * tensor-parallel form of its decoder layer, where the o and down projections are sharded by K and their
  * partial results must be added over the ranks, each rank keeping the token rows it owns.
  *
@@ -341,8 +341,8 @@ int arcq_matmul_nvfp4_residual(const uint8_t* A, const uint8_t* B, const uint8_t
  *   returns the previous one), after which the kernel returns and arcq_peer_poll_error() reports
  *   ARCQ_ERR_TIMEOUT (it synchronises the device and clears the record): a rank that never arrives costs its
  *   peers that wait, not the GPU.
- * arcq_ep_send_layout / arcq_ep_rows: the dispatch of an expert-parallel MoE block (the per-expert loop of
- *   model/qMixtralLayer.py:524-543 spread over `ep` ranks with e_local experts each) as stores into the peers'
+ * arcq_ep_send_layout / arcq_ep_rows: the dispatch of an expert-parallel MoE block (the loop over experts of
+ *   model/qMixtralLayer.py:458-471 spread over `ep` ranks with e_local experts each) as stores into the peers'
  *   memory instead of all-to-all collectives.  _send_layout (one small launch): copy i of this rank's n routed
  *   copies, global expert ids[i], gets the next free place j of this rank's block of `cap` places in the receive
  *   buffer of rank d = ids[i] / e_local: slot[i] = d * cap + j, and the place's local expert goes into rank d's
