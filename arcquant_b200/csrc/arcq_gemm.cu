@@ -988,10 +988,13 @@ int launch_pair(const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const ui
   p.natoms = gp.natoms;
   p.tiles_m = (int)((M + 255) / 256);
   p.tiles_n = (int)((N + 255) / 256);
-  // Column by column unless A alone overflows half of L2: then bands of 32 tile rows, whose A rows
-  // (plus all of B) stay resident while the band lasts.  Measured on B200, the order makes no
-  // difference beyond run-to-run noise for operands that fit.
-  p.group_m = (double)M * (double)K_eff / 2.0 > 64e6 ? 32 : p.tiles_m;
+  // Column by column (one strip of B shared by the whole wave, A streamed from L2 once per column) unless A
+  // alone overflows half of L2: then narrow bands of 4 tile rows, whose A rows stay resident next to B while
+  // the band lasts.  Measured on B200 (M 16384, PFLOP/s): the down projection (A 118 MB) 4.32 with bands of 32
+  // or 64 tile rows, 4.54 with 8 or 16, 4.62 - 4.65 with 4 (bands of 32 read A three times from HBM: 885 MB
+  // where the operands and the residual are 282 MB); gate_up, qkv and o (A 35 MB) within 1.5 % of one another
+  // for every band height from 8 to 64.
+  p.group_m = (double)M * (double)K_eff / 2.0 > 64e6 ? 4 : p.tiles_m;
   // grouped: tile rows of one matrix are neighbours, so narrow bands keep a strip of B shared by the
   // pairs that are in flight together
   if (tile_group != nullptr) p.group_m = 4;
