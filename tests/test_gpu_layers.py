@@ -507,6 +507,14 @@ def test_swiglu_epilogue_equals_gemm_then_silu(m, f, kq):
     got, amax_g = ops.matmul_swiglu(a, b2, sfa, sfb2, sx, sw)
     assert torch.equal(got, want)
     assert float(amax_g) == float(amax_w)
+    # gate values of every magnitude (tiny, huge, overflowing to infinity): same bits as the separate pass
+    for factor in (1e-6, 1e-12, 1e-30, 3e3, 1e8, 1e30, 3e36):
+        sx2 = (sx * factor).to(torch.float32)
+        want2, amax_w2 = ops.silu_mul(ops.matmul_dev_alpha(a, b1, sfa, sfb1, sx2, sw))
+        got2, amax_g2 = ops.matmul_swiglu(a, b2, sfa, sfb2, sx2, sw)
+        same = (got2 == want2) | (got2.isnan() & want2.isnan())
+        assert bool(same.all()), factor
+        assert float(amax_g2) == float(amax_w2) or (amax_g2.isnan() and amax_w2.isnan()), factor
     assert ops.gemm_poll_error() == 0
 
 
@@ -715,3 +723,4 @@ def test_peer_barrier_gives_up_when_a_rank_never_arrives():
         assert torch.equal(torch.ones(4, device="cuda") * 2, torch.full((4,), 2.0, device="cuda"))
     finally:
         ops.peer_set_wait_limit_ms(old)
+
