@@ -140,3 +140,58 @@ def test_agemm_argument_checks_on_device_tensors():
         agemm.matmul_dev_alpha(a, b, sf, sf, torch.ones(2, device=dev), None)
     torch.cuda.synchronize()                                          # nothing was launched, nothing faulted
     assert agemm.matmul(a, b, sf, sf, 1.0).shape == (4, 8)
+
+
+def test_peer_and_scatter_entry_points_validate_before_any_cuda_call():
+    """The entry points of the tensor- / expert-parallel forms refuse bad shapes and null pointers on the host."""
+    import ctypes as C
+
+    from arcquant_b200 import _lib, ops
+
+    L = _lib.load()
+    p = 1 << 12
+    two = (C.c_void_p * 2)(p, p)
+    hole = (C.c_void_p * 2)(p, None)
+    # GEMM with scattered output: 1..8 destinations, rows split evenly in multiples of 32, no null destination
+    assert L.arcq_matmul_nvfp4_scatter(p, p, p, p, 128, 64, 64, p, None, None, 2, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_matmul_nvfp4_scatter(p, p, p, p, 128, 64, 64, p, None, two, 9, None) == _lib.ERR_BAD_SHAPE
+    assert L.arcq_matmul_nvfp4_scatter(p, p, p, p, 96, 64, 64, p, None, two, 2, None) == _lib.ERR_BAD_SHAPE      # 48 rows each
+    assert L.arcq_matmul_nvfp4_scatter(p, p, p, p, 128, 64, 64, p, None, hole, 2, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_matmul_nvfp4_scatter(p, p, p, p, 128, 64, 64, None, None, two, 2, None) == _lib.ERR_NULL_POINTER   # alpha_a
+    assert L.arcq_matmul_nvfp4_residual(p, p, p, p, 128, 64, 64, p, None, None, p, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_matmul_nvfp4_residual(p, p, p, p, 128, 64, 64, p, None, p + 2, p, None) == _lib.ERR_ALIGNMENT
+    # sum of partial results
+    assert L.arcq_sum_partials_bf16(two, 0, 1024, None, p, None) == _lib.ERR_BAD_SHAPE
+    assert L.arcq_sum_partials_bf16(two, 2, 1020, None, p, None) == _lib.ERR_BAD_SHAPE                 # elems % 8
+    assert L.arcq_sum_partials_bf16(hole, 2, 1024, None, p, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_sum_partials_bf16(two, 2, 0, None, p, None) == _lib.OK
+    # quantizer with several destinations
+    assert L.arcq_rmsnorm_quantize_x_multi(p, p, 1e-5, p, 128, 4096, 128, two, two, 0, None) == _lib.ERR_BAD_SHAPE
+    assert L.arcq_rmsnorm_quantize_x_multi(p, p, 1e-5, p, 128, 4096, 128, two, hole, 2, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_rmsnorm_quantize_x_multi(p, p, 1e-5, p, 128, 1000, 0, two, two, 2, None) != _lib.OK   # width
+    # barrier and expert-parallel dispatch
+    assert L.arcq_peer_barrier(two, 2, 2, p, None) == _lib.ERR_BAD_SHAPE                               # rank outside the group
+    assert L.arcq_peer_barrier(two, 0, 9, p, None) == _lib.ERR_BAD_SHAPE
+    assert L.arcq_peer_barrier(hole, 0, 2, p, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_peer_barrier(two, 0, 2, None, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_ep_send_layout(p, 16, 2, 9, 128, 0, p, two, p, None) == _lib.ERR_BAD_SHAPE           # more than 8 ranks
+    assert L.arcq_ep_send_layout(p, 16, 2, 2, 128, 2, p, two, p, None) == _lib.ERR_BAD_SHAPE           # rank outside
+    assert L.arcq_ep_send_layout(p, 16, 2, 2, 128, 0, p, hole, p, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_ep_rows(p, None, 2, 16, None, 32, 100, 128, 2, 0, two, None) == _lib.ERR_BAD_SHAPE   # row bytes % 16
+    assert L.arcq_ep_rows(p, None, 0, 16, None, 32, 128, 128, 2, 0, two, None) == _lib.ERR_BAD_SHAPE   # div
+    assert L.arcq_ep_rows(p, None, 2, 16, None, 0, 128, 128, 2, 0, two, None) == _lib.OK               # nothing to move
+    assert L.arcq_peer_export(None, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_peer_open(None, None) == _lib.ERR_NULL_POINTER
+    assert L.arcq_peer_set_wait_limit_ms(L.arcq_peer_set_wait_limit_ms(1234)) == 1234
+    # the torch-facing wrappers refuse host tensors
+    u8 = torch.zeros(64, 32, dtype=torch.uint8)
+    sf = torch.zeros(512, dtype=torch.uint8)
+    s = torch.tensor(1.0)
+    for call in (lambda: ops.matmul_scatter(u8, u8, sf, sf, s, None, [p]),
+                 lambda: ops.matmul_residual(u8, u8, sf, sf, s, None, torch.zeros(64, 64, dtype=torch.bfloat16)),
+                 lambda: ops.sum_partials([p], 64, torch.zeros(64, dtype=torch.bfloat16)),
+                 lambda: ops.rmsnorm_quantize_x_multi(torch.zeros(128, 4096, dtype=torch.bfloat16),
+                                                      torch.zeros(4096, dtype=torch.bfloat16), 1e-5,
+                                                      torch.zeros(4096, dtype=torch.int16), 128, [p], [p])):
+        with pytest.raises(RuntimeError, match="CUDA tensor"):
+            call()
